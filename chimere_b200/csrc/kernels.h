@@ -1,0 +1,77 @@
+// kernels.h -- parameter blocks and launchers shared by the .cu files of the library.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace chimere {
+
+// layout of the workspace's integer scratch ("counters"); everything returns to zero after a call
+constexpr int kCtrRouteAll = 0;    // token tiles whose top-k is done
+constexpr int kCtrRouteTile = 16;  // [ceil(max_T/8)] row tiles done per token tile
+// the combine counters follow at ws-specific offset (one per token and output row tile)
+
+struct RouteParams {
+    int T, H, E, top_k, route_mode, has_shared;
+    float route_scale;
+    const float* x;             // [T][H]
+    const float* router_w;      // [E][H]
+    const float* router_bias;   // [E] or null
+    const float* shexp_gate_w;  // [H] or null
+    float* router_logits;       // [T][E]
+    float* sh_gate_logit;       // [T]
+    int32_t* topk_idx;          // [T][k]
+    float* topk_w;              // [T][k]
+    uint8_t* x_q8;              // [T][H/32][36]
+    int32_t* perm;              // [T*k]
+    int32_t* offsets;           // [E+1]
+    int32_t* group_list;
+    int32_t* counters;
+};
+
+// Grouped GEMV over work entries (see common.cuh for the list layout).
+struct GemvParams {
+    int T, top_k, H;
+    int ncols_routed, ncols_shared;  // input width: H, H for gate/up; F, F_s for down
+    int nrows_routed, nrows_shared;  // output rows per expert: F, F_s for gate/up; H, H for down
+    int act;                     // CHIMERE_ACT_* (gate/up stage)
+    int type_routed, type_shared;
+    const int32_t* group_list;
+    const int32_t* perm;
+    // weights
+    const uint8_t* w_a;          // gate (or null) / down
+    const uint8_t* w_b;          // up
+    int64_t stride_a, stride_b;  // bytes per routed expert
+    const uint8_t* sh_a;         // shared-expert gate (or null) / down
+    const uint8_t* sh_b;         // shared-expert up
+    // input: Q8_1 rows
+    const uint8_t* in_q8;        // gate/up: x_q8 [T]; down: inter_q8 [pairs]
+    int64_t in_stride;           // bytes per input row
+    // gate/up output
+    uint8_t* inter_q8;           // [T*k + T][inter_stride]
+    int64_t inter_stride;
+    // down output + combine
+    float* pair_out;             // [T*k + T][H]
+    const float* topk_w;         // [T][k]
+    const float* sh_gate_logit;  // [T] or null
+    float* y;                    // [T][H]
+    int32_t* combine_ctr;        // [T][row tiles]
+    int tile_rows;               // down stage: output rows per CTA (multiple of 8, <= 64)
+    int n_row_tiles;             // down stage: ceil(H / tile_rows)
+    int32_t* status;
+};
+
+cudaError_t launch_route(const RouteParams& p, cudaStream_t stream);
+cudaError_t launch_gate_up(const GemvParams& p, int max_entries, cudaStream_t stream);
+cudaError_t launch_down(const GemvParams& p, int max_entries, cudaStream_t stream);
+
+// Plain batched GEMV (legacy operator entries): y[slot][row] = W[ids[slot]][row] . xq8[slot].
+cudaError_t launch_mmvq(int wtype, const void* w, const void* xq8, float* y, const int* ids, int ncols, int nrows,
+                        int64_t expert_stride, int64_t input_stride, int nslots, cudaStream_t stream);
+cudaError_t launch_block_sumi(int wtype, const void* w, const void* xq8, int32_t* sumi, int ncols, int nrows,
+                              cudaStream_t stream);
+cudaError_t launch_quantize_q8_1(const float* x, void* out, int64_t ncols, int64_t ncols_padded, int batch,
+                                 cudaStream_t stream);
+cudaError_t launch_rmsnorm(const float* x, float* y, int T, int H, float eps, cudaStream_t stream);
+int down_tile_rows(int type_routed, int ncols_routed, int type_shared, int ncols_shared);
+
+}  // namespace chimere

@@ -1,0 +1,314 @@
+// router.cu -- routing front end of the MoE layer, one launch for T tokens:
+//   router logits (+ shared-expert gate logit), softmax / sigmoid top-k, Q8_1 of the input rows,
+//   dispatch permutation and the work list of the grouped GEMV kernels.
+//
+// Arithmetic order is the reference's, so that logits, probabilities, indices and weights are
+// bit-identical to its kernels on the same GPU:
+//   f32_gemv_kernel      chimere-server/kernels/chimere_kernels.cu:706-741
+//   dot_product_kernel   chimere-server/src/scratch_pool.rs:243-261
+//   topk_softmax         chimere-server/kernels/chimere_kernels.cu:1150-1223
+//   ggml_quantize_q8_1   chimere-server/kernels/chimere_kernels.cu:1495-1523
+#include "common.cuh"
+#include "kernels.h"
+
+namespace chimere {
+
+// Sum of 256 partials held in shared memory in the order of a binary tree with strides
+// 128, 64, ..., 1 (element i+stride added into element i), done by one warp.
+__device__ __forceinline__ float tree256(const float* r, int lane) {
+    float a0 = r[lane] + r[lane + 128];
+    float a1 = r[lane + 32] + r[lane + 160];
+    float a2 = r[lane + 64] + r[lane + 192];
+    float a3 = r[lane + 96] + r[lane + 224];
+    float b0 = a0 + a2;
+    float b1 = a1 + a3;
+    float v = b0 + b1;
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) v += __shfl_down_sync(0xffffffffu, v, s);
+    return v;  // valid in lane 0
+}
+
+// Q8_1 of one 32-float block by one warp; lane = element.
+__device__ __forceinline__ void quantize_block_q8_1(float xi, uint8_t* out, int lane) {
+    float amax = fabsf(xi), sum = xi;
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+        sum += __shfl_xor_sync(0xffffffffu, sum, m);
+    }
+    const float d = amax / 127.0f;
+    const int8_t q = (amax == 0.0f) ? (int8_t)0 : (int8_t)roundf(xi / d);
+    reinterpret_cast<int8_t*>(out)[4 + lane] = q;
+    if (lane == 0) {
+        *reinterpret_cast<__half2*>(out) = __halves2half2(__float2half(d), __float2half(sum));
+    }
+}
+
+// One token's scores -> top-k, by one warp.  Lane l owns experts l, l+32, ...
+__device__ void topk_warp(const RouteParams& p, const float* logit_row, int t, int lane, float* tree_scratch) {
+    const int E = p.E, k = p.top_k;
+    float v[8], pr[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = lane + 32 * i;
+        v[i] = (e < E) ? __ldcg(logit_row + e) : -1.0e30f;
+    }
+    if (p.route_mode == CHIMERE_ROUTE_SOFTMAX_RENORM) {
+        float mx = v[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) mx = fmaxf(mx, v[i]);
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
+        float ev[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = lane + 32 * i;
+            ev[i] = (e < E) ? expf(v[i] - mx) : 0.0f;
+            tree_scratch[e] = ev[i];
+        }
+        __syncwarp();
+        float sum = tree256(tree_scratch, lane);
+        sum = __shfl_sync(0xffffffffu, sum, 0);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pr[i] = (sum > 0.0f) ? (ev[i] / sum) : (1.0f / (float)E);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pr[i] = 1.0f / (1.0f + expf(-v[i]));
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (lane + 32 * i >= E) pr[i] = -2.0f;  // never selected
+
+    float wsum = 0.0f;
+    float wsel = 0.0f;  // lane j keeps the weight of slot j
+    int isel = 0;
+    for (int j = 0; j < k; ++j) {
+        float bv = -1.0f;
+        int bi = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (pr[i] > bv) { bv = pr[i]; bi = lane + 32 * i; }
+        // warp arg-max; equal values go to the lower index, like a strict-greater scan from 0
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        wsum += bv;
+        if (lane == j) { wsel = bv; isel = bi; }
+        if ((bi & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (i == (bi >> 5)) pr[i] = -1.0f;
+        }
+    }
+    if (lane < k) {
+        float w = wsel;
+        if (wsum > 0.0f) {
+            const float inv = 1.0f / wsum;
+            w = w * inv;
+        }
+        if (p.route_mode != CHIMERE_ROUTE_SOFTMAX_RENORM || p.route_scale != 1.0f) w = w * p.route_scale;
+        p.topk_idx[(size_t)t * k + lane] = isel;
+        p.topk_w[(size_t)t * k + lane] = w;
+    }
+}
+
+// Stable counting sort of the T*k pairs by expert, plus the GEMV work list.  One CTA of 256.
+__device__ void build_dispatch(const RouteParams& p, int* smem_i) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int E = p.E, P = p.T * p.top_k;
+    int* hist = smem_i;              // [256]
+    int* cursor = smem_i + 256;      // [256]
+    int* warp_cnt = smem_i + 512;    // [8][256]
+    int* scan = smem_i + 512 + 2048; // [256]
+    hist[tid] = 0;
+    for (int i = tid; i < 2048; i += 256) warp_cnt[i] = 0;
+    __syncthreads();
+    for (int q = tid; q < P; q += 256) atomicAdd(&hist[__ldcg(p.topk_idx + q)], 1);
+    __syncthreads();
+    // exclusive scans over the experts: pair offsets and work-entry offsets
+    const int cnt = (tid < E) ? hist[tid] : 0;
+    const int nent = (cnt + kMaxGroupTokens - 1) / kMaxGroupTokens;
+    int incl_c = cnt, incl_n = nent;
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+        const int a = __shfl_up_sync(0xffffffffu, incl_c, s), b = __shfl_up_sync(0xffffffffu, incl_n, s);
+        if (lane >= s) { incl_c += a; incl_n += b; }
+    }
+    if (lane == 31) { scan[warp] = incl_c; scan[8 + warp] = incl_n; }
+    __syncthreads();
+    int base_c = 0, base_n = 0;
+    for (int w = 0; w < warp; ++w) { base_c += scan[w]; base_n += scan[8 + w]; }
+    const int off = base_c + incl_c - cnt;      // exclusive
+    const int ent0 = base_n + incl_n - nent;
+    cursor[tid] = off;
+    if (tid < E) p.offsets[tid] = off;
+    if (tid == 255) {
+        p.offsets[E] = P;  // tid 255 holds the inclusive total (cnt = 0 beyond E)
+    }
+    int total_routed = 0;
+    for (int w = 0; w < 8; ++w) total_routed += scan[8 + w];
+    // routed work entries
+    for (int i = 0; i < nent; ++i) {
+        int* ent = p.group_list + kListHeader + 4 * (ent0 + i);
+        ent[0] = tid;
+        ent[1] = off + i * kMaxGroupTokens;
+        ent[2] = min(kMaxGroupTokens, cnt - i * kMaxGroupTokens);
+        ent[3] = 0;
+    }
+    // shared-expert entries: all tokens, identity order
+    const int nsh = p.has_shared ? (p.T + kMaxGroupTokens - 1) / kMaxGroupTokens : 0;
+    for (int i = tid; i < nsh; i += 256) {
+        int* ent = p.group_list + kListHeader + 4 * (total_routed + i);
+        ent[0] = -1;
+        ent[1] = i * kMaxGroupTokens;
+        ent[2] = min(kMaxGroupTokens, p.T - i * kMaxGroupTokens);
+        ent[3] = 0;
+    }
+    if (tid == 0) {
+        p.group_list[0] = total_routed + nsh;
+        p.group_list[1] = total_routed;
+        p.group_list[2] = nsh;
+        p.group_list[3] = 0;
+    }
+    __syncthreads();
+    // stable placement, 256 pairs per step
+    for (int base = 0; base < P; base += 256) {
+        const int q = base + tid;
+        const bool valid = q < P;
+        const int e = valid ? __ldcg(p.topk_idx + q) : (0x40000000 + tid);
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        const int rank = __popc(same & ((1u << lane) - 1u));
+        const bool leader = valid && rank == 0;
+        if (leader) warp_cnt[warp * 256 + e] = __popc(same);
+        __syncthreads();
+        if (valid) {
+            int pos = cursor[e] + rank;
+            for (int w = 0; w < warp; ++w) pos += warp_cnt[w * 256 + e];
+            p.perm[pos] = q;
+        }
+        __syncthreads();
+        if (leader) {
+            atomicAdd(&cursor[e], __popc(same));
+            warp_cnt[warp * 256 + e] = 0;
+        }
+        __syncthreads();
+    }
+}
+
+// grid = (row tiles, token tiles), 256 threads.  Thread p owns partial sum p of every output of
+// the tile: elements p, p+256, ... in ascending order, one fused multiply-add each.
+template <int TT, int TE>
+__global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
+    extern __shared__ __align__(16) float smem_f[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int H = p.H, E = p.E;
+    const int nrows = E + (p.shexp_gate_w ? 1 : 0);
+    const int t0 = blockIdx.y * TT, r0 = blockIdx.x * TE;
+    const int n_rtiles = gridDim.x;
+
+    // ---- Q8_1 of this token tile's input rows, blocks dealt round-robin to the row tiles ----
+    {
+        const int nbH = H >> 5;
+        const int nt = min(TT, p.T - t0);
+        for (int q = blockIdx.x * 8 + warp; q < nt * nbH; q += n_rtiles * 8) {
+            const int tt = q / nbH, b = q - tt * nbH;
+            const float xi = p.x[(size_t)(t0 + tt) * H + b * 32 + lane];
+            quantize_block_q8_1(xi, p.x_q8 + ((size_t)(t0 + tt) * nbH + b) * kQ81Bytes, lane);
+        }
+    }
+
+    // ---- partial dot products ----
+    float acc[TT][TE];
+#pragma unroll
+    for (int a = 0; a < TT; ++a)
+#pragma unroll
+        for (int b = 0; b < TE; ++b) acc[a][b] = 0.0f;
+    const float* wrow[TE];
+#pragma unroll
+    for (int b = 0; b < TE; ++b) {
+        const int r = r0 + b;
+        wrow[b] = (r < E) ? p.router_w + (size_t)r * H : ((r == E && r < nrows) ? p.shexp_gate_w : nullptr);
+    }
+#pragma unroll 2
+    for (int j = tid; j < H; j += 256) {
+        float xv[TT], wv[TE];
+#pragma unroll
+        for (int a = 0; a < TT; ++a) xv[a] = (t0 + a < p.T) ? p.x[(size_t)(t0 + a) * H + j] : 0.0f;
+#pragma unroll
+        for (int b = 0; b < TE; ++b) wv[b] = wrow[b] ? __ldg(wrow[b] + j) : 0.0f;
+#pragma unroll
+        for (int a = 0; a < TT; ++a)
+#pragma unroll
+            for (int b = 0; b < TE; ++b) acc[a][b] = fmaf(wv[b], xv[a], acc[a][b]);
+    }
+    float* red = smem_f;  // [TT*TE][256]
+#pragma unroll
+    for (int a = 0; a < TT; ++a)
+#pragma unroll
+        for (int b = 0; b < TE; ++b) red[(a * TE + b) * 256 + tid] = acc[a][b];
+    __syncthreads();
+    for (int o = warp; o < TT * TE; o += 8) {
+        const float v = tree256(red + o * 256, lane);
+        const int a = o / TE, b = o - a * TE;
+        const int t = t0 + a, r = r0 + b;
+        if (lane == 0 && t < p.T && r < nrows) {
+            if (r < E) p.router_logits[(size_t)t * E + r] = p.router_bias ? v + p.router_bias[r] : v;
+            else p.sh_gate_logit[t] = v;
+        }
+    }
+
+    // ---- last CTA of the token tile: scores and top-k ----
+    __shared__ int s_flag;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_flag = (atomicAdd(&p.counters[kCtrRouteTile + blockIdx.y], 1) == n_rtiles - 1);
+    __syncthreads();
+    if (!s_flag) return;
+    __threadfence();
+    if (tid == 0) p.counters[kCtrRouteTile + blockIdx.y] = 0;
+    for (int a = warp; a < TT; a += 8) {
+        const int t = t0 + a;
+        if (t < p.T) topk_warp(p, p.router_logits + (size_t)t * E, t, lane, red + warp * 256);
+    }
+
+    // ---- last token tile overall: dispatch permutation and work list ----
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_flag = (atomicAdd(&p.counters[kCtrRouteAll], 1) == (int)gridDim.y - 1);
+    __syncthreads();
+    if (!s_flag) return;
+    __threadfence();
+    if (tid == 0) p.counters[kCtrRouteAll] = 0;
+    build_dispatch(p, reinterpret_cast<int*>(smem_f));
+}
+
+static size_t route_smem(int TT, int TE) {
+    size_t a = (size_t)TT * TE * 256 * sizeof(float);
+    size_t b = (512 + 2048 + 256) * sizeof(int);
+    return a > b ? a : b;
+}
+
+cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
+    const int nrows = p.E + (p.shexp_gate_w ? 1 : 0);
+    if (p.T <= 32) {
+        constexpr int TT = 8, TE = 2;
+        dim3 grid((nrows + TE - 1) / TE, (p.T + TT - 1) / TT);
+        route_kernel<TT, TE><<<grid, 256, route_smem(TT, TE), stream>>>(p);
+    } else {
+        constexpr int TT = 8, TE = 8;
+        static bool attr_set = false;
+        if (!attr_set) {
+            cudaFuncSetAttribute(route_kernel<TT, TE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)route_smem(TT, TE));
+            attr_set = true;
+        }
+        dim3 grid((nrows + TE - 1) / TE, (p.T + TT - 1) / TT);
+        route_kernel<TT, TE><<<grid, 256, route_smem(TT, TE), stream>>>(p);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace chimere

@@ -1,0 +1,182 @@
+/* chimere_b200_moe.h -- C ABI of the B200 (sm_100a) quantized MoE feed-forward library.
+ *
+ * Two groups of entry points:
+ *
+ *  1. Legacy operator entries.  Same names, argument order and meaning as the reference's
+ *     FFI layer (chimere-server/ffi/ggml_cuda_gemv.cu, Rust declarations in
+ *     chimere-server/src/kernels/ggml_gpu.rs:101-240), so the Rust wrappers link unchanged.
+ *     They return void and report nothing, exactly like the reference.
+ *
+ *  2. Layer-level entries (chimere_b200_moe_*).  One call replaces the launch sequence of
+ *     forward_moe_cudarc_with_cache (chimere-server/src/qwen35_model/moe_ffn.rs:1094-1766):
+ *     router GEMV, softmax/top-k, Q8_1 quantization, batched gate/up GEMVs, SwiGLU,
+ *     re-quantization, batched down GEMV, weighted combine, shared expert and sigmoid gate,
+ *     for T tokens at once.  They return int: 0 = ok, <0 = argument error found on the host
+ *     before anything was launched.
+ *
+ * Conventions (both groups): every pointer named dev / d_* is device memory owned by the
+ * caller; the library never allocates, frees or keeps device memory; all work is enqueued on
+ * the stream passed in (NULL = legacy default stream); no entry synchronises the host unless
+ * its comment says so.  Quantized weights use the ggml block layouts unchanged
+ * (Q4_0 18 B / 32, Q8_0 34 B / 32, IQ3_S 110 B / 256; sizes as in
+ * chimere-server/src/gguf_loader.rs:161-193), row-major, experts contiguous.
+ */
+#ifndef CHIMERE_B200_MOE_H
+#define CHIMERE_B200_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef __DRIVER_TYPES_H__
+typedef struct CUstream_st* cudaStream_t;
+#endif
+
+/* ggml tensor-type ids of the weight formats this path supports. */
+enum { CHIMERE_TYPE_Q4_0 = 2, CHIMERE_TYPE_Q8_0 = 8, CHIMERE_TYPE_IQ3_S = 21 };
+/* Router variants. */
+enum { CHIMERE_ROUTE_SOFTMAX_RENORM = 0,  /* softmax over E, top-k on probabilities, renormalise (chimere_kernels.cu:1150-1223) */
+       CHIMERE_ROUTE_SIGMOID_NORM_SCALE = 1 /* sigmoid scores, top-k, normalise to sum 1, multiply by route_scale (Nemotron-H style) */ };
+/* Expert activation. */
+enum { CHIMERE_ACT_SWIGLU = 0,  /* silu(gate x) * (up x)   (fused_ops.rs:34-45) */
+       CHIMERE_ACT_RELU2 = 1    /* relu(up x)^2, no gate matrix */ };
+
+/* One MoE layer: dimensions, modes and device pointers.  Mirrors MoeWeightsRaw
+ * (chimere-server/src/qwen35_model/compute_graph.rs:1000-1049).  For the CPU oracle the same
+ * struct is used with host pointers. */
+typedef struct chimere_moe_layer {
+    int32_t H;            /* hidden size (multiple of 256 for IQ3_S inputs, of 32 otherwise) */
+    int32_t E;            /* routed experts (<= 256) */
+    int32_t F;            /* routed expert width */
+    int32_t F_s;          /* shared expert width, 0 = no shared expert */
+    int32_t top_k;        /* experts per token (<= 8) */
+    int32_t route_mode;   /* CHIMERE_ROUTE_* */
+    int32_t act;          /* CHIMERE_ACT_* */
+    float   route_scale;  /* multiplier on the normalised weights (1.0 for softmax mode) */
+    int32_t type_gate, type_up, type_down;          /* routed expert weight types */
+    int32_t type_sh_gate, type_sh_up, type_sh_down; /* shared expert weight types */
+    const float* router_w;     /* f32 [E][H] row-major */
+    const float* router_bias;  /* f32 [E] added to the logits before scoring, or NULL */
+    const float* shexp_gate_w; /* f32 [H]: shared expert scaled by sigmoid(x . w), or NULL = scale 1 */
+    const void*  gate_exps;    /* [E][F rows][H cols] quant blocks; NULL when act == RELU2 */
+    const void*  up_exps;      /* [E][F rows][H cols] */
+    const void*  down_exps;    /* [E][H rows][F cols] */
+    int64_t stride_gate, stride_up, stride_down;    /* bytes per expert */
+    const void*  sh_gate;      /* [F_s rows][H cols]; NULL when act == RELU2 */
+    const void*  sh_up;        /* [F_s rows][H cols] */
+    const void*  sh_down;      /* [H rows][F_s cols] */
+} chimere_moe_layer;
+
+/* Scratch of one stream.  Mirrors GgmlGpuBuffers::with_moe
+ * (chimere-server/src/kernels/ggml_gpu.rs:358-406): allocated once by the caller, reused by
+ * every call, not re-entrant.  All members point into the caller's arena; they stay readable
+ * after a call and are the parity taps (routing indices, permutation, Q8_1 bytes). */
+typedef struct chimere_moe_workspace {
+    int32_t max_T;          /* capacity in tokens */
+    int32_t reserved0;
+    int32_t* topk_idx;      /* [T][top_k] expert ids, descending score */
+    float*   topk_w;        /* [T][top_k] combine weights */
+    float*   router_logits; /* [T][E] (after bias) */
+    float*   sh_gate_logit; /* [T] x . shexp_gate_w */
+    uint8_t* x_q8;          /* [T][H/32] Q8_1 blocks (36 B) of the input rows */
+    int32_t* perm;          /* [T*top_k] pair ids t*top_k+j sorted by expert (stable) */
+    int32_t* offsets;       /* [E+1] start of each expert's pairs in perm */
+    int32_t* group_list;    /* work list of the grouped GEMV kernels, built on the device */
+    int32_t* counters;      /* small integer scratch; zero between calls */
+    uint8_t* inter_q8;      /* [(T*top_k + T)][F_max/32] Q8_1 blocks of the activated intermediates */
+    float*   pair_out;      /* [(T*top_k + T)][H] down-projection rows before the combine */
+    void*    prefill_arena; /* staging for the grouped int8 GEMM path */
+    size_t   prefill_bytes;
+    int32_t* status;        /* device status word: 0 = ok */
+} chimere_moe_workspace;
+
+/* ---------------------------------------------------------------- layer-level entries ---- */
+
+/* Bytes of device memory a workspace for up to max_T tokens needs. */
+size_t chimere_b200_moe_workspace_bytes(const chimere_moe_layer* w, int max_T);
+
+/* Carve `ws` out of the caller's device arena (`bytes` >= workspace_bytes, 256-byte aligned)
+ * and zero what must start at zero (enqueued on `stream`).  Returns 0, or <0 on bad arguments. */
+int chimere_b200_moe_workspace_init(chimere_moe_workspace* ws, void* d_arena, size_t bytes,
+                                    const chimere_moe_layer* w, int max_T, cudaStream_t stream);
+
+/* y[T][H] = MoE(x[T][H]).  Replaces moe_ffn.rs:1094-1766 for T tokens.  x, y: device f32.
+ * Capturable in a CUDA graph: no allocation, no host synchronisation, no device-to-host copy. */
+int chimere_b200_moe_forward(const chimere_moe_layer* w, const float* d_x, float* d_y, int T,
+                             chimere_moe_workspace* ws, cudaStream_t stream);
+
+/* Same, with HOST buffers: copies x in, runs the layer, copies y out, all on `stream`, and
+ * waits for the stream.  h_x / h_y should be pinned.  d_x / d_y are caller-provided staging. */
+int chimere_b200_moe_forward_host(const chimere_moe_layer* w, const float* h_x, float* h_y, int T,
+                                  float* d_x, float* d_y, chimere_moe_workspace* ws,
+                                  cudaStream_t stream);
+
+/* Routing only: fills ws->router_logits, topk_idx, topk_w, sh_gate_logit, x_q8
+ * (moe_ffn.rs:1094-1126 + 1185-1204 + 1736-1746). */
+int chimere_b200_moe_route(const chimere_moe_layer* w, const float* d_x, int T,
+                           chimere_moe_workspace* ws, cudaStream_t stream);
+
+/* Dispatch permutation from ws->topk_idx: stable counting sort of the pairs (t, j) by expert id
+ * into ws->perm / ws->offsets.  The reference has no token permutation (it loops tokens,
+ * compute_graph.rs:1787-1808); this is the canonical order the grouped kernels use. */
+int chimere_b200_moe_permute(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws,
+                             cudaStream_t stream);
+
+/* Parity tap: integer block dot products.  For `nrows` weight rows of type `wtype` with `ncols`
+ * columns and one Q8_1 input row, writes sumi[nrows][ncols/32] (int32): the exact integer sum of
+ * each 32-wide block (for IQ3_S including the (1 + 2*scale) factor, chimere_kernels.cu:860). */
+int chimere_b200_block_sumi(int wtype, const void* d_w, const void* d_xq8, int32_t* d_sumi,
+                            int ncols, int nrows, cudaStream_t stream);
+
+/* RMSNorm with unit weight over rows of length H: y = x / sqrt(mean(x^2) + eps). Used between
+ * stacked layers. */
+int chimere_b200_rmsnorm(const float* d_x, float* d_y, int T, int H, float eps, cudaStream_t stream);
+
+/* Library/ABI version and the compute capability it was built for (100 = sm_100a). */
+int chimere_b200_abi_version(void);
+int chimere_b200_built_for_sm(void);
+
+/* --------------------------------------------------------- legacy operator entries ------- */
+/* Each replaces the function of the same name in chimere-server/ffi/ggml_cuda_gemv.cu. */
+
+/* ggml_cuda_gemv.cu:184-194.  out needs pad(ncols,512)/32*36 bytes; blocks past ncols are zero. */
+void chimere_quantize_q8_1(const float* input, void* output, int64_t ncols, int64_t ncols_padded,
+                           cudaStream_t stream);
+/* ggml_cuda_gemv.cu:393-404.  `batch` rows, output row stride = ncols_padded/32*36 bytes. */
+void chimere_quantize_q8_1_batched(const float* input, void* output, int64_t ncols,
+                                   int64_t ncols_padded, int batch, cudaStream_t stream);
+/* ggml_cuda_gemv.cu:105-116 / 150-160: y[nrows] = W[nrows][ncols] . x_q8 */
+void chimere_mmvq_iq3s(const void* weights, const void* input_q8, float* output, int ncols,
+                       int nrows, int nrows_y_padded, cudaStream_t stream);
+void chimere_mmvq_q8_0(const void* weights, const void* input_q8, float* output, int ncols,
+                       int nrows, int nrows_y_padded, cudaStream_t stream);
+/* New, same shape as the two above, for Q4_0 experts. */
+void chimere_mmvq_q4_0(const void* weights, const void* input_q8, float* output, int ncols,
+                       int nrows, int nrows_y_padded, cudaStream_t stream);
+/* ggml_cuda_gemv.cu:243-279: top_k expert GEMVs in one launch, expert ids read on the device.
+ * input_stride = 0: one shared Q8_1 input; otherwise bytes between the per-slot inputs. */
+void chimere_mmvq_iq3s_batched(const void* all_weights, const void* input_q8, float* output,
+                               const int* expert_ids, int ncols, int nrows, int nrows_y_padded,
+                               int64_t expert_stride, int64_t input_stride, int top_k,
+                               cudaStream_t stream);
+/* New, same shape, for Q4_0 and Q8_0 experts. */
+void chimere_mmvq_q4_0_batched(const void* all_weights, const void* input_q8, float* output,
+                               const int* expert_ids, int ncols, int nrows, int nrows_y_padded,
+                               int64_t expert_stride, int64_t input_stride, int top_k,
+                               cudaStream_t stream);
+void chimere_mmvq_q8_0_batched(const void* all_weights, const void* input_q8, float* output,
+                               const int* expert_ids, int ncols, int nrows, int nrows_y_padded,
+                               int64_t expert_stride, int64_t input_stride, int top_k,
+                               cudaStream_t stream);
+/* ggml_cuda_gemv.cu:196-209 */
+int chimere_q8_1_block_bytes(void);   /* 36 */
+int chimere_q8_1_block_elems(void);   /* 32 */
+int chimere_matrix_row_padding(void); /* 512 */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CHIMERE_B200_MOE_H */
