@@ -51,6 +51,8 @@ PROTOTYPES = {
     "chimere_b200_moe_forward": (C.c_int, [_LAYER_P, _P, _P, C.c_int, _WS_P, _P]),
     "chimere_b200_moe_forward_host": (C.c_int, [_LAYER_P, _P, _P, C.c_int, _P, _P, _WS_P, _P]),
     "chimere_b200_moe_route": (C.c_int, [_LAYER_P, _P, C.c_int, _WS_P, _P]),
+    "chimere_b200_moe_gate_up": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P]),
+    "chimere_b200_moe_down_combine": (C.c_int, [_LAYER_P, _P, C.c_int, _WS_P, _P]),
     "chimere_b200_moe_permute": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P]),
     "chimere_b200_block_sumi": (C.c_int, [C.c_int, _P, _P, _P, C.c_int, C.c_int, _P]),
     "chimere_b200_rmsnorm": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_float, _P]),

@@ -158,21 +158,12 @@ int chimere_b200_moe_permute(const chimere_moe_layer* w, int T, chimere_moe_work
     return -6;  // not built yet
 }
 
-int chimere_b200_moe_forward(const chimere_moe_layer* w, const float* d_x, float* d_y, int T, chimere_moe_workspace* ws,
-                             cudaStream_t stream) {
-    int rc = check_call(w, d_x, d_y, T, ws);
-    if (rc) return rc;
-    const Layout L = make_layout(w, ws->max_T);
-    const int max_entries = max_entries_for(w, T);
-    cudaError_t e = launch_route(route_params(w, d_x, T, ws), stream);
-    if (e != cudaSuccess) return cuda_rc(e);
-
+static GemvParams gate_up_params(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, const Layout& L) {
     GemvParams g{};
     g.T = T; g.top_k = w->top_k; g.H = w->H;
     g.act = w->act;
     g.group_list = ws->group_list; g.perm = ws->perm;
     g.status = ws->status;
-    // gate / up stage
     g.ncols_routed = w->H; g.ncols_shared = w->H;
     g.nrows_routed = w->F; g.nrows_shared = w->F_s;
     g.type_routed = w->type_up; g.type_shared = w->type_sh_up;
@@ -181,22 +172,55 @@ int chimere_b200_moe_forward(const chimere_moe_layer* w, const float* d_x, float
     g.sh_a = (const uint8_t*)w->sh_gate; g.sh_b = (const uint8_t*)w->sh_up;
     g.in_q8 = ws->x_q8; g.in_stride = (int64_t)(w->H / 32) * kQ81Bytes;
     g.inter_q8 = ws->inter_q8; g.inter_stride = (int64_t)L.inter_stride;
-    e = launch_gate_up(g, max_entries, stream);
-    if (e != cudaSuccess) return cuda_rc(e);
-    // down stage + combine
+    return g;
+}
+
+static GemvParams down_params(const chimere_moe_layer* w, float* d_y, int T, chimere_moe_workspace* ws, const Layout& L) {
+    GemvParams g{};
+    g.T = T; g.top_k = w->top_k; g.H = w->H;
+    g.act = w->act;
+    g.group_list = ws->group_list; g.perm = ws->perm;
+    g.status = ws->status;
     g.ncols_routed = w->F; g.ncols_shared = w->F_s;
     g.nrows_routed = w->H; g.nrows_shared = w->F_s > 0 ? w->H : 0;
     g.type_routed = w->type_down; g.type_shared = w->type_sh_down;
-    g.w_a = (const uint8_t*)w->down_exps; g.w_b = nullptr;
-    g.stride_a = w->stride_down; g.stride_b = 0;
-    g.sh_a = (const uint8_t*)w->sh_down; g.sh_b = nullptr;
+    g.w_a = (const uint8_t*)w->down_exps; g.stride_a = w->stride_down;
+    g.sh_a = (const uint8_t*)w->sh_down;
     g.in_q8 = ws->inter_q8; g.in_stride = (int64_t)L.inter_stride;
     g.pair_out = ws->pair_out; g.topk_w = ws->topk_w;
     g.sh_gate_logit = (w->F_s > 0 && w->shexp_gate_w) ? ws->sh_gate_logit : nullptr;
     g.y = d_y;
     g.combine_ctr = ws->counters + kCtrRouteTile + (ws->max_T + 7) / 8;
     g.tile_rows = L.tile_rows; g.n_row_tiles = L.n_row_tiles;
-    e = launch_down(g, max_entries, stream);
+    return g;
+}
+
+int chimere_b200_moe_gate_up(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, cudaStream_t stream) {
+    int rc = check_call(w, ws, ws, T, ws);
+    if (rc) return rc;
+    const Layout L = make_layout(w, ws->max_T);
+    return cuda_rc(launch_gate_up(gate_up_params(w, T, ws, L), max_entries_for(w, T), stream));
+}
+
+int chimere_b200_moe_down_combine(const chimere_moe_layer* w, float* d_y, int T, chimere_moe_workspace* ws,
+                                  cudaStream_t stream) {
+    int rc = check_call(w, d_y, d_y, T, ws);
+    if (rc) return rc;
+    const Layout L = make_layout(w, ws->max_T);
+    return cuda_rc(launch_down(down_params(w, d_y, T, ws, L), max_entries_for(w, T), stream));
+}
+
+int chimere_b200_moe_forward(const chimere_moe_layer* w, const float* d_x, float* d_y, int T, chimere_moe_workspace* ws,
+                             cudaStream_t stream) {
+    int rc = check_call(w, d_x, d_y, T, ws);
+    if (rc) return rc;
+    const Layout L = make_layout(w, ws->max_T);
+    const int max_entries = max_entries_for(w, T);
+    cudaError_t e = launch_route(route_params(w, d_x, T, ws), stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    e = launch_gate_up(gate_up_params(w, T, ws, L), max_entries, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    e = launch_down(down_params(w, d_y, T, ws, L), max_entries, stream);
     return cuda_rc(e);
 }
 

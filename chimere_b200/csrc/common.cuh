@@ -31,6 +31,14 @@ __device__ __forceinline__ uint32_t ld_u16(const uint8_t* p) { return *reinterpr
 // 32-bit load from an address that is only 2-byte aligned (ggml blocks are 2-byte aligned).
 __device__ __forceinline__ uint32_t ld_u32_a2(const uint8_t* p) { return ld_u16(p) | (ld_u16(p + 2) << 16); }
 
+// PTX prmt in its default mode: selector nibble bit 3 replicates the sign bit of the chosen byte.
+// (__byte_perm documents only the low three selector bits, so the instruction is spelled out.)
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 // ---- mbarrier + bulk async copy (global -> shared), no multicast -------------------------
@@ -113,7 +121,7 @@ template <> struct Unit<CHIMERE_TYPE_IQ3_S> {
             // 4 sign bits -> bit 7 of each byte -> 0xFF/0x00 byte mask; -m = (m ^ 0xFF) + 1 never
             // carries out of its byte because every magnitude is >= 1.
             const uint32_t t7 = (((sgn >> (4 * g)) & 15u) * 0x10204080u) & 0x80808080u;
-            const uint32_t mask = __byte_perm(t7, 0u, 0xBA98);
+            const uint32_t mask = prmt(t7, 0u, 0xBA98u);
             w[g] = (int)((gv ^ mask) + (t7 >> 7));
         }
     }

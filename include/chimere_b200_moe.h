@@ -119,6 +119,18 @@ int chimere_b200_moe_forward_host(const chimere_moe_layer* w, const float* h_x, 
 int chimere_b200_moe_route(const chimere_moe_layer* w, const float* d_x, int T,
                            chimere_moe_workspace* ws, cudaStream_t stream);
 
+/* The fused expert up/gate operator on its own: for every (token, selected expert) pair and the
+ * shared expert, act(gate . x, up . x) quantized to Q8_1 into ws->inter_q8.  Needs the routing
+ * results of chimere_b200_moe_route in `ws`.  Replaces moe_ffn.rs:1206-1323 (batched gate GEMV,
+ * batched up GEMV, silu_mul, batched Q8_1) and :1597-1700 for the shared expert. */
+int chimere_b200_moe_gate_up(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws,
+                             cudaStream_t stream);
+
+/* Down projections of ws->inter_q8, routing-weighted combine in slot order, sigmoid-gated shared
+ * expert; writes y[T][H].  Replaces moe_ffn.rs:1325-1384 and :1700-1766. */
+int chimere_b200_moe_down_combine(const chimere_moe_layer* w, float* d_y, int T,
+                                  chimere_moe_workspace* ws, cudaStream_t stream);
+
 /* Dispatch permutation from ws->topk_idx: stable counting sort of the pairs (t, j) by expert id
  * into ws->perm / ws->offsets.  The reference has no token permutation (it loops tokens,
  * compute_graph.rs:1787-1808); this is the canonical order the grouped kernels use. */
