@@ -1,0 +1,338 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized MoE feed-forward layer on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--tokens T] [--layers L]
+
+Workload (N = 1): the decode configuration -- a Qwen3.5-35B-A3B-shaped MoE layer (H 2048, 256 experts,
+top-8, expert width 512, one sigmoid-gated shared expert), gate/up in IQ3_S, down in Q4_0, activations
+Q8_1, T concurrent tokens (default 8, the top of the 1/2/4/8 sweep).  One STEP is one pass of the T-token
+batch through L independent layers (default 16, seeded synthetic weights ~N(0, 0.02), fresh input per
+layer).  The weights of consecutive calls differ, and one cycle touches L x ~99 MB > the 126 MB L2, so the
+timed calls stream their weights from HBM.  metric = tokens x layer-calls per second.
+
+The JSON line also carries: `roofline` for the dominant kernel (gate/up GEMV), measured live with CUDA
+events; `sweep` with the layer-level numbers for T = 1, 2, 4, 8; `e2e` through the host-buffer C entry
+(pinned host x in, y out, per layer call); `cpu_baseline`: the CPU oracle port timed on this host.
+
+--impl reference times the CPU port of the reference's path (the reference's own CPU code needs ik_llama's
+ggml, which is neither vendored nor pinned) with all host threads on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_decode_tokens_per_s"
+UNIT = "tokens*layers/s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                       "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        time.sleep(0.15)
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        rows = [r.strip().split(", ") for r in open(self.f.name) if r.strip()]
+        os.unlink(self.f.name)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[5:9]):
+                if v.strip().lower() == "active":
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_port_tokens_per_s(cfg, T, n_layers, threads=None):
+    """The oracle's layer forward on the host cores: tokens x layer-calls per second."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle
+    from chimere_b200 import configs
+    if threads:
+        oracle.lib().orc_set_num_threads(threads)
+    layers = [configs.make_layer(cfg, device="cpu", seed=9000 + i) for i in range(n_layers)]
+    xs = [configs.make_input(cfg, T, seed=77 + i).numpy() for i in range(n_layers)]
+    oracle.moe_forward(layers[0], xs[0], taps=False)  # warm
+    t0 = time.perf_counter()
+    for w, x in zip(layers, xs):
+        oracle.moe_forward(w, x, taps=False)
+    dt = time.perf_counter() - t0
+    return T * n_layers / dt, oracle.lib().orc_num_threads(), dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from chimere_b200 import configs
+    cfg = configs.QWEN_IQ3S
+    T = args.tokens
+    sample_layers = 2
+    vals = []
+    for _ in range(args.warmup):
+        cpu_port_tokens_per_s(cfg, T, 1)
+    t_total = 0.0
+    for _ in range(args.steps):
+        v, threads, dt = cpu_port_tokens_per_s(cfg, T, sample_layers)
+        vals.append(v); t_total += dt
+    v = statistics.median(vals)
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * t_total / max(1, args.steps), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8 block dots, f32 accumulate", "data": "synthetic",
+            "config": workload_config(cfg, T, sample_layers),
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": f"T={T} tokens through {sample_layers} layers per step (CPU restatement in oracle/, OpenMP)"},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def workload_config(cfg, T, L):
+    return {"workload": f"{cfg.name}: H={cfg.H} E={cfg.E} top{cfg.top_k} F={cfg.F} shared F_s={cfg.F_s}; gate/up IQ3_S, down Q4_0, "
+                        f"Q8_1 activations; T={T} tokens x {L} independent layers per step",
+            "tokens": T, "layers": L,
+            "l2": f"weights rotate over {L} layers; one cycle touches more than the 126 MB L2, inputs differ per layer"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=16)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    from chimere_b200 import abi, configs
+    from chimere_b200.layer import MoeScratch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the MoE path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    lib = abi.load()
+    cfg = configs.QWEN_IQ3S
+    T, L, K, W = args.tokens, args.layers, args.steps, args.warmup
+    hbm_peak, peak_kind = peaks()
+
+    # ---- resident state: L layers of weights, one scratch per (layer), inputs, outputs ----
+    layers = [configs.make_layer(cfg, device=dev, seed=1000 * (rank + 1) + i) for i in range(L)]
+    scratch = [MoeScratch(w, max(T, 8), device=dev) for w in layers]
+    xs = [configs.make_input(cfg, max(T, 8), device=dev, seed=31 * (rank + 1) + i) for i in range(L)]
+    ys = [torch.empty_like(x) for x in xs]
+    stream = torch.cuda.Stream(device=dev)
+    sptr = stream.cuda_stream
+
+    def enqueue_layers(Tn):
+        for w, sc, x, y in zip(layers, scratch, xs, ys):
+            rc = lib.chimere_b200_moe_forward(C.byref(w.as_struct()), x.data_ptr(), y.data_ptr(), Tn, C.byref(sc.ws), sptr)
+            if rc:
+                raise RuntimeError(f"chimere_b200_moe_forward rc={rc}")
+
+    def make_graph(Tn):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            enqueue_layers(Tn)  # warm (also sets kernel attributes outside capture)
+            stream.synchronize()
+            with torch.cuda.graph(g, stream=stream):
+                enqueue_layers(Tn)
+        return g
+
+    def time_steps(run, k, w):
+        """k timed repetitions of run() on `stream` after w warm-ups; returns seconds (device time)."""
+        with torch.cuda.stream(stream):
+            for _ in range(w):
+                run()
+            stream.synchronize()
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(k):
+                run()
+            e1.record(stream)
+            stream.synchronize()
+            torch.cuda.synchronize()
+            if dist is not None:
+                dist.barrier()
+        return e0.elapsed_time(e1) * 1e-3
+
+    def distinct_experts(Tn):
+        return [int(torch.unique(sc.topk_indices(Tn)).numel()) for sc in scratch]
+
+    # ---- headline: graph replay of one step = L layer calls ----
+    graph = make_graph(T)
+    sampler = ClockSampler(local)
+    secs = time_steps(graph.replay, K, W)
+    clocks = sampler.stop()
+    if dist is not None:
+        t = torch.tensor([secs], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        secs = float(t.item())
+    value = world * T * L * K / secs
+    U = distinct_experts(T)
+    layer_bytes = sum(configs.algorithmic_bytes(cfg, T, u) for u in U) / L
+    layer_us = secs / (K * L) * 1e6
+    layer_gbs = layer_bytes / (layer_us * 1e-6) / 1e9
+
+    # ---- roofline of the dominant kernel (gate/up GEMV), timed alone over the rotating layers ----
+    def gate_up_all():
+        for w, sc in zip(layers, scratch):
+            rc = lib.chimere_b200_moe_gate_up(C.byref(w.as_struct()), T, C.byref(sc.ws), sptr)
+            if rc:
+                raise RuntimeError(f"gate_up rc={rc}")
+
+    def down_all():
+        for w, sc, y in zip(layers, scratch, ys):
+            rc = lib.chimere_b200_moe_down_combine(C.byref(w.as_struct()), y.data_ptr(), T, C.byref(sc.ws), sptr)
+            if rc:
+                raise RuntimeError(f"down rc={rc}")
+
+    from chimere_b200 import formats
+    b_gu = cfg.F * formats.row_bytes(cfg.type_gate_up, cfg.H)
+    b_gu_sh = cfg.F_s * formats.row_bytes(cfg.type_gate_up, cfg.H)
+    b_dn = cfg.H * formats.row_bytes(cfg.type_down, cfg.F)
+    b_dn_sh = cfg.H * formats.row_bytes(cfg.type_down, cfg.F_s)
+    xq_row = cfg.H // 32 * 36
+    iq_row = max(cfg.F, cfg.F_s) // 32 * 36
+    pairs = T * cfg.top_k + T
+    gu_bytes = sum(2 * (u * b_gu + b_gu_sh) + T * xq_row + pairs * (cfg.F // 32 * 36) for u in U) / L
+    dn_bytes = sum(u * b_dn + b_dn_sh + pairs * iq_row + T * cfg.H * 4 for u in U) / L
+    gu_secs = time_steps(gate_up_all, max(5, K), 3) / (max(5, K) * L)
+    dn_secs = time_steps(down_all, max(5, K), 3) / (max(5, K) * L)
+    roof = {"bound": "hbm", "kernel": "gate_up_kernel<IQ3_S>", "achieved": gu_bytes / gu_secs / 1e9, "peak": hbm_peak,
+            "unit": "GB/s", "frac": gu_bytes / gu_secs / 1e9 / hbm_peak, "peak_kind": peak_kind, "traffic": None,
+            "us_per_launch": gu_secs * 1e6, "algorithmic_bytes_per_launch": gu_bytes,
+            "down_kernel": {"achieved": dn_bytes / dn_secs / 1e9, "frac": dn_bytes / dn_secs / 1e9 / hbm_peak,
+                            "us_per_launch": dn_secs * 1e6, "algorithmic_bytes_per_launch": dn_bytes},
+            "layer": {"achieved": layer_gbs, "frac": layer_gbs / hbm_peak, "us_per_layer_call": layer_us,
+                      "algorithmic_bytes_per_call": layer_bytes, "distinct_experts_mean": sum(U) / L}}
+
+    # ---- sweep over T (layer level, graph replay) ----
+    sweep = []
+    if not args.no_sweep and rank == 0:
+        for Tn in (1, 2, 4, 8):
+            g = make_graph(Tn)
+            s = time_steps(g.replay, max(5, K), 3) / max(5, K)
+            Un = distinct_experts(Tn)
+            b = sum(configs.algorithmic_bytes(cfg, Tn, u) for u in Un) / L
+            us = s / L * 1e6
+            sweep.append({"T": Tn, "us_per_layer_call": us, "tokens_layers_per_s": Tn * L / s,
+                          "hbm_gbs": b / (us * 1e-6) / 1e9, "hbm_frac": b / (us * 1e-6) / 1e9 / hbm_peak,
+                          "distinct_experts_mean": sum(Un) / L})
+    elif dist is not None:
+        pass
+
+    # ---- end to end through the host-buffer C entry: pinned x in, y out, every layer call ----
+    hx = [x[:T].cpu().pin_memory() for x in xs]
+    hy = [torch.empty(T, cfg.H).pin_memory() for _ in xs]
+
+    def e2e_step():
+        for w, sc, a, b in zip(layers, scratch, hx, hy):
+            rc = lib.chimere_b200_moe_forward_host(C.byref(w.as_struct()), a.data_ptr(), b.data_ptr(), T,
+                                                   sc.x_dev.data_ptr(), sc.y_dev.data_ptr(), C.byref(sc.ws), sptr)
+            if rc:
+                raise RuntimeError(f"forward_host rc={rc}")
+
+    for _ in range(W):
+        e2e_step()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_secs = time.perf_counter() - t0
+    if dist is not None:
+        t = torch.tensor([e2e_secs], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_secs = float(t.item())
+    e2e = {"value": world * T * L * K / e2e_secs, "unit": UNIT, "h2d_bytes_per_step": L * T * cfg.H * 4,
+           "d2h_bytes_per_step": L * T * cfg.H * 4, "ms_per_step": 1e3 * e2e_secs / K}
+
+    status = max(sc.status() for sc in scratch)
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        v, threads, dt = cpu_port_tokens_per_s(cfg, T, 2)
+        cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"T={T} tokens through 2 layers ({dt:.2f} s), CPU restatement in oracle/ with OpenMP"}
+
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": 1e3 * secs / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 block dots (dp4a), f32 accumulate", "data": "synthetic",
+            "config": dict(workload_config(cfg, T, L), parallelism=("single GPU" if world == 1 else f"{world} independent replicas"),
+                           timing="CUDA graph replay of one step, CUDA events on the launching stream"),
+            "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": 3 * L * K, "clocks": clocks,
+            "sweep": sweep, "device_status": status}
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(HERE, "libchimere_b200_moe.so")
 TYPE_Q4_0, TYPE_Q8_0, TYPE_IQ3_S = 2, 8, 21
 ROUTE_SOFTMAX_RENORM, ROUTE_SIGMOID_NORM_SCALE = 0, 1
 ACT_SWIGLU, ACT_RELU2 = 0, 1
+LAYOUT_GGML, LAYOUT_TILED32 = 0, 1
 
 
 class MoeLayer(C.Structure):
@@ -23,6 +24,7 @@ class MoeLayer(C.Structure):
         ("route_mode", C.c_int32), ("act", C.c_int32), ("route_scale", C.c_float),
         ("type_gate", C.c_int32), ("type_up", C.c_int32), ("type_down", C.c_int32),
         ("type_sh_gate", C.c_int32), ("type_sh_up", C.c_int32), ("type_sh_down", C.c_int32),
+        ("layout", C.c_int32), ("reserved", C.c_int32),
         ("router_w", C.c_void_p), ("router_bias", C.c_void_p), ("shexp_gate_w", C.c_void_p),
         ("gate_exps", C.c_void_p), ("up_exps", C.c_void_p), ("down_exps", C.c_void_p),
         ("stride_gate", C.c_int64), ("stride_up", C.c_int64), ("stride_down", C.c_int64),
@@ -48,6 +50,11 @@ _LAYER_P, _WS_P = C.POINTER(MoeLayer), C.POINTER(MoeWorkspace)
 PROTOTYPES = {
     "chimere_b200_moe_workspace_bytes": (C.c_size_t, [_LAYER_P, C.c_int]),
     "chimere_b200_moe_workspace_init": (C.c_int, [_WS_P, _P, C.c_size_t, _LAYER_P, C.c_int, _P]),
+    "chimere_b200_moe_pack_bytes": (C.c_size_t, [_LAYER_P]),
+    "chimere_b200_moe_pack": (C.c_int, [_LAYER_P, _P, C.c_size_t, _LAYER_P, _P]),
+    "chimere_b200_packed_matrix_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "chimere_b200_pack_matrix": (C.c_int, [C.c_int, _P, _P, C.c_int, C.c_int, _P]),
+    "chimere_b200_block_sumi_tiled": (C.c_int, [C.c_int, _P, _P, _P, C.c_int, C.c_int, _P]),
     "chimere_b200_moe_forward": (C.c_int, [_LAYER_P, _P, _P, C.c_int, _WS_P, _P]),
     "chimere_b200_moe_forward_host": (C.c_int, [_LAYER_P, _P, _P, C.c_int, _P, _P, _WS_P, _P]),
     "chimere_b200_moe_route": (C.c_int, [_LAYER_P, _P, C.c_int, _WS_P, _P]),

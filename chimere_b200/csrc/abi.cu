@@ -10,6 +10,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "tiled.cuh"
 
 using namespace chimere;
 
@@ -25,6 +26,7 @@ int validate_layer(const chimere_moe_layer* w) {
     if (w->H <= 0 || w->E <= 0 || w->E > kMaxExperts || w->F <= 0 || w->F_s < 0) return -2;
     if (w->top_k <= 0 || w->top_k > kMaxTopK || w->top_k > w->E) return -2;
     if (w->H % 32 || w->F % 32 || w->F_s % 32) return -2;
+    if (w->layout != CHIMERE_LAYOUT_GGML && w->layout != CHIMERE_LAYOUT_TILED32) return -2;
     if (w->route_mode != CHIMERE_ROUTE_SOFTMAX_RENORM && w->route_mode != CHIMERE_ROUTE_SIGMOID_NORM_SCALE) return -2;
     if (w->act != CHIMERE_ACT_SWIGLU && w->act != CHIMERE_ACT_RELU2) return -2;
     const bool dual = w->act == CHIMERE_ACT_SWIGLU;
@@ -44,6 +46,7 @@ int validate_layer(const chimere_moe_layer* w) {
 struct Layout {
     size_t topk_idx, topk_w, logits, sh_logit, x_q8, perm, offsets, group_list, counters, inter_q8, pair_out, status, total;
     int max_entries, n_row_tiles, tile_rows, n_counters;
+    int n_row_tiles_tiled;
     size_t inter_stride;
 };
 
@@ -60,7 +63,10 @@ Layout make_layout(const chimere_moe_layer* w, int T) {
     L.max_entries = max_entries_for(w, T);
     L.tile_rows = down_tile_rows(w->type_down, w->F, w->type_sh_down, w->F_s);
     L.n_row_tiles = (H + L.tile_rows - 1) / L.tile_rows;
-    L.n_counters = kCtrRouteTile + (T + 7) / 8 + T * L.n_row_tiles;
+    L.n_row_tiles_tiled = (H + 32 * tiled_down_geom(w->type_down, w->F, w->type_sh_down, w->F_s).wr - 1) /
+                          (32 * tiled_down_geom(w->type_down, w->F, w->type_sh_down, w->F_s).wr);
+    const int max_tiles = L.n_row_tiles > L.n_row_tiles_tiled ? L.n_row_tiles : L.n_row_tiles_tiled;
+    L.n_counters = kCtrRouteTile + (T + 7) / 8 + T * max_tiles;
     L.inter_stride = (size_t)(Fmax / 32) * kQ81Bytes;
     size_t o = 0;
     L.topk_idx = o; o += up256((size_t)T * k * 4);
@@ -191,15 +197,104 @@ static GemvParams down_params(const chimere_moe_layer* w, float* d_y, int T, chi
     g.sh_gate_logit = (w->F_s > 0 && w->shexp_gate_w) ? ws->sh_gate_logit : nullptr;
     g.y = d_y;
     g.combine_ctr = ws->counters + kCtrRouteTile + (ws->max_T + 7) / 8;
-    g.tile_rows = L.tile_rows; g.n_row_tiles = L.n_row_tiles;
+    g.tile_rows = L.tile_rows;
+    g.n_row_tiles = (w->layout == CHIMERE_LAYOUT_TILED32) ? L.n_row_tiles_tiled : L.n_row_tiles;
     return g;
+}
+
+static cudaError_t run_gate_up(const chimere_moe_layer* w, const GemvParams& g, int max_entries, cudaStream_t stream) {
+    return w->layout == CHIMERE_LAYOUT_TILED32 ? launch_gate_up_tiled(g, max_entries, stream) : launch_gate_up(g, max_entries, stream);
+}
+static cudaError_t run_down(const chimere_moe_layer* w, const GemvParams& g, int max_entries, cudaStream_t stream) {
+    return w->layout == CHIMERE_LAYOUT_TILED32 ? launch_down_tiled(g, max_entries, stream) : launch_down(g, max_entries, stream);
+}
+
+// ---- tiled32 packing ----
+struct PackPlan { size_t gate, up, down, sh_gate, sh_up, sh_down, total; int64_t sg, su, sd; };
+static PackPlan pack_plan(const chimere_moe_layer* w) {
+    PackPlan P{};
+    const bool dual = w->act == CHIMERE_ACT_SWIGLU;
+    size_t o = 0;
+    P.su = tiled_matrix_bytes(w->type_up, w->F, w->H);
+    P.sg = dual ? tiled_matrix_bytes(w->type_gate, w->F, w->H) : 0;
+    P.sd = tiled_matrix_bytes(w->type_down, w->H, w->F);
+    P.gate = o; o += up256((size_t)P.sg * w->E);
+    P.up = o; o += up256((size_t)P.su * w->E);
+    P.down = o; o += up256((size_t)P.sd * w->E);
+    if (w->F_s > 0) {
+        P.sh_gate = o; o += dual ? up256((size_t)tiled_matrix_bytes(w->type_sh_gate, w->F_s, w->H)) : 0;
+        P.sh_up = o; o += up256((size_t)tiled_matrix_bytes(w->type_sh_up, w->F_s, w->H));
+        P.sh_down = o; o += up256((size_t)tiled_matrix_bytes(w->type_sh_down, w->H, w->F_s));
+    }
+    P.total = o;
+    return P;
+}
+
+size_t chimere_b200_moe_pack_bytes(const chimere_moe_layer* raw) {
+    if (validate_layer(raw) != 0 || raw->layout != CHIMERE_LAYOUT_GGML) return 0;
+    return pack_plan(raw).total;
+}
+
+int chimere_b200_moe_pack(const chimere_moe_layer* raw, void* d_arena, size_t bytes, chimere_moe_layer* packed,
+                          cudaStream_t stream) {
+    int rc = validate_layer(raw);
+    if (rc) return rc;
+    if (!d_arena || !packed) return -1;
+    if (raw->layout != CHIMERE_LAYOUT_GGML) return -2;
+    if ((uintptr_t)d_arena & 255) return -5;
+    const PackPlan P = pack_plan(raw);
+    if (bytes < P.total) return -4;
+    const bool dual = raw->act == CHIMERE_ACT_SWIGLU;
+    uint8_t* base = (uint8_t*)d_arena;
+    *packed = *raw;
+    packed->layout = CHIMERE_LAYOUT_TILED32;
+    cudaError_t e = cudaSuccess;
+    if (dual) {
+        e = launch_pack(raw->type_gate, raw->gate_exps, base + P.gate, raw->E, raw->F, raw->H, raw->stride_gate, P.sg, stream);
+        packed->gate_exps = base + P.gate; packed->stride_gate = P.sg;
+    }
+    if (e == cudaSuccess) e = launch_pack(raw->type_up, raw->up_exps, base + P.up, raw->E, raw->F, raw->H, raw->stride_up, P.su, stream);
+    packed->up_exps = base + P.up; packed->stride_up = P.su;
+    if (e == cudaSuccess) e = launch_pack(raw->type_down, raw->down_exps, base + P.down, raw->E, raw->H, raw->F, raw->stride_down, P.sd, stream);
+    packed->down_exps = base + P.down; packed->stride_down = P.sd;
+    if (raw->F_s > 0) {
+        if (dual) {
+            if (e == cudaSuccess) e = launch_pack(raw->type_sh_gate, raw->sh_gate, base + P.sh_gate, 1, raw->F_s, raw->H, 0, 0, stream);
+            packed->sh_gate = base + P.sh_gate;
+        }
+        if (e == cudaSuccess) e = launch_pack(raw->type_sh_up, raw->sh_up, base + P.sh_up, 1, raw->F_s, raw->H, 0, 0, stream);
+        packed->sh_up = base + P.sh_up;
+        if (e == cudaSuccess) e = launch_pack(raw->type_sh_down, raw->sh_down, base + P.sh_down, 1, raw->H, raw->F_s, 0, 0, stream);
+        packed->sh_down = base + P.sh_down;
+    }
+    return cuda_rc(e);
+}
+
+size_t chimere_b200_packed_matrix_bytes(int wtype, int nrows, int ncols) {
+    if (!type_ok(wtype) || nrows <= 0 || nrows % 32 || ncols <= 0 || ncols % type_cols_multiple(wtype)) return 0;
+    return (size_t)tiled_matrix_bytes(wtype, nrows, ncols);
+}
+
+int chimere_b200_pack_matrix(int wtype, const void* d_raw, void* d_out, int nrows, int ncols, cudaStream_t stream) {
+    if (!d_raw || !d_out) return -1;
+    if (!type_ok(wtype)) return -3;
+    if (nrows <= 0 || nrows % 32 || ncols <= 0 || ncols % type_cols_multiple(wtype)) return -2;
+    return cuda_rc(launch_pack(wtype, d_raw, d_out, 1, nrows, ncols, 0, 0, stream));
+}
+
+int chimere_b200_block_sumi_tiled(int wtype, const void* d_packed, const void* d_xq8, int32_t* d_sumi, int ncols, int nrows,
+                                  cudaStream_t stream) {
+    if (!d_packed || !d_xq8 || !d_sumi) return -1;
+    if (!type_ok(wtype)) return -3;
+    if (ncols <= 0 || nrows < 0 || nrows % 32 || ncols % type_cols_multiple(wtype)) return -2;
+    return cuda_rc(launch_block_sumi_tiled(wtype, d_packed, d_xq8, d_sumi, ncols, nrows, stream));
 }
 
 int chimere_b200_moe_gate_up(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, cudaStream_t stream) {
     int rc = check_call(w, ws, ws, T, ws);
     if (rc) return rc;
     const Layout L = make_layout(w, ws->max_T);
-    return cuda_rc(launch_gate_up(gate_up_params(w, T, ws, L), max_entries_for(w, T), stream));
+    return cuda_rc(run_gate_up(w, gate_up_params(w, T, ws, L), max_entries_for(w, T), stream));
 }
 
 int chimere_b200_moe_down_combine(const chimere_moe_layer* w, float* d_y, int T, chimere_moe_workspace* ws,
@@ -207,7 +302,7 @@ int chimere_b200_moe_down_combine(const chimere_moe_layer* w, float* d_y, int T,
     int rc = check_call(w, d_y, d_y, T, ws);
     if (rc) return rc;
     const Layout L = make_layout(w, ws->max_T);
-    return cuda_rc(launch_down(down_params(w, d_y, T, ws, L), max_entries_for(w, T), stream));
+    return cuda_rc(run_down(w, down_params(w, d_y, T, ws, L), max_entries_for(w, T), stream));
 }
 
 int chimere_b200_moe_forward(const chimere_moe_layer* w, const float* d_x, float* d_y, int T, chimere_moe_workspace* ws,
@@ -218,9 +313,9 @@ int chimere_b200_moe_forward(const chimere_moe_layer* w, const float* d_x, float
     const int max_entries = max_entries_for(w, T);
     cudaError_t e = launch_route(route_params(w, d_x, T, ws), stream);
     if (e != cudaSuccess) return cuda_rc(e);
-    e = launch_gate_up(gate_up_params(w, T, ws, L), max_entries, stream);
+    e = run_gate_up(w, gate_up_params(w, T, ws, L), max_entries, stream);
     if (e != cudaSuccess) return cuda_rc(e);
-    e = launch_down(down_params(w, d_y, T, ws, L), max_entries, stream);
+    e = run_down(w, down_params(w, d_y, T, ws, L), max_entries, stream);
     return cuda_rc(e);
 }
 

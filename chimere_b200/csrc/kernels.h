@@ -74,4 +74,15 @@ cudaError_t launch_quantize_q8_1(const float* x, void* out, int64_t ncols, int64
 cudaError_t launch_rmsnorm(const float* x, float* y, int T, int H, float eps, cudaStream_t stream);
 int down_tile_rows(int type_routed, int ncols_routed, int type_shared, int ncols_shared);
 
+// tiled32 layout (tiled.cuh): pack, kernels on packed weights, parity tap
+struct TiledGeomHost { int wk, wr; };  // warps along K x row tiles per CTA (wk * wr = 8)
+TiledGeomHost tiled_gate_up_geom(int type_routed, int type_shared, int H, bool has_shared);
+TiledGeomHost tiled_down_geom(int type_routed, int F, int type_shared, int F_s);
+cudaError_t launch_pack(int type, const void* raw, void* out, int n_mats, int nrows, int ncols, int64_t raw_stride,
+                        int64_t out_stride, cudaStream_t stream);
+cudaError_t launch_gate_up_tiled(const GemvParams& p, int max_entries, cudaStream_t stream);
+cudaError_t launch_down_tiled(const GemvParams& p, int max_entries, cudaStream_t stream);
+cudaError_t launch_block_sumi_tiled(int type, const void* packed, const void* xq8, int32_t* sumi, int ncols, int nrows,
+                                    cudaStream_t stream);
+
 }  // namespace chimere

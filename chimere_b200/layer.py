@@ -96,10 +96,42 @@ class MoeWeightsRaw:
         return self._struct
 
 
+class MoeWeightsTiled:
+    """The layer after the one-time load-side rewrite into the library's tiled32 layout
+    (chimere_b200_moe_pack).  Router tensors are shared with the raw object; the expert matrices live
+    in `arena`.  Offers the same attributes and as_struct() as MoeWeightsRaw."""
+
+    def __init__(self, raw: MoeWeightsRaw, keep_raw: bool = True):
+        lib = abi.load()
+        assert raw.router_weight.is_cuda, "packing runs on the device"
+        self.raw = raw
+        for a in ("H", "E", "F", "F_s", "top_k", "type_gate", "type_up", "type_down", "route_mode", "route_scale", "act"):
+            setattr(self, a, getattr(raw, a))
+        rs = raw.as_struct()
+        nbytes = lib.chimere_b200_moe_pack_bytes(C.byref(rs))
+        if nbytes == 0:
+            raise RuntimeError("chimere_b200_moe_pack_bytes rejected the layer description")
+        self.arena = torch.empty(nbytes, dtype=torch.uint8, device=raw.router_weight.device)
+        self._struct = abi.MoeLayer()
+        stream = torch.cuda.current_stream(self.arena.device).cuda_stream
+        abi.check(lib.chimere_b200_moe_pack(C.byref(rs), self.arena.data_ptr(), nbytes, C.byref(self._struct), stream),
+                  "chimere_b200_moe_pack")
+        self._keep = [raw.router_weight, raw.router_bias, raw.shexp_gate_proj]
+        if not keep_raw:
+            torch.cuda.current_stream(self.arena.device).synchronize()
+            self.raw = None
+
+    def as_struct(self) -> abi.MoeLayer:
+        return self._struct
+
+    def weight_bytes(self) -> int:
+        return self.arena.numel() + sum(t.numel() * t.element_size() for t in self._keep if t is not None)
+
+
 class MoeScratch:
     """Device scratch for one stream, allocated once (the library itself never allocates)."""
 
-    def __init__(self, w: MoeWeightsRaw, max_T: int, device="cuda"):
+    def __init__(self, w, max_T: int, device="cuda"):
         lib = abi.load()
         self.w, self.max_T, self.device = w, max_T, torch.device(device)
         nbytes = lib.chimere_b200_moe_workspace_bytes(C.byref(w.as_struct()), max_T)
@@ -150,7 +182,7 @@ class MoeScratch:
         return int(self._view(self.ws.status, 4).view(torch.int32).item())
 
 
-def forward_moe(w: MoeWeightsRaw, scratch: MoeScratch, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def forward_moe(w, scratch: MoeScratch, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = MoE(x) for x [T, H] f32 on the device; all launches go to torch's current stream."""
     lib = abi.load()
     T = x.shape[0]
@@ -163,7 +195,7 @@ def forward_moe(w: MoeWeightsRaw, scratch: MoeScratch, x: torch.Tensor, out: Opt
     return out
 
 
-def forward_moe_host(w: MoeWeightsRaw, scratch: MoeScratch, x_host: torch.Tensor, y_host: torch.Tensor) -> torch.Tensor:
+def forward_moe_host(w, scratch: MoeScratch, x_host: torch.Tensor, y_host: torch.Tensor) -> torch.Tensor:
     """Same with (pinned) host tensors: copy in, layer, copy out, wait -- one C call."""
     lib = abi.load()
     T = x_host.shape[0]
@@ -175,7 +207,7 @@ def forward_moe_host(w: MoeWeightsRaw, scratch: MoeScratch, x_host: torch.Tensor
     return y_host
 
 
-def route_only(w: MoeWeightsRaw, scratch: MoeScratch, x: torch.Tensor) -> None:
+def route_only(w, scratch: MoeScratch, x: torch.Tensor) -> None:
     lib = abi.load()
     stream = torch.cuda.current_stream(x.device).cuda_stream
     abi.check(lib.chimere_b200_moe_route(C.byref(w.as_struct()), x.data_ptr(), x.shape[0], C.byref(scratch.ws), stream),

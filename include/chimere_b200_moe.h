@@ -44,6 +44,12 @@ enum { CHIMERE_ROUTE_SOFTMAX_RENORM = 0,  /* softmax over E, top-k on probabilit
 enum { CHIMERE_ACT_SWIGLU = 0,  /* silu(gate x) * (up x)   (fused_ops.rs:34-45) */
        CHIMERE_ACT_RELU2 = 1    /* relu(up x)^2, no gate matrix */ };
 
+/* Weight layouts.  GGML: the blocks exactly as the GGUF file holds them.  TILED32: the library's own
+ * lossless rearrangement made once by chimere_b200_moe_pack (32-row tiles, 16 bytes per row and
+ * 32-weight unit, IQ3_S expanded from codebook indices to signed 4-bit codes); the layer-level
+ * entries run several times faster on it. */
+enum { CHIMERE_LAYOUT_GGML = 0, CHIMERE_LAYOUT_TILED32 = 1 };
+
 /* One MoE layer: dimensions, modes and device pointers.  Mirrors MoeWeightsRaw
  * (chimere-server/src/qwen35_model/compute_graph.rs:1000-1049).  For the CPU oracle the same
  * struct is used with host pointers. */
@@ -58,6 +64,8 @@ typedef struct chimere_moe_layer {
     float   route_scale;  /* multiplier on the normalised weights (1.0 for softmax mode) */
     int32_t type_gate, type_up, type_down;          /* routed expert weight types */
     int32_t type_sh_gate, type_sh_up, type_sh_down; /* shared expert weight types */
+    int32_t layout;       /* CHIMERE_LAYOUT_* of the nine expert matrices below */
+    int32_t reserved;
     const float* router_w;     /* f32 [E][H] row-major */
     const float* router_bias;  /* f32 [E] added to the logits before scoring, or NULL */
     const float* shexp_gate_w; /* f32 [H]: shared expert scaled by sigmoid(x . w), or NULL = scale 1 */
@@ -103,6 +111,21 @@ size_t chimere_b200_moe_workspace_bytes(const chimere_moe_layer* w, int max_T);
 int chimere_b200_moe_workspace_init(chimere_moe_workspace* ws, void* d_arena, size_t bytes,
                                     const chimere_moe_layer* w, int max_T, cudaStream_t stream);
 
+/* Bytes of device memory the TILED32 copy of the layer's expert matrices needs (0 on bad arguments). */
+size_t chimere_b200_moe_pack_bytes(const chimere_moe_layer* raw);
+
+/* One-time, load-side: rewrite the expert matrices of `raw` (layout GGML) into `d_arena`
+ * (256-byte aligned, >= pack_bytes) and fill `packed` with a copy of `raw` that points at the
+ * rewritten matrices (layout TILED32; router tensors are shared with `raw`).  The caller may free the
+ * GGML expert matrices afterwards.  F, F_s and H must be multiples of 32. */
+int chimere_b200_moe_pack(const chimere_moe_layer* raw, void* d_arena, size_t bytes,
+                          chimere_moe_layer* packed, cudaStream_t stream);
+
+/* The same rewrite for one matrix [nrows][ncols] (nrows % 32 == 0), and its size. */
+size_t chimere_b200_packed_matrix_bytes(int wtype, int nrows, int ncols);
+int chimere_b200_pack_matrix(int wtype, const void* d_raw, void* d_out, int nrows, int ncols,
+                             cudaStream_t stream);
+
 /* y[T][H] = MoE(x[T][H]).  Replaces moe_ffn.rs:1094-1766 for T tokens.  x, y: device f32.
  * Capturable in a CUDA graph: no allocation, no host synchronisation, no device-to-host copy. */
 int chimere_b200_moe_forward(const chimere_moe_layer* w, const float* d_x, float* d_y, int T,
@@ -142,6 +165,10 @@ int chimere_b200_moe_permute(const chimere_moe_layer* w, int T, chimere_moe_work
  * each 32-wide block (for IQ3_S including the (1 + 2*scale) factor, chimere_kernels.cu:860). */
 int chimere_b200_block_sumi(int wtype, const void* d_w, const void* d_xq8, int32_t* d_sumi,
                             int ncols, int nrows, cudaStream_t stream);
+
+/* The same tap on a TILED32 matrix; the integers must equal those of the GGML form. */
+int chimere_b200_block_sumi_tiled(int wtype, const void* d_packed, const void* d_xq8,
+                                  int32_t* d_sumi, int ncols, int nrows, cudaStream_t stream);
 
 /* RMSNorm with unit weight over rows of length H: y = x / sqrt(mean(x^2) + eps). Used between
  * stacked layers. */

@@ -393,34 +393,15 @@ void orc_permute(const int32_t* idx, int T, int k, int E, int32_t* perm, int32_t
     free(cur);
 }
 
-/* ------------------------------------------------------------------- one expert --------- */
-
-/* act(gate x, up x) -> Q8_1 -> down, for one token and one expert (F wide).
- * Sequence of moe_ffn.rs:1206-1373 for one slot: gate GEMV, up GEMV, SwiGLU, Q8_1 of the
- * intermediate, down GEMV.  inter_q8 (optional) receives the intermediate's Q8_1 bytes. */
-static void expert_forward(int act, int tg, int tu, int td, const void* Wg, const void* Wu, const void* Wd,
-                           const uint8_t* xq8, int H, int F, float* out, uint8_t* inter_q8, float* scratch) {
-    int nbH = H / 32, nbF = F / 32;
-    int64_t rbu = orc_row_bytes(tu, H), rbg = (act == CHIMERE_ACT_SWIGLU) ? orc_row_bytes(tg, H) : 0;
-    float* inter = scratch;
-    for (int r = 0; r < F; r++) {
-        float u = row_dot(tu, (const uint8_t*)Wu + (size_t)r * rbu, xq8, nbH);
-        if (act == CHIMERE_ACT_SWIGLU) {
-            float g = row_dot(tg, (const uint8_t*)Wg + (size_t)r * rbg, xq8, nbH);
-            inter[r] = orc_swiglu(g, u);
-        } else inter[r] = orc_relu2(u);
-    }
-    uint8_t* iq = inter_q8 ? inter_q8 : (uint8_t*)(scratch + F);
-    orc_quantize_q8_1(inter, iq, F);
-    int64_t rbd = orc_row_bytes(td, F);
-    for (int h = 0; h < H; h++) out[h] = row_dot(td, (const uint8_t*)Wd + (size_t)h * rbd, iq, nbF);
-}
-
 /* ------------------------------------------------------------------- whole layer -------- */
 
 /* y[T][H] = MoE(x[T][H]) with host pointers in `w`.  Follows forward_moe_cudarc_with_cache
- * (moe_ffn.rs:1094-1766) token by token: router, top-k, Q8_1 of x, k experts, combine in slot
- * order, shared expert, sigmoid gate add.  Optional taps (any may be NULL):
+ * (moe_ffn.rs:1094-1766) step by step -- router GEMV, top-k, Q8_1 of x (:1099-1204); gate and up
+ * GEMVs and the activation per selected expert (:1206-1305); Q8_1 of the intermediates
+ * (:1307-1323); down GEMVs (:1325-1373); weighted combine in slot order (:1375-1384); the shared
+ * expert (:1597-1730) and the sigmoid gate add (:1736-1766) -- with the loops over tokens,
+ * slots and rows spread over the host threads (tokens are processed in chunks of 64).
+ * Optional taps (any may be NULL):
  *   topk_idx[T][k], topk_w[T][k], logits[T][E], x_q8[T][H/32*36],
  *   inter_q8[T][k+1][Fmax/32*36] (slot k = shared expert), sh_logit[T]. */
 int orc_moe_forward(const chimere_moe_layer* w, const float* x, float* y, int T,
@@ -428,57 +409,91 @@ int orc_moe_forward(const chimere_moe_layer* w, const float* x, float* y, int T,
                     uint8_t* inter_q8_out, float* sh_logit_out) {
     const int H = w->H, E = w->E, F = w->F, Fs = w->F_s, k = w->top_k;
     if (E > 256 || k > 16 || H % 32 || F % 32 || Fs % 32) return -1;
+    const int dual = w->act == CHIMERE_ACT_SWIGLU;
     const int Fmax = F > Fs ? F : Fs;
+    const int S = k + (Fs > 0 ? 1 : 0);                    /* slots per token, the last one shared */
     const size_t xq_row = (size_t)(H / 32) * Q8_1_BYTES, iq_row = (size_t)(Fmax / 32) * Q8_1_BYTES;
-    int rc = 0;
-    #pragma omp parallel
-    {
-        float* logits = (float*)malloc(sizeof(float) * 256);
-        uint8_t* xq = (uint8_t*)malloc(xq_row);
-        float* eout = (float*)malloc(sizeof(float) * (size_t)H * (size_t)(k + 1));
-        float* scratch = (float*)malloc(sizeof(float) * (size_t)Fmax * 3);
-        int32_t idx[16]; float wt[16];
-        #pragma omp for schedule(dynamic, 1)
-        for (int t = 0; t < T; t++) {
+    enum { CHUNK = 64 };
+    int32_t* idx = (int32_t*)malloc(sizeof(int32_t) * CHUNK * 16);
+    float* wt = (float*)malloc(sizeof(float) * CHUNK * 16);
+    float* shl = (float*)calloc(CHUNK, sizeof(float));
+    uint8_t* xq = (uint8_t*)malloc(xq_row * CHUNK);
+    float* inter = (float*)malloc(sizeof(float) * (size_t)CHUNK * S * Fmax);
+    uint8_t* iq = (uint8_t*)malloc(iq_row * (size_t)CHUNK * S);
+    float* eout = (float*)malloc(sizeof(float) * (size_t)CHUNK * S * H);
+    for (int t0 = 0; t0 < T; t0 += CHUNK) {
+        const int nt = (T - t0 < CHUNK) ? T - t0 : CHUNK;
+        /* router, top-k, Q8_1 of the input rows */
+        #pragma omp parallel for schedule(dynamic, 1)
+        for (int i = 0; i < nt; i++) {
+            const int t = t0 + i;
             const float* xt = x + (size_t)t * H;
+            float logits[256];
             orc_router_logits(w->router_w, w->router_bias, xt, E, H, logits);
-            if (w->route_mode == CHIMERE_ROUTE_SOFTMAX_RENORM) orc_topk_softmax(logits, E, k, idx, wt, NULL);
-            else orc_topk_sigmoid(logits, E, k, w->route_scale, idx, wt, NULL);
-            if (w->route_mode == CHIMERE_ROUTE_SOFTMAX_RENORM && w->route_scale != 1.0f)
-                for (int j = 0; j < k; j++) wt[j] *= w->route_scale;
-            orc_quantize_q8_1(xt, xq, H);
-            if (topk_idx) memcpy(topk_idx + (size_t)t * k, idx, sizeof(int32_t) * (size_t)k);
-            if (topk_w) memcpy(topk_w + (size_t)t * k, wt, sizeof(float) * (size_t)k);
+            if (w->route_mode == CHIMERE_ROUTE_SOFTMAX_RENORM) {
+                orc_topk_softmax(logits, E, k, idx + i * 16, wt + i * 16, NULL);
+                if (w->route_scale != 1.0f) for (int j = 0; j < k; j++) wt[i * 16 + j] *= w->route_scale;
+            } else orc_topk_sigmoid(logits, E, k, w->route_scale, idx + i * 16, wt + i * 16, NULL);
+            orc_quantize_q8_1(xt, xq + (size_t)i * xq_row, H);
+            if (Fs > 0 && w->shexp_gate_w) shl[i] = orc_dot_strided256(xt, w->shexp_gate_w, H);
+            if (topk_idx) memcpy(topk_idx + (size_t)t * k, idx + i * 16, sizeof(int32_t) * (size_t)k);
+            if (topk_w) memcpy(topk_w + (size_t)t * k, wt + i * 16, sizeof(float) * (size_t)k);
             if (logits_out) memcpy(logits_out + (size_t)t * E, logits, sizeof(float) * (size_t)E);
-            if (x_q8_out) memcpy(x_q8_out + (size_t)t * xq_row, xq, xq_row);
-            for (int j = 0; j < k; j++) {
-                int e = idx[j];
-                expert_forward(w->act, w->type_gate, w->type_up, w->type_down,
-                               w->gate_exps ? (const uint8_t*)w->gate_exps + (size_t)e * w->stride_gate : NULL,
-                               (const uint8_t*)w->up_exps + (size_t)e * w->stride_up,
-                               (const uint8_t*)w->down_exps + (size_t)e * w->stride_down,
-                               xq, H, F, eout + (size_t)j * H,
-                               inter_q8_out ? inter_q8_out + ((size_t)t * (k + 1) + j) * iq_row : NULL, scratch);
-            }
-            float* yt = y + (size_t)t * H;
-            orc_weighted_combine(eout, wt, yt, H, k);
-            if (Fs > 0) {
-                float* sh = eout + (size_t)k * H;
-                expert_forward(w->act, w->type_sh_gate, w->type_sh_up, w->type_sh_down,
-                               w->sh_gate, w->sh_up, w->sh_down, xq, H, Fs, sh,
-                               inter_q8_out ? inter_q8_out + ((size_t)t * (k + 1) + k) * iq_row : NULL, scratch);
-                if (w->shexp_gate_w) {
-                    float lg = orc_dot_strided256(xt, w->shexp_gate_w, H);
-                    if (sh_logit_out) sh_logit_out[t] = lg;
-                    orc_sigmoid_gate_add(sh, lg, yt, yt, H);
-                } else {
-                    for (int h = 0; h < H; h++) yt[h] = sh[h] + yt[h];
-                }
+            if (x_q8_out) memcpy(x_q8_out + (size_t)t * xq_row, xq + (size_t)i * xq_row, xq_row);
+            if (sh_logit_out && Fs > 0 && w->shexp_gate_w) sh_logit_out[t] = shl[i];
+        }
+        /* gate / up rows and the activation, one (token, slot, row) at a time */
+        #pragma omp parallel for collapse(2) schedule(dynamic, 16)
+        for (int p = 0; p < nt * S; p++) {
+            for (int r = 0; r < Fmax; r++) {
+                const int i = p / S, j = p % S, sh = (j == k);
+                const int Fe = sh ? Fs : F;
+                if (r >= Fe) continue;
+                const int tu = sh ? w->type_sh_up : w->type_up, tg = sh ? w->type_sh_gate : w->type_gate;
+                const uint8_t* Wu = sh ? (const uint8_t*)w->sh_up : (const uint8_t*)w->up_exps + (size_t)idx[i * 16 + j] * w->stride_up;
+                const uint8_t* xr = xq + (size_t)i * xq_row;
+                float u = row_dot(tu, Wu + (size_t)r * orc_row_bytes(tu, H), xr, H / 32), v;
+                if (dual) {
+                    const uint8_t* Wg = sh ? (const uint8_t*)w->sh_gate : (const uint8_t*)w->gate_exps + (size_t)idx[i * 16 + j] * w->stride_gate;
+                    v = orc_swiglu(row_dot(tg, Wg + (size_t)r * orc_row_bytes(tg, H), xr, H / 32), u);
+                } else v = orc_relu2(u);
+                inter[(size_t)p * Fmax + r] = v;
             }
         }
-        free(logits); free(xq); free(eout); free(scratch);
+        /* Q8_1 of the intermediates */
+        #pragma omp parallel for schedule(static)
+        for (int p = 0; p < nt * S; p++) {
+            const int i = p / S, j = p % S;
+            const int Fe = (j == k) ? Fs : F;
+            memset(iq + (size_t)p * iq_row, 0, iq_row);
+            orc_quantize_q8_1(inter + (size_t)p * Fmax, iq + (size_t)p * iq_row, Fe);
+            if (inter_q8_out) memcpy(inter_q8_out + ((size_t)(t0 + i) * (k + 1) + j) * iq_row, iq + (size_t)p * iq_row, iq_row);
+        }
+        /* down rows */
+        #pragma omp parallel for collapse(2) schedule(dynamic, 16)
+        for (int p = 0; p < nt * S; p++) {
+            for (int h = 0; h < H; h++) {
+                const int i = p / S, j = p % S, sh = (j == k);
+                const int Fe = sh ? Fs : F;
+                const int td = sh ? w->type_sh_down : w->type_down;
+                const uint8_t* Wd = sh ? (const uint8_t*)w->sh_down : (const uint8_t*)w->down_exps + (size_t)idx[i * 16 + j] * w->stride_down;
+                eout[(size_t)p * H + h] = row_dot(td, Wd + (size_t)h * orc_row_bytes(td, Fe), iq + (size_t)p * iq_row, Fe / 32);
+            }
+        }
+        /* combine in slot order, then the shared expert */
+        #pragma omp parallel for schedule(static)
+        for (int i = 0; i < nt; i++) {
+            float* yt = y + (size_t)(t0 + i) * H;
+            orc_weighted_combine(eout + (size_t)i * S * H, wt + i * 16, yt, H, k);
+            if (Fs > 0) {
+                const float* sh = eout + ((size_t)i * S + k) * H;
+                if (w->shexp_gate_w) orc_sigmoid_gate_add(sh, shl[i], yt, yt, H);
+                else for (int h = 0; h < H; h++) yt[h] = sh[h] + yt[h];
+            }
+        }
     }
-    return rc;
+    free(idx); free(wt); free(shl); free(xq); free(inter); free(iq); free(eout);
+    return 0;
 }
 
 int orc_num_threads(void) {

@@ -17,9 +17,12 @@ _lib = None
 
 
 def build(force: bool = False) -> str:
-    src = os.path.join(ORACLE_DIR, "moe_oracle.c")
-    if force or not os.path.exists(LIB_PATH) or os.path.getmtime(src) > os.path.getmtime(LIB_PATH):
-        subprocess.run(["make", "-C", ORACLE_DIR, "libmoe_oracle.so"], check=True, capture_output=True)
+    """make decides whether the oracle is stale (it depends on the C file, the codebook and the ABI header)."""
+    if force and os.path.exists(LIB_PATH):
+        os.unlink(LIB_PATH)
+    r = subprocess.run(["make", "-C", ORACLE_DIR, "libmoe_oracle.so"], capture_output=True, text=True)
+    if r.returncode != 0 and not os.path.exists(LIB_PATH):
+        raise RuntimeError("building the CPU oracle failed:\n" + r.stdout + r.stderr)
     return LIB_PATH
 
 

@@ -41,7 +41,7 @@ def test_constants(lib):
 
 
 def test_struct_sizes():
-    assert C.sizeof(abi.MoeLayer) == 152
+    assert C.sizeof(abi.MoeLayer) == 160
     assert C.sizeof(abi.MoeWorkspace) == 8 + 14 * 8
 
 

@@ -13,7 +13,7 @@ import torch
 import oracle
 import refkernels
 from chimere_b200 import abi, configs, formats
-from chimere_b200.layer import MoeScratch, forward_moe, forward_moe_host, route_only
+from chimere_b200.layer import MoeScratch, MoeWeightsTiled, forward_moe, forward_moe_host, route_only
 
 pytestmark = pytest.mark.gpu
 
@@ -46,12 +46,22 @@ def near_tie_ok(idx_gpu, idx_cpu, logits):
 _layers = {}
 
 
-def layer_pair(cfg):
-    """(device weights, host copy) of a configuration, generated once per session on the GPU."""
+def layer_pair(cfg, layout="ggml"):
+    """(device weights, host copy) of a configuration, generated once per session on the GPU;
+    layout "tiled" returns the packed form of the same weights."""
     if cfg not in _layers:
         wd = configs.make_layer(cfg, device="cuda")
         _layers[cfg] = (wd, wd.to("cpu"))
-    return _layers[cfg]
+    wd, wh = _layers[cfg]
+    if layout == "tiled":
+        key = (cfg, "tiled")
+        if key not in _layers:
+            _layers[key] = MoeWeightsTiled(wd)
+        return _layers[key], wh
+    return wd, wh
+
+
+LAYOUTS = ["ggml", "tiled"]
 
 
 SMALL = [
@@ -65,8 +75,9 @@ SMALL = [
 
 @pytest.mark.parametrize("cfg", SMALL, ids=lambda c: c.name)
 @pytest.mark.parametrize("T", [1, 3, 8, 9, 40])
-def test_forward_small(cfg, T):
-    wd, wh = layer_pair(cfg)
+@pytest.mark.parametrize("layout", LAYOUTS)
+def test_forward_small(cfg, T, layout):
+    wd, wh = layer_pair(cfg, layout)
     x = configs.make_input(cfg, T, device="cuda")
     sc = MoeScratch(wd, T)
     y = forward_moe(wd, sc, x)
@@ -103,8 +114,9 @@ FULL = [(configs.QWEN_Q4_0, 16), (configs.QWEN_IQ3S, 1), (configs.QWEN_IQ3S, 2),
 
 
 @pytest.mark.parametrize("cfg,T", FULL, ids=lambda v: getattr(v, "name", str(v)))
-def test_forward_full_size(cfg, T):
-    wd, wh = layer_pair(cfg)
+@pytest.mark.parametrize("layout", LAYOUTS)
+def test_forward_full_size(cfg, T, layout):
+    wd, wh = layer_pair(cfg, layout)
     x = configs.make_input(cfg, T, device="cuda")
     sc = MoeScratch(wd, T)
     y = forward_moe(wd, sc, x)
@@ -176,6 +188,15 @@ def test_block_sumi_bit_exact(qtype):
     abi.check(lib.chimere_b200_block_sumi(qtype, Wd.data_ptr(), xd.data_ptr(), out.data_ptr(), cols, rows, None), "sumi")
     torch.cuda.synchronize()
     assert np.array_equal(out.cpu().numpy(), ref)
+    # the packed (tiled32) form of the same matrix must give the same integers: the rewrite is lossless
+    nbytes = lib.chimere_b200_packed_matrix_bytes(qtype, rows, cols)
+    assert nbytes > 0
+    packed = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    abi.check(lib.chimere_b200_pack_matrix(qtype, Wd.data_ptr(), packed.data_ptr(), rows, cols, None), "pack")
+    out2 = torch.full((rows, cols // 32), -1, dtype=torch.int32, device="cuda")
+    abi.check(lib.chimere_b200_block_sumi_tiled(qtype, packed.data_ptr(), xd.data_ptr(), out2.data_ptr(), cols, rows, None), "sumi tiled")
+    torch.cuda.synchronize()
+    assert np.array_equal(out2.cpu().numpy(), ref)
 
 
 def _mmvq(name):
@@ -280,7 +301,7 @@ def test_full_size_properties_decode_sweep():
     """Properties at the benchmark's full size that need no oracle run: rows of y depend only on
     their own token (batch of 8 == eight batches of 1), and routing weights sum to 1."""
     cfg = configs.QWEN_IQ3S
-    wd, _ = layer_pair(cfg)
+    wd, _ = layer_pair(cfg, "tiled")
     x = configs.make_input(cfg, 8, device="cuda")
     sc = MoeScratch(wd, 8)
     y8 = forward_moe(wd, sc, x).clone()
