@@ -27,6 +27,7 @@ int validate_layer(const chimere_moe_layer* w) {
     if (w->top_k <= 0 || w->top_k > kMaxTopK || w->top_k > w->E) return -2;
     if (w->H % 32 || w->F % 32 || w->F_s % 32) return -2;
     if (w->layout != CHIMERE_LAYOUT_GGML && w->layout != CHIMERE_LAYOUT_TILED32) return -2;
+    if (w->layout == CHIMERE_LAYOUT_TILED32 && w->H % 128) return -2;   // Q8_1 input rows must be 16-byte multiples
     if (w->route_mode != CHIMERE_ROUTE_SOFTMAX_RENORM && w->route_mode != CHIMERE_ROUTE_SIGMOID_NORM_SCALE) return -2;
     if (w->act != CHIMERE_ACT_SWIGLU && w->act != CHIMERE_ACT_RELU2) return -2;
     const bool dual = w->act == CHIMERE_ACT_SWIGLU;
@@ -67,7 +68,7 @@ Layout make_layout(const chimere_moe_layer* w, int T) {
                           (32 * tiled_down_geom(w->type_down, w->F, w->type_sh_down, w->F_s).wr);
     const int max_tiles = L.n_row_tiles > L.n_row_tiles_tiled ? L.n_row_tiles : L.n_row_tiles_tiled;
     L.n_counters = kCtrRouteTile + (T + 7) / 8 + T * max_tiles;
-    L.inter_stride = (size_t)(Fmax / 32) * kQ81Bytes;
+    L.inter_stride = ((size_t)(Fmax / 32) * kQ81Bytes + 15) & ~(size_t)15;   // rows start on 16-byte boundaries (bulk copies)
     size_t o = 0;
     L.topk_idx = o; o += up256((size_t)T * k * 4);
     L.topk_w = o; o += up256((size_t)T * k * 4);

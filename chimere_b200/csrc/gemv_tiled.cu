@@ -1,122 +1,134 @@
 // gemv_tiled.cu -- the decode-path GEMV kernels on tiled32 weights (see tiled.cuh).
 //
-// One warp = 32 consecutive rows of one expert matrix, lane = row.  A warp streams its part of
-// the K range with contiguous 512-byte reads (128 bits per lane) straight into registers, decodes
-// in registers and multiplies with the tokens' Q8_1 activations, which sit in shared memory as an
-// int8 plane + f32 scale plane and are read as warp-wide broadcasts.  The eight warps of a CTA
-// are WR row tiles x WK slices of K; slices are added up through shared memory in a fixed order.
+// Persistent CTAs, one per SM: a producer warp walks the CTA's share of the work items and keeps
+// a ring of shared-memory stages filled with cp.async.bulk copies (weights come as contiguous
+// slabs of the tiled layout, activations as whole Q8_1 rows); eight consumer warps drain it.
+// The producer runs ahead across items, so the dependent look-ups that name an item's bytes
+// (work list -> permutation -> token row) are off the consumers' critical path and the memory
+// system always has a few tens of KB per SM in flight.
 //
-//   gate_up_tiled_kernel : act(gate . x, up . x) -> Q8_1 blocks of the intermediates
-//                          (replaces moe_ffn.rs:1206-1323 and :1597-1700 of the reference)
-//   down_tiled_kernel    : down . inter -> per-pair rows, then the weighted combine in slot order
-//                          plus the sigmoid-gated shared expert by whichever CTA completes a
-//                          token's row tile (replaces moe_ffn.rs:1325-1384 and :1700-1766)
+// Consumer side: one warp = 32 consecutive rows of one expert matrix, lane = row; a lane reads its
+// own 16 bytes of every 32-weight unit from the stage (conflict-free 128-bit shared loads), decodes
+// in registers and multiplies with the tokens' Q8_1 blocks, read from shared memory as warp-wide
+// broadcasts.  The eight warps are WR row tiles x WK slices of K; slices meet in shared memory
+// and are added in a fixed order.
+//
+//   STAGE_GATE_UP : act(gate . x, up . x) -> Q8_1 blocks of the intermediates
+//                   (replaces moe_ffn.rs:1206-1323 and :1597-1700 of the reference)
+//   STAGE_DOWN    : down . inter -> per-pair rows; the CTA that completes a token's row tile adds the
+//                   rows up in slot order with the routing weights and the sigmoid-gated shared
+//                   expert (replaces moe_ffn.rs:1325-1384 and :1700-1766)
 #include "common.cuh"
 #include "kernels.h"
 #include "tiled.cuh"
 
 namespace chimere {
 
-constexpr int kThreadsT = 256;
+constexpr int kConsumerWarps = 8;
+constexpr int kStreamThreads = 32 * (kConsumerWarps + 1);  // + one producer warp
+constexpr int kSlabMax = 36 * 1024 + 1024;                  // bytes of one weight stage
+constexpr int kStageGateUp = 0, kStageDown = 1;
 
-// acc[i] += sum over the units of one group of (scale_w * scale_x) * integer block dot, for up to M tokens
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// How an item's weights are cut into slabs (identical on the host, in the producer and in the consumers).
+struct SlabPlan {
+    int tile_bytes, group_bytes, ngroups;
+    int whole_tiles;       // 1: a slab is `per` whole tiles; 0: a slab is `per` groups of the single tile (wr == 1)
+    int per, slabs_per_mat;
+};
+__host__ __device__ inline SlabPlan slab_plan(int tile_bytes, int group_bytes, int wr) {
+    SlabPlan s;
+    s.tile_bytes = tile_bytes; s.group_bytes = group_bytes;
+    s.ngroups = (tile_bytes + group_bytes - 1) / group_bytes;
+    if (tile_bytes <= kSlabMax) {
+        s.whole_tiles = 1;
+        s.per = kSlabMax / tile_bytes; if (s.per > wr) s.per = wr;
+        s.slabs_per_mat = (wr + s.per - 1) / s.per;
+    } else {
+        s.whole_tiles = 0;
+        s.per = kSlabMax / group_bytes;
+        s.slabs_per_mat = (s.ngroups + s.per - 1) / s.per;
+    }
+    return s;
+}
+
+struct StreamSmem { uint32_t bars, meta, red, act, ring, total; int nst; };
+// bars: full[nst] empty[nst] afull[2] aempty[2]; meta: 2 x 64 ints; red; act: 2 buffers; ring: nst stages
+__host__ __device__ inline StreamSmem stream_smem(int act_row_bytes, int wr, int wk, bool dual) {
+    StreamSmem s;
+    uint32_t o = 0;
+    s.bars = o; o += 256;
+    s.meta = o; o += 2 * 64 * 4;
+    s.red = o; o += (uint32_t)(dual ? 2 : 1) * wk * kMaxGroupTokens * 32 * wr * 4;
+    o = (o + 127u) & ~127u;
+    s.act = o; o += 2u * kMaxGroupTokens * (uint32_t)act_row_bytes;
+    o = (o + 127u) & ~127u;
+    s.ring = o;
+    int nst = (int)((220u * 1024u - o) / kSlabMax);
+    if (nst > 6) nst = 6;
+    s.nst = nst;
+    s.total = o + (uint32_t)nst * kSlabMax;
+    return s;
+}
+
+// acc[i] += sum over the units of one group of (scale_w * scale_x) * integer block dot, for up to M tokens.
+// Activations: Q8_1 rows in shared memory, row i at act + i * act_stride.
 template <int TYPE, int M>
-__device__ __forceinline__ void group_dot(const typename Tiled<TYPE>::Regs& r, int nu, int unit0, const int8_t* aq,
-                                          const float* ad, int ncols, int nb, int m, float (&acc)[M]) {
+__device__ __forceinline__ void group_dot(const uint8_t* tile, int grp, int lane, int nu, const uint8_t* act, int act_stride,
+                                          int m, float (&acc)[M]) {
     using TT = Tiled<TYPE>;
+    typename TT::Regs r;
+    TT::load(tile, grp, lane, nu, r);
 #pragma unroll
     for (int u = 0; u < TT::kGroupUnits; ++u) {
         if (u < nu) {
             int w[8];
             TT::decode(r, u, w);
             const float dw = TT::dscale(r, u);
-            const int b = unit0 + u;
+            const int b = grp * TT::kGroupUnits + u;
 #pragma unroll
             for (int i = 0; i < M; ++i) {
                 if (i < m) {
-                    const int4* q = reinterpret_cast<const int4*>(aq + (size_t)i * ncols + b * 32);
-                    const int4 q0 = q[0], q1 = q[1];
-                    int s = __dp4a(w[0], q0.x, 0);
-                    s = __dp4a(w[1], q0.y, s); s = __dp4a(w[2], q0.z, s); s = __dp4a(w[3], q0.w, s);
-                    s = __dp4a(w[4], q1.x, s); s = __dp4a(w[5], q1.y, s); s = __dp4a(w[6], q1.z, s); s = __dp4a(w[7], q1.w, s);
-                    acc[i] = fmaf(dw * ad[i * nb + b], (float)TT::finish(s, r, u), acc[i]);
+                    const uint32_t* q = reinterpret_cast<const uint32_t*>(act + (size_t)i * act_stride + b * kQ81Bytes);
+                    int s = __dp4a(w[0], (int)q[1], 0);
+                    s = __dp4a(w[1], (int)q[2], s); s = __dp4a(w[2], (int)q[3], s); s = __dp4a(w[3], (int)q[4], s);
+                    s = __dp4a(w[4], (int)q[5], s); s = __dp4a(w[5], (int)q[6], s); s = __dp4a(w[6], (int)q[7], s);
+                    s = __dp4a(w[7], (int)q[8], s);
+                    acc[i] = fmaf(dw * h2f(q[0] & 0xFFFFu), (float)TT::finish(s, r, u), acc[i]);
                 }
             }
         }
     }
 }
 
-// Q8_1 rows (36-byte blocks) -> int8 plane aq[i][ncols] and f32 scale plane ad[i][nb]
-__device__ __forceinline__ void stage_q8_rows(const uint8_t* const* rows, int m, int nb, int ncols, int8_t* aq, float* ad, int tid) {
-    for (int i = 0; i < m; ++i) {
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(rows[i]);
-        uint32_t* dq = reinterpret_cast<uint32_t*>(aq + (size_t)i * ncols);
-        for (int wd = tid; wd < nb * 9; wd += kThreadsT) {
-            const int b = wd / 9, r = wd - b * 9;
-            const uint32_t v = __ldcg(src + wd);
-            if (r == 0) ad[i * nb + b] = h2f(v & 0xFFFFu);
-            else dq[b * 8 + (r - 1)] = v;
-        }
-    }
-}
+struct StreamGeom { int wk, wr; };
 
-struct TiledGeom { int wk, wr; };
-__host__ __device__ inline TiledGeom tiled_geom(int ngroups_min) {
-    int wk = 8;
-    while (wk > 1 && wk > ngroups_min) wk >>= 1;
-    return TiledGeom{wk, 8 / wk};
-}
-
-struct TiledSmem { uint32_t aq, ad, red, total; };
-__host__ __device__ inline TiledSmem tiled_smem(int ncols, int wr, int wk, bool dual) {
-    TiledSmem s;
-    uint32_t o = 0;
-    s.aq = o; o += (uint32_t)kMaxGroupTokens * ncols;
-    s.ad = o; o += (uint32_t)kMaxGroupTokens * (ncols / 32) * 4;
-    o = (o + 15u) & ~15u;
-    s.red = o; o += (uint32_t)(dual ? 2 : 1) * wk * kMaxGroupTokens * 32 * wr * 4;
-    s.total = o;
-    return s;
-}
-
-// The shared front part of both kernels: every warp accumulates its (row tile, K slice) for the
-// entry's tokens and leaves the partial sums in red[(mat * wk + k) * 8 + i][wr * 32 + lane].
-template <int TYPE, bool DUAL, int M>
-__device__ __forceinline__ void tile_partials(const uint8_t* tile_a, const uint8_t* tile_b, bool valid, int wk_id, int wk, int wr_id,
-                                              int wr, int lane, int ncols, int m, const int8_t* aq, const float* ad, float* red) {
+template <int TYPE, int M>
+__device__ __forceinline__ void consume_slab(const uint8_t* stage, const SlabPlan& sp, int si, int wr_id, int wk_id, int wk,
+                                             int wr, int lane, int nb, bool row_tile_valid, const uint8_t* act, int act_stride,
+                                             int m, float (&acc)[M]) {
     using TT = Tiled<TYPE>;
-    const int nb = ncols >> 5;
-    const int ngroups = (nb + TT::kGroupUnits - 1) / TT::kGroupUnits;
-    float aa[M], ab[M];
-#pragma unroll
-    for (int i = 0; i < M; ++i) { aa[i] = 0.0f; ab[i] = 0.0f; }
-    if (valid) {
-        for (int grp = wk_id; grp < ngroups; grp += wk) {
-            const int nu = min(TT::kGroupUnits, nb - grp * TT::kGroupUnits);
-            typename TT::Regs ra, rb;
-            TT::load(tile_a, grp, lane, nu, ra);
-            if (DUAL) TT::load(tile_b, grp, lane, nu, rb);
-            group_dot<TYPE, M>(ra, nu, grp * TT::kGroupUnits, aq, ad, ncols, nb, m, aa);
-            if (DUAL) group_dot<TYPE, M>(rb, nu, grp * TT::kGroupUnits, aq, ad, ncols, nb, m, ab);
-        }
+    if (!row_tile_valid) return;
+    const uint8_t* tile;
+    int g0, g1;
+    if (sp.whole_tiles) {
+        const int t0 = si * sp.per;
+        if (wr_id < t0 || wr_id >= t0 + sp.per || wr_id >= wr) return;
+        tile = stage + (size_t)(wr_id - t0) * sp.tile_bytes;
+        g0 = 0; g1 = sp.ngroups;
+    } else {
+        if (wr_id != 0) return;
+        g0 = si * sp.per; g1 = min(sp.ngroups, g0 + sp.per);
+        tile = stage - (size_t)g0 * sp.group_bytes;
     }
-    const int col = wr_id * 32 + lane, width = 32 * wr;
-#pragma unroll
-    for (int i = 0; i < M; ++i) {
-        if (i < m) {
-            red[((0 * wk + wk_id) * kMaxGroupTokens + i) * width + col] = aa[i];
-            if (DUAL) red[((1 * wk + wk_id) * kMaxGroupTokens + i) * width + col] = ab[i];
-        }
+    for (int g = g0 + wk_id; g < g1; g += wk) {
+        const int nu = min(TT::kGroupUnits, nb - g * TT::kGroupUnits);
+        group_dot<TYPE, M>(tile, g, lane, nu, act, act_stride, m, acc);
     }
-}
-
-template <int TYPE, bool DUAL>
-__device__ __forceinline__ void tile_partials_m(const uint8_t* tile_a, const uint8_t* tile_b, bool valid, int wk_id, int wk, int wr_id,
-                                                int wr, int lane, int ncols, int m, const int8_t* aq, const float* ad, float* red) {
-    if (m == 1) tile_partials<TYPE, DUAL, 1>(tile_a, tile_b, valid, wk_id, wk, wr_id, wr, lane, ncols, m, aq, ad, red);
-    else if (m == 2) tile_partials<TYPE, DUAL, 2>(tile_a, tile_b, valid, wk_id, wk, wr_id, wr, lane, ncols, m, aq, ad, red);
-    else if (m <= 4) tile_partials<TYPE, DUAL, 4>(tile_a, tile_b, valid, wk_id, wk, wr_id, wr, lane, ncols, m, aq, ad, red);
-    else tile_partials<TYPE, DUAL, 8>(tile_a, tile_b, valid, wk_id, wk, wr_id, wr, lane, ncols, m, aq, ad, red);
 }
 
 __device__ __forceinline__ float sum_slices(const float* red, int mat, int wk, int i, int width, int col) {
@@ -125,146 +137,222 @@ __device__ __forceinline__ float sum_slices(const float* red, int mat, int wk, i
     return v;
 }
 
-// grid = (ceil(max rows / (32*wr)), max entries); an instance handles the entries of its weight type
-template <int TYPE, bool DUAL>
-__global__ void __launch_bounds__(kThreadsT) gate_up_tiled_kernel(const GemvParams p, int wk, int wr) {
+// meta words per item (written by the producer, read by the consumers)
+constexpr int kMetaM = 0, kMetaTile0 = 1, kMetaNTilesTotal = 2, kMetaShared = 3, kMetaOutRow = 8, kMetaTok = 16, kMetaValid = 4;
+
+template <int TYPE, int STAGE, bool DUAL>
+__global__ void __launch_bounds__(kStreamThreads, 1) stream_kernel(const GemvParams p, int wk, int wr) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ const uint8_t* s_rows[kMaxGroupTokens];
-    __shared__ int s_out_row[kMaxGroupTokens];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if ((int)blockIdx.y >= __ldcg(p.group_list)) return;
-    const int* ent = p.group_list + kListHeader + 4 * blockIdx.y;
-    const int expert = __ldcg(ent), start = __ldcg(ent + 1), m = __ldcg(ent + 2);
-    const bool shared = expert < 0;
-    if ((shared ? p.type_shared : p.type_routed) != TYPE) return;
-    const int nrows = shared ? p.nrows_shared : p.nrows_routed;
-    if ((int)blockIdx.x * 32 * wr >= nrows) return;
-    const int ncols = p.H, nb = ncols >> 5;
-    const TiledSmem sp = tiled_smem(ncols, wr, wk, DUAL);
-    int8_t* aq = reinterpret_cast<int8_t*>(smem + sp.aq);
-    float* ad = reinterpret_cast<float*>(smem + sp.ad);
-    float* red = reinterpret_cast<float*>(smem + sp.red);
+    // ---- static description of an item ----
+    const int ncols_r = p.ncols_routed, ncols_s = p.ncols_shared;
+    const int nrows_r = p.nrows_routed, nrows_s = p.nrows_shared;
+    const bool do_r = p.type_routed == TYPE, do_s = nrows_s > 0 && p.type_shared == TYPE;
+    const int tiles_r = (nrows_r / 32 + wr - 1) / wr, tiles_s = nrows_s > 0 ? (nrows_s / 32 + wr - 1) / wr : 0;  // items per entry
+    const int act_row_bytes = (int)p.in_stride;
+    const StreamSmem ss = stream_smem(act_row_bytes, wr, wk, DUAL);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + ss.bars);
+    uint64_t* empty = full + ss.nst;
+    uint64_t* afull = empty + ss.nst;
+    uint64_t* aempty = afull + 2;
+    int* meta = reinterpret_cast<int*>(smem + ss.meta);
+    float* red = reinterpret_cast<float*>(smem + ss.red);
+    uint8_t* actbuf = smem + ss.act;
+    uint8_t* ring = smem + ss.ring;
+    const int nst = ss.nst;
 
-    if (tid < m) {
-        int t, orow;
-        if (shared) { t = start + tid; orow = p.T * p.top_k + t; }
-        else { const int q = __ldcg(p.perm + start + tid); t = q / p.top_k; orow = q; }
-        s_rows[tid] = p.in_q8 + (size_t)t * p.in_stride;
-        s_out_row[tid] = orow;
+    if (tid == 0) {
+        for (int i = 0; i < nst; ++i) { mbar_init(full + i, 1); mbar_init(empty + i, kConsumerWarps); }
+        for (int i = 0; i < 2; ++i) { mbar_init(afull + i, 1); mbar_init(aempty + i, kConsumerWarps); }
+        mbar_fence_init();
     }
     __syncthreads();
-    stage_q8_rows(s_rows, m, nb, ncols, aq, ad, tid);
-    __syncthreads();
 
-    const int wr_id = warp / wk, wk_id = warp - wr_id * wk;
-    const int tile = blockIdx.x * wr + wr_id;
-    const bool valid = tile * 32 < nrows;
-    const int64_t tb = Tiled<TYPE>::tile_bytes(ncols);
-    const uint8_t* up = (shared ? p.sh_b : p.w_b + (size_t)expert * p.stride_b) + (size_t)tile * tb;
-    const uint8_t* gate = DUAL ? (shared ? p.sh_a : p.w_a + (size_t)expert * p.stride_a) + (size_t)tile * tb : nullptr;
-    tile_partials_m<TYPE, DUAL>(up, gate, valid, wk_id, wk, wr_id, wr, lane, ncols, m, aq, ad, red);
-    __syncthreads();
+    const int n_routed = __ldcg(p.group_list + 1), n_shared = __ldcg(p.group_list + 2);
+    const int items_r = do_r ? n_routed * tiles_r : 0, items_s = do_s ? n_shared * tiles_s : 0;
+    const int total = items_r + items_s;
+    const int it0 = (int)(((int64_t)blockIdx.x * total) / gridDim.x), it1 = (int)(((int64_t)(blockIdx.x + 1) * total) / gridDim.x);
+    const int n_mats = DUAL ? 2 : 1;
 
-    // (token, row tile) pairs: sum the K slices, activation, Q8_1 of the 32 results (lane = element)
-    const int width = 32 * wr;
-    for (int pr = warp; pr < m * wr; pr += 8) {
-        const int i = pr / wr, wq = pr - i * wr;
-        const int t32 = blockIdx.x * wr + wq;
-        if (t32 * 32 >= nrows) continue;
-        const float u = sum_slices(red, 0, wk, i, width, wq * 32 + lane);
-        float v;
-        if (DUAL) v = silu_mul_ref(sum_slices(red, 1, wk, i, width, wq * 32 + lane), u);
-        else { const float r = fmaxf(u, 0.0f); v = r * r; }
-        float amax = fabsf(v), sum = v;
-#pragma unroll
-        for (int s = 16; s > 0; s >>= 1) {
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
-            sum += __shfl_xor_sync(0xffffffffu, sum, s);
-        }
-        const float d = amax / 127.0f;
-        const int8_t q = (amax == 0.0f) ? (int8_t)0 : (int8_t)roundf(v / d);
-        uint8_t* out = p.inter_q8 + (size_t)s_out_row[i] * p.inter_stride + (size_t)t32 * kQ81Bytes;
-        reinterpret_cast<int8_t*>(out)[4 + lane] = q;
-        if (lane == 0) *reinterpret_cast<__half2*>(out) = __halves2half2(__float2half(d), __float2half(sum));
-    }
-}
-
-template <int TYPE>
-__global__ void __launch_bounds__(kThreadsT) down_tiled_kernel(const GemvParams p, int wk, int wr) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ const uint8_t* s_rows[kMaxGroupTokens];
-    __shared__ int s_out_row[kMaxGroupTokens];
-    __shared__ int s_tok[kMaxGroupTokens];
-    __shared__ int s_done[kMaxGroupTokens];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if ((int)blockIdx.y >= __ldcg(p.group_list)) return;
-    const int* ent = p.group_list + kListHeader + 4 * blockIdx.y;
-    const int expert = __ldcg(ent), start = __ldcg(ent + 1), m = __ldcg(ent + 2);
-    const bool shared = expert < 0;
-    if ((shared ? p.type_shared : p.type_routed) != TYPE) return;
-    const int H = p.H;
-    const int ncols = shared ? p.ncols_shared : p.ncols_routed, nb = ncols >> 5;
-    const int width = 32 * wr;
-    const int r0 = blockIdx.x * width;
-    if (r0 >= H) return;
-    const TiledSmem sp = tiled_smem(max(p.ncols_routed, p.ncols_shared), wr, wk, false);
-    int8_t* aq = reinterpret_cast<int8_t*>(smem + sp.aq);
-    float* ad = reinterpret_cast<float*>(smem + sp.ad);
-    float* red = reinterpret_cast<float*>(smem + sp.red);
-
-    if (tid < m) {
-        int t, irow;
-        if (shared) { t = start + tid; irow = p.T * p.top_k + t; }
-        else { irow = __ldcg(p.perm + start + tid); t = irow / p.top_k; }
-        s_rows[tid] = p.in_q8 + (size_t)irow * p.in_stride;
-        s_out_row[tid] = irow;
-        s_tok[tid] = t;
-    }
-    __syncthreads();
-    stage_q8_rows(s_rows, m, nb, ncols, aq, ad, tid);
-    __syncthreads();
-
-    const int wr_id = warp / wk, wk_id = warp - wr_id * wk;
-    const int tile = blockIdx.x * wr + wr_id;
-    const bool valid = tile * 32 < H;
-    const uint8_t* wt = (shared ? p.sh_a : p.w_a + (size_t)expert * p.stride_a) + (size_t)tile * Tiled<TYPE>::tile_bytes(ncols);
-    tile_partials_m<TYPE, false>(wt, nullptr, valid, wk_id, wk, wr_id, wr, lane, ncols, m, aq, ad, red);
-    __syncthreads();
-
-    const int rows_here = min(width, H - r0);
-    for (int e = tid; e < m * width; e += kThreadsT) {
-        const int i = e / width, c = e - i * width;
-        if (c < rows_here) p.pair_out[(size_t)s_out_row[i] * H + r0 + c] = sum_slices(red, 0, wk, i, width, c);
-    }
-
-    // ---- combine: whoever completes a token's contributions for this row tile adds them up ----
-    __threadfence();
-    __syncthreads();
-    const int expected = p.top_k + (p.nrows_shared > 0 ? 1 : 0);
-    if (tid < m) {
-        int* ctr = p.combine_ctr + (size_t)s_tok[tid] * p.n_row_tiles + blockIdx.x;
-        const int c = atomicAdd(ctr, 1);
-        s_done[tid] = (c == expected - 1);
-        if (c == expected - 1) *ctr = 0;
-    }
-    __syncthreads();
-    __threadfence();
-    const int k = p.top_k;
-    for (int i = 0; i < m; ++i) {
-        if (!s_done[i]) continue;
-        const int t = s_tok[i];
-        for (int r = tid; r < rows_here; r += kThreadsT) {
-            const int h = r0 + r;
-            float sum = 0.0f;   // weighted_combine_kernel (chimere_kernels.cu:1551-1565): slots ascending
-            for (int j = 0; j < k; ++j)
-                sum = fmaf(p.topk_w[(size_t)t * k + j], __ldcg(p.pair_out + ((size_t)t * k + j) * H + h), sum);
-            if (p.nrows_shared > 0) {  // sigmoid_gate_add_kernel (scratch_pool.rs:266-277)
-                const float sh = __ldcg(p.pair_out + ((size_t)p.T * k + t) * H + h);
-                if (p.sh_gate_logit) sum = fmaf(sh, sigmoid_ref(__ldcg(p.sh_gate_logit + t)), sum);
-                else sum = sh + sum;
+    if (warp == kConsumerWarps) {
+        // ================================ producer ================================
+        if (lane != 0) return;
+        int slab_seq = 0;
+        for (int it = it0; it < it1; ++it) {
+            const bool shared = it >= items_r;
+            const int rel = shared ? it - items_r : it;
+            const int tiles_e = shared ? tiles_s : tiles_r;
+            const int eidx = (shared ? n_routed : 0) + rel / tiles_e, item_tile = rel % tiles_e;
+            const int* ent = p.group_list + kListHeader + 4 * eidx;
+            const int expert = __ldcg(ent), start = __ldcg(ent + 1), m = __ldcg(ent + 2);
+            const int ncols = shared ? ncols_s : ncols_r, nrows = shared ? nrows_s : nrows_r;
+            const int tb = (int)Tiled<TYPE>::tile_bytes(ncols);
+            const SlabPlan sp = slab_plan(tb, Tiled<TYPE>::kGroupBytes, wr);
+            const int tiles_total = nrows / 32, tile0 = item_tile * wr;
+            const int ntiles_here = min(wr, tiles_total - tile0);
+            // activations + meta of this item
+            const int ab = (it - it0) & 1, aphase = ((it - it0) >> 1) & 1;
+            if (!mbar_wait(aempty + ab, aphase ^ 1)) { atomicOr(p.status, kStatusWaitTimeout); return; }
+            int* mt = meta + ab * 64;
+            mt[kMetaM] = m; mt[kMetaTile0] = tile0; mt[kMetaNTilesTotal] = tiles_total; mt[kMetaShared] = shared ? 1 : 0;
+            mt[kMetaValid] = ntiles_here;
+            const uint32_t row_bytes = (uint32_t)(((ncols / 32) * kQ81Bytes + 15) & ~15);   // used part of the Q8_1 row, 16-byte granules
+            int irow[kMaxGroupTokens];
+            for (int i = 0; i < m; ++i) {
+                int t, prow;
+                if (shared) { t = start + i; prow = p.T * p.top_k + t; }
+                else { prow = __ldcg(p.perm + start + i); t = prow / p.top_k; }
+                mt[kMetaOutRow + i] = prow; mt[kMetaTok + i] = t;
+                irow[i] = (STAGE == kStageGateUp) ? t : prow;
             }
-            p.y[(size_t)t * H + h] = sum;
+            mbar_expect_tx(afull + ab, (uint32_t)m * row_bytes);   // releases the meta words written above
+            for (int i = 0; i < m; ++i)
+                bulk_g2s(actbuf + (size_t)(ab * kMaxGroupTokens + i) * act_row_bytes, p.in_q8 + (size_t)irow[i] * p.in_stride,
+                         row_bytes, afull + ab);
+            // weight slabs: matrix A (up / down) first, then B (gate)
+            for (int mat = 0; mat < n_mats; ++mat) {
+                const uint8_t* wbase = (mat == 0) ? (shared ? (STAGE == kStageGateUp ? p.sh_b : p.sh_a)
+                                                            : (STAGE == kStageGateUp ? p.w_b + (size_t)expert * p.stride_b
+                                                                                     : p.w_a + (size_t)expert * p.stride_a))
+                                                  : (shared ? p.sh_a : p.w_a + (size_t)expert * p.stride_a);
+                const uint8_t* item_base = wbase + (size_t)tile0 * tb;
+                for (int si = 0; si < sp.slabs_per_mat; ++si) {
+                    size_t off; uint32_t bytes;
+                    if (sp.whole_tiles) {
+                        const int t0 = si * sp.per, nt = min(sp.per, ntiles_here - t0);
+                        off = (size_t)t0 * tb; bytes = nt > 0 ? (uint32_t)nt * tb : 0u;
+                    } else {
+                        const int g0 = si * sp.per;
+                        off = (size_t)g0 * sp.group_bytes;
+                        bytes = (uint32_t)min((int64_t)sp.per * sp.group_bytes, (int64_t)tb - (int64_t)off);
+                    }
+                    const int st = slab_seq % nst, ph = (slab_seq / nst) & 1;
+                    if (!mbar_wait(empty + st, ph ^ 1)) { atomicOr(p.status, kStatusWaitTimeout); return; }
+                    if (bytes > 0) {
+                        mbar_expect_tx(full + st, bytes);
+                        bulk_g2s(ring + (size_t)st * kSlabMax, item_base + off, bytes, full + st);
+                    } else {
+                        mbar_arrive(full + st);
+                    }
+                    ++slab_seq;
+                }
+            }
         }
+        return;
+    }
+
+    // ================================ consumers ================================
+    const int wr_id = warp / wk, wk_id = warp - wr_id * wk;
+    const int width = 32 * wr;
+    int slab_seq = 0;
+    for (int it = it0; it < it1; ++it) {
+        const int ab = (it - it0) & 1, aphase = ((it - it0) >> 1) & 1;
+        if (!mbar_wait(afull + ab, aphase)) { atomicOr(p.status, kStatusWaitTimeout); return; }
+        const int* mt = meta + ab * 64;
+        const int m = mt[kMetaM], tile0 = mt[kMetaTile0], tiles_total = mt[kMetaNTilesTotal];
+        const bool shared = mt[kMetaShared] != 0;
+        const int ncols = shared ? ncols_s : ncols_r, nb = ncols >> 5;
+        const SlabPlan sp = slab_plan((int)Tiled<TYPE>::tile_bytes(ncols), Tiled<TYPE>::kGroupBytes, wr);
+        const uint8_t* act = actbuf + (size_t)ab * kMaxGroupTokens * act_row_bytes;
+        const bool tile_valid = tile0 + wr_id < tiles_total;
+        float aa[kMaxGroupTokens], ab_[kMaxGroupTokens];
+#pragma unroll
+        for (int i = 0; i < kMaxGroupTokens; ++i) { aa[i] = 0.0f; ab_[i] = 0.0f; }
+        for (int mat = 0; mat < n_mats; ++mat) {
+            for (int si = 0; si < sp.slabs_per_mat; ++si) {
+                const int st = slab_seq % nst, ph = (slab_seq / nst) & 1;
+                if (!mbar_wait(full + st, ph)) { atomicOr(p.status, kStatusWaitTimeout); return; }
+                const uint8_t* stage = ring + (size_t)st * kSlabMax;
+                float (&acc)[kMaxGroupTokens] = (mat == 0) ? aa : ab_;
+                if (m == 1) {
+                    float a1[1] = {acc[0]};
+                    consume_slab<TYPE, 1>(stage, sp, si, wr_id, wk_id, wk, wr, lane, nb, tile_valid, act, act_row_bytes, m, a1);
+                    acc[0] = a1[0];
+                } else if (m == 2) {
+                    float a2[2] = {acc[0], acc[1]};
+                    consume_slab<TYPE, 2>(stage, sp, si, wr_id, wk_id, wk, wr, lane, nb, tile_valid, act, act_row_bytes, m, a2);
+                    acc[0] = a2[0]; acc[1] = a2[1];
+                } else {
+                    consume_slab<TYPE, kMaxGroupTokens>(stage, sp, si, wr_id, wk_id, wk, wr, lane, nb, tile_valid, act, act_row_bytes, m, acc);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty + st);
+                ++slab_seq;
+            }
+        }
+        // partial sums of this warp's K slice
+#pragma unroll
+        for (int i = 0; i < kMaxGroupTokens; ++i) {
+            if (i < m) {
+                red[((0 * wk + wk_id) * kMaxGroupTokens + i) * width + wr_id * 32 + lane] = aa[i];
+                if (DUAL) red[((1 * wk + wk_id) * kMaxGroupTokens + i) * width + wr_id * 32 + lane] = ab_[i];
+            }
+        }
+        consumer_sync();
+
+        if (STAGE == kStageGateUp) {
+            // (token, row tile): sum the K slices, activation, Q8_1 of the 32 results (lane = element)
+            for (int pr = warp; pr < m * wr; pr += kConsumerWarps) {
+                const int i = pr / wr, wq = pr - i * wr;
+                if (tile0 + wq >= tiles_total) continue;
+                const float u = sum_slices(red, 0, wk, i, width, wq * 32 + lane);
+                float v;
+                if (DUAL) v = silu_mul_ref(sum_slices(red, 1, wk, i, width, wq * 32 + lane), u);
+                else { const float r = fmaxf(u, 0.0f); v = r * r; }
+                float amax = fabsf(v), sum = v;
+#pragma unroll
+                for (int s = 16; s > 0; s >>= 1) {
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+                    sum += __shfl_xor_sync(0xffffffffu, sum, s);
+                }
+                const float d = amax / 127.0f;
+                const int8_t q = (amax == 0.0f) ? (int8_t)0 : (int8_t)roundf(v / d);
+                uint8_t* out = p.inter_q8 + (size_t)mt[kMetaOutRow + i] * p.inter_stride + (size_t)(tile0 + wq) * kQ81Bytes;
+                reinterpret_cast<int8_t*>(out)[4 + lane] = q;
+                if (lane == 0) *reinterpret_cast<__half2*>(out) = __halves2half2(__float2half(d), __float2half(sum));
+            }
+        } else {
+            const int H = p.H, r0 = tile0 * 32, rows_here = min(width, H - r0);
+            const int ctid = tid;  // 0..255 among consumers
+            for (int e = ctid; e < m * width; e += 256) {
+                const int i = e / width, c = e - i * width;
+                if (c < rows_here) p.pair_out[(size_t)mt[kMetaOutRow + i] * H + r0 + c] = sum_slices(red, 0, wk, i, width, c);
+            }
+            // whoever completes a token's contributions for this row tile adds them up
+            __threadfence();
+            consumer_sync();
+            int* done = reinterpret_cast<int*>(red);   // red is free now: reuse 8 words as flags
+            const int expected = p.top_k + (p.nrows_shared > 0 ? 1 : 0);
+            const int row_tile = tile0 / wr;
+            consumer_sync();
+            if (ctid < m) {
+                int* ctr = p.combine_ctr + (size_t)mt[kMetaTok + ctid] * p.n_row_tiles + row_tile;
+                const int c = atomicAdd(ctr, 1);
+                done[ctid] = (c == expected - 1);
+                if (c == expected - 1) *ctr = 0;
+            }
+            consumer_sync();
+            __threadfence();
+            const int k = p.top_k;
+            for (int i = 0; i < m; ++i) {
+                if (!done[i]) continue;
+                const int t = mt[kMetaTok + i];
+                for (int r = ctid; r < rows_here; r += 256) {
+                    const int h = r0 + r;
+                    float sum = 0.0f;   // weighted_combine_kernel (chimere_kernels.cu:1551-1565): slots ascending
+                    for (int j = 0; j < k; ++j)
+                        sum = fmaf(p.topk_w[(size_t)t * k + j], __ldcg(p.pair_out + ((size_t)t * k + j) * H + h), sum);
+                    if (p.nrows_shared > 0) {  // sigmoid_gate_add_kernel (scratch_pool.rs:266-277)
+                        const float sh = __ldcg(p.pair_out + ((size_t)p.T * k + t) * H + h);
+                        if (p.sh_gate_logit) sum = fmaf(sh, sigmoid_ref(__ldcg(p.sh_gate_logit + t)), sum);
+                        else sum = sh + sum;
+                    }
+                    p.y[(size_t)t * H + h] = sum;
+                }
+            }
+        }
+        consumer_sync();   // red, meta and the activation buffer are free again
+        if (lane == 0) mbar_arrive(aempty + ab);
     }
 }
 
@@ -274,77 +362,80 @@ static int ngroups_of(int type, int ncols) {
     const int gu = (type == CHIMERE_TYPE_Q8_0) ? 4 : 8;
     return (nb + gu - 1) / gu;
 }
+static StreamGeom geom_for(int ngroups_min) {
+    int wk = 8;
+    while (wk > 1 && wk > ngroups_min) wk >>= 1;
+    return StreamGeom{wk, 8 / wk};
+}
+static int64_t host_tile_bytes(int type, int ncols) { return tiled_matrix_bytes(type, 32, ncols); }
 
 TiledGeomHost tiled_gate_up_geom(int type_routed, int type_shared, int H, bool has_shared) {
     int g = ngroups_of(type_routed, H);
     if (has_shared) g = min(g, ngroups_of(type_shared, H));
-    const TiledGeom t = tiled_geom(g);
+    StreamGeom t = geom_for(g);
+    // a tile too large for one ring stage is cut along K, which needs one row tile per CTA
+    if (host_tile_bytes(type_routed, H) > kSlabMax || (has_shared && host_tile_bytes(type_shared, H) > kSlabMax)) t = StreamGeom{8, 1};
     return TiledGeomHost{t.wk, t.wr};
 }
 TiledGeomHost tiled_down_geom(int type_routed, int F, int type_shared, int F_s) {
     int g = ngroups_of(type_routed, F);
     if (F_s > 0) g = min(g, ngroups_of(type_shared, F_s));
-    const TiledGeom t = tiled_geom(g);
+    StreamGeom t = geom_for(g);
+    if (host_tile_bytes(type_routed, F) > kSlabMax || (F_s > 0 && host_tile_bytes(type_shared, F_s) > kSlabMax)) t = StreamGeom{8, 1};
     return TiledGeomHost{t.wk, t.wr};
 }
 
-template <int TYPE, bool DUAL>
-static cudaError_t launch_gate_up_tiled_t(const GemvParams& p, int max_entries, int wk, int wr, cudaStream_t stream) {
-    const size_t smem = tiled_smem(p.H, wr, wk, DUAL).total;
-    if (smem > 200 * 1024) return cudaErrorInvalidValue;
-    cudaError_t e = cudaFuncSetAttribute(gate_up_tiled_kernel<TYPE, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+static int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int TYPE, int STAGE, bool DUAL>
+static cudaError_t launch_stream_t(const GemvParams& p, int wk, int wr, cudaStream_t stream) {
+    const StreamSmem ss = stream_smem((int)p.in_stride, wr, wk, DUAL);
+    if (ss.nst < 2) return cudaErrorInvalidValue;
+    cudaError_t e = cudaFuncSetAttribute(stream_kernel<TYPE, STAGE, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
     if (e != cudaSuccess) return e;
-    const int tiles = (max(p.nrows_routed, p.nrows_shared) + 32 * wr - 1) / (32 * wr);
-    gate_up_tiled_kernel<TYPE, DUAL><<<dim3(tiles, max_entries), kThreadsT, smem, stream>>>(p, wk, wr);
+    stream_kernel<TYPE, STAGE, DUAL><<<sm_count(), kStreamThreads, ss.total, stream>>>(p, wk, wr);
     return cudaGetLastError();
 }
 
-static cudaError_t dispatch_gate_up_tiled(int type, const GemvParams& p, int max_entries, int wk, int wr, cudaStream_t stream) {
-    const bool dual = p.act == CHIMERE_ACT_SWIGLU;
+template <int STAGE>
+static cudaError_t dispatch_stream(int type, const GemvParams& p, int wk, int wr, cudaStream_t stream) {
+    const bool dual = STAGE == kStageGateUp && p.act == CHIMERE_ACT_SWIGLU;
     switch (type) {
-        case CHIMERE_TYPE_Q4_0: return dual ? launch_gate_up_tiled_t<CHIMERE_TYPE_Q4_0, true>(p, max_entries, wk, wr, stream)
-                                            : launch_gate_up_tiled_t<CHIMERE_TYPE_Q4_0, false>(p, max_entries, wk, wr, stream);
-        case CHIMERE_TYPE_Q8_0: return dual ? launch_gate_up_tiled_t<CHIMERE_TYPE_Q8_0, true>(p, max_entries, wk, wr, stream)
-                                            : launch_gate_up_tiled_t<CHIMERE_TYPE_Q8_0, false>(p, max_entries, wk, wr, stream);
-        case CHIMERE_TYPE_IQ3_S: return dual ? launch_gate_up_tiled_t<CHIMERE_TYPE_IQ3_S, true>(p, max_entries, wk, wr, stream)
-                                             : launch_gate_up_tiled_t<CHIMERE_TYPE_IQ3_S, false>(p, max_entries, wk, wr, stream);
+        case CHIMERE_TYPE_Q4_0: return dual ? launch_stream_t<CHIMERE_TYPE_Q4_0, STAGE, true>(p, wk, wr, stream)
+                                            : launch_stream_t<CHIMERE_TYPE_Q4_0, STAGE, false>(p, wk, wr, stream);
+        case CHIMERE_TYPE_Q8_0: return dual ? launch_stream_t<CHIMERE_TYPE_Q8_0, STAGE, true>(p, wk, wr, stream)
+                                            : launch_stream_t<CHIMERE_TYPE_Q8_0, STAGE, false>(p, wk, wr, stream);
+        case CHIMERE_TYPE_IQ3_S: return dual ? launch_stream_t<CHIMERE_TYPE_IQ3_S, STAGE, true>(p, wk, wr, stream)
+                                             : launch_stream_t<CHIMERE_TYPE_IQ3_S, STAGE, false>(p, wk, wr, stream);
         default: return cudaErrorInvalidValue;
     }
 }
 
 cudaError_t launch_gate_up_tiled(const GemvParams& p, int max_entries, cudaStream_t stream) {
+    (void)max_entries;
     const TiledGeomHost g = tiled_gate_up_geom(p.type_routed, p.type_shared, p.H, p.nrows_shared > 0);
-    cudaError_t e = dispatch_gate_up_tiled(p.type_routed, p, max_entries, g.wk, g.wr, stream);
+    cudaError_t e = dispatch_stream<kStageGateUp>(p.type_routed, p, g.wk, g.wr, stream);
     if (e == cudaSuccess && p.nrows_shared > 0 && p.type_shared != p.type_routed)
-        e = dispatch_gate_up_tiled(p.type_shared, p, max_entries, g.wk, g.wr, stream);
+        e = dispatch_stream<kStageGateUp>(p.type_shared, p, g.wk, g.wr, stream);
     return e;
-}
-
-template <int TYPE>
-static cudaError_t launch_down_tiled_t(const GemvParams& p, int max_entries, int wk, int wr, cudaStream_t stream) {
-    const size_t smem = tiled_smem(max(p.ncols_routed, p.ncols_shared), wr, wk, false).total;
-    if (smem > 200 * 1024) return cudaErrorInvalidValue;
-    cudaError_t e = cudaFuncSetAttribute(down_tiled_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) return e;
-    down_tiled_kernel<TYPE><<<dim3(p.n_row_tiles, max_entries), kThreadsT, smem, stream>>>(p, wk, wr);
-    return cudaGetLastError();
-}
-
-static cudaError_t dispatch_down_tiled(int type, const GemvParams& p, int max_entries, int wk, int wr, cudaStream_t stream) {
-    switch (type) {
-        case CHIMERE_TYPE_Q4_0: return launch_down_tiled_t<CHIMERE_TYPE_Q4_0>(p, max_entries, wk, wr, stream);
-        case CHIMERE_TYPE_Q8_0: return launch_down_tiled_t<CHIMERE_TYPE_Q8_0>(p, max_entries, wk, wr, stream);
-        case CHIMERE_TYPE_IQ3_S: return launch_down_tiled_t<CHIMERE_TYPE_IQ3_S>(p, max_entries, wk, wr, stream);
-        default: return cudaErrorInvalidValue;
-    }
 }
 
 // p.n_row_tiles must be ceil(H / (32 * wr)) with the geometry of tiled_down_geom
 cudaError_t launch_down_tiled(const GemvParams& p, int max_entries, cudaStream_t stream) {
+    (void)max_entries;
     const TiledGeomHost g = tiled_down_geom(p.type_routed, p.ncols_routed, p.type_shared, p.nrows_shared > 0 ? p.ncols_shared : 0);
-    cudaError_t e = dispatch_down_tiled(p.type_routed, p, max_entries, g.wk, g.wr, stream);
+    cudaError_t e = dispatch_stream<kStageDown>(p.type_routed, p, g.wk, g.wr, stream);
     if (e == cudaSuccess && p.nrows_shared > 0 && p.type_shared != p.type_routed)
-        e = dispatch_down_tiled(p.type_shared, p, max_entries, g.wk, g.wr, stream);
+        e = dispatch_stream<kStageDown>(p.type_shared, p, g.wk, g.wr, stream);
     return e;
 }
 

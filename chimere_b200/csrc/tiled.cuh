@@ -26,21 +26,18 @@
 
 namespace chimere {
 
-__device__ __forceinline__ uint4 ldg128(const uint8_t* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint32_t ldg_u16(const uint8_t* p) { return __ldg(reinterpret_cast<const uint16_t*>(p)); }
-__device__ __forceinline__ uint32_t ldg_u32(const uint8_t* p) { return __ldg(reinterpret_cast<const uint32_t*>(p)); }
+// The decode helpers read through plain pointers: global memory in the parity tap, the
+// shared-memory ring in the GEMV kernels (the compiler resolves the address space).
+__device__ __forceinline__ uint4 ldg128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ uint32_t ldg_u16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }
+__device__ __forceinline__ uint32_t ldg_u32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
 
 // A "group" is kGroupUnits consecutive units of the 32 rows of a tile: what one lane keeps in
 // flight at a time (kGroupUnits x kVec 128-bit loads).
 template <int TYPE> struct Tiled;
 
 template <> struct Tiled<CHIMERE_TYPE_Q4_0> {
-    static constexpr int kGroupUnits = 8, kVec = 1, kUnitBytes = 576;
+    static constexpr int kGroupUnits = 8, kVec = 1, kUnitBytes = 576, kGroupBytes = 8 * 576;
     struct Regs { uint4 v[8]; uint32_t d[8]; };
     __host__ __device__ static int64_t tile_bytes(int ncols) { return (int64_t)(ncols / 32) * kUnitBytes; }
     __device__ static __forceinline__ void load(const uint8_t* tile, int grp, int lane, int nu, Regs& r) {
@@ -86,7 +83,7 @@ template <> struct Tiled<CHIMERE_TYPE_IQ3_S> {
 };
 
 template <> struct Tiled<CHIMERE_TYPE_Q8_0> {
-    static constexpr int kGroupUnits = 4, kVec = 2, kUnitBytes = 1088;
+    static constexpr int kGroupUnits = 4, kVec = 2, kUnitBytes = 1088, kGroupBytes = 4 * 1088;
     struct Regs { uint4 v[8]; uint32_t d[4]; };
     __host__ __device__ static int64_t tile_bytes(int ncols) { return (int64_t)(ncols / 32) * kUnitBytes; }
     __device__ static __forceinline__ void load(const uint8_t* tile, int grp, int lane, int nu, Regs& r) {

@@ -174,7 +174,7 @@ class MoeScratch:
 
     def inter_q8(self, T: int) -> torch.Tensor:
         """[T*k + T, Fmax/32*36]: rows t*k+j = routed slot j of token t, rows T*k+t = shared expert."""
-        rb = max(self.w.F, self.w.F_s) // 32 * 36
+        rb = (max(self.w.F, self.w.F_s) // 32 * 36 + 15) & ~15   # rows start on 16-byte boundaries
         n = T * self.w.top_k + (T if self.w.F_s > 0 else 0)
         return self._view(self.ws.inter_q8, n * rb).reshape(n, rb)
 

@@ -94,7 +94,7 @@ typedef struct chimere_moe_workspace {
     int32_t* offsets;       /* [E+1] start of each expert's pairs in perm */
     int32_t* group_list;    /* work list of the grouped GEMV kernels, built on the device */
     int32_t* counters;      /* small integer scratch; zero between calls */
-    uint8_t* inter_q8;      /* [(T*top_k + T)][F_max/32] Q8_1 blocks of the activated intermediates */
+    uint8_t* inter_q8;      /* [(T*top_k + T)] rows of F_max/32 Q8_1 blocks (row stride rounded up to 16 B) */
     float*   pair_out;      /* [(T*top_k + T)][H] down-projection rows before the combine */
     void*    prefill_arena; /* staging for the grouped int8 GEMM path */
     size_t   prefill_bytes;
