@@ -39,6 +39,7 @@ class MoeWorkspace(C.Structure):
         ("topk_idx", C.c_void_p), ("topk_w", C.c_void_p), ("router_logits", C.c_void_p),
         ("sh_gate_logit", C.c_void_p), ("x_q8", C.c_void_p), ("perm", C.c_void_p), ("offsets", C.c_void_p),
         ("group_list", C.c_void_p), ("counters", C.c_void_p), ("inter_q8", C.c_void_p), ("pair_out", C.c_void_p),
+        ("x_q", C.c_void_p), ("x_d", C.c_void_p), ("inter_q", C.c_void_p), ("inter_d", C.c_void_p),
         ("prefill_arena", C.c_void_p), ("prefill_bytes", C.c_size_t), ("status", C.c_void_p),
     ]
 

@@ -46,6 +46,8 @@ int validate_layer(const chimere_moe_layer* w) {
 
 struct Layout {
     size_t topk_idx, topk_w, logits, sh_logit, x_q8, perm, offsets, group_list, counters, inter_q8, pair_out, status, total;
+    size_t x_q, x_d, inter_q, inter_d;
+    int x_d_stride, inter_d_stride, Fmax;
     int max_entries, n_row_tiles, tile_rows, n_counters;
     int n_row_tiles_tiled;
     size_t inter_stride;
@@ -81,6 +83,13 @@ Layout make_layout(const chimere_moe_layer* w, int T) {
     L.counters = o; o += up256((size_t)L.n_counters * 4);
     L.inter_q8 = o; o += up256(pairs * L.inter_stride);
     L.pair_out = o; o += up256(pairs * H * 4);
+    L.Fmax = Fmax;
+    L.x_d_stride = (H / 32 + 3) & ~3;
+    L.inter_d_stride = (Fmax / 32 + 3) & ~3;
+    L.x_q = o; o += up256((size_t)T * H);
+    L.x_d = o; o += up256((size_t)T * L.x_d_stride * 4);
+    L.inter_q = o; o += up256(pairs * Fmax);
+    L.inter_d = o; o += up256(pairs * L.inter_d_stride * 4);
     L.status = o; o += 256;
     L.total = o;
     return L;
@@ -123,6 +132,10 @@ int chimere_b200_moe_workspace_init(chimere_moe_workspace* ws, void* d_arena, si
     ws->counters = (int32_t*)(base + L.counters);
     ws->inter_q8 = base + L.inter_q8;
     ws->pair_out = (float*)(base + L.pair_out);
+    ws->x_q = (int8_t*)(base + L.x_q);
+    ws->x_d = (float*)(base + L.x_d);
+    ws->inter_q = (int8_t*)(base + L.inter_q);
+    ws->inter_d = (float*)(base + L.inter_d);
     ws->status = (int32_t*)(base + L.status);
     cudaError_t e = cudaMemsetAsync(ws->counters, 0, (size_t)L.n_counters * 4, stream);
     if (e == cudaSuccess) e = cudaMemsetAsync(ws->status, 0, 256, stream);
@@ -140,6 +153,7 @@ static RouteParams route_params(const chimere_moe_layer* w, const float* d_x, in
     p.router_logits = ws->router_logits; p.sh_gate_logit = ws->sh_gate_logit;
     p.topk_idx = ws->topk_idx; p.topk_w = ws->topk_w; p.x_q8 = ws->x_q8;
     p.perm = ws->perm; p.offsets = ws->offsets; p.group_list = ws->group_list; p.counters = ws->counters;
+    p.x_soa_q = ws->x_q; p.x_soa_d = ws->x_d; p.x_soa_d_stride = (w->H / 32 + 3) & ~3;
     return p;
 }
 
@@ -171,6 +185,7 @@ static GemvParams gate_up_params(const chimere_moe_layer* w, int T, chimere_moe_
     g.act = w->act;
     g.group_list = ws->group_list; g.perm = ws->perm;
     g.status = ws->status;
+    g.queue = ws->counters + kCtrQueue;
     g.ncols_routed = w->H; g.ncols_shared = w->H;
     g.nrows_routed = w->F; g.nrows_shared = w->F_s;
     g.type_routed = w->type_up; g.type_shared = w->type_sh_up;
@@ -179,6 +194,8 @@ static GemvParams gate_up_params(const chimere_moe_layer* w, int T, chimere_moe_
     g.sh_a = (const uint8_t*)w->sh_gate; g.sh_b = (const uint8_t*)w->sh_up;
     g.in_q8 = ws->x_q8; g.in_stride = (int64_t)(w->H / 32) * kQ81Bytes;
     g.inter_q8 = ws->inter_q8; g.inter_stride = (int64_t)L.inter_stride;
+    g.in_soa_q = ws->x_q; g.in_soa_q_stride = w->H; g.in_soa_d = ws->x_d; g.in_soa_d_stride = L.x_d_stride;
+    g.out_soa_q = ws->inter_q; g.out_soa_q_stride = L.Fmax; g.out_soa_d = ws->inter_d; g.out_soa_d_stride = L.inter_d_stride;
     return g;
 }
 
@@ -188,12 +205,14 @@ static GemvParams down_params(const chimere_moe_layer* w, float* d_y, int T, chi
     g.act = w->act;
     g.group_list = ws->group_list; g.perm = ws->perm;
     g.status = ws->status;
+    g.queue = ws->counters + kCtrQueue;
     g.ncols_routed = w->F; g.ncols_shared = w->F_s;
     g.nrows_routed = w->H; g.nrows_shared = w->F_s > 0 ? w->H : 0;
     g.type_routed = w->type_down; g.type_shared = w->type_sh_down;
     g.w_a = (const uint8_t*)w->down_exps; g.stride_a = w->stride_down;
     g.sh_a = (const uint8_t*)w->sh_down;
     g.in_q8 = ws->inter_q8; g.in_stride = (int64_t)L.inter_stride;
+    g.in_soa_q = ws->inter_q; g.in_soa_q_stride = L.Fmax; g.in_soa_d = ws->inter_d; g.in_soa_d_stride = L.inter_d_stride;
     g.pair_out = ws->pair_out; g.topk_w = ws->topk_w;
     g.sh_gate_logit = (w->F_s > 0 && w->shexp_gate_w) ? ws->sh_gate_logit : nullptr;
     g.y = d_y;

@@ -24,7 +24,7 @@
 
 namespace chimere {
 
-constexpr int kConsumerWarps = 8;
+constexpr int kConsumerWarps = 16;
 constexpr int kStreamThreads = 32 * (kConsumerWarps + 1);  // + one producer warp
 constexpr int kSlabMax = 36 * 1024 + 1024;                  // bytes of one weight stage
 constexpr int kStageGateUp = 0, kStageDown = 1;
@@ -32,73 +32,78 @@ constexpr int kStageGateUp = 0, kStageDown = 1;
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
 // How an item's weights are cut into slabs (identical on the host, in the producer and in the consumers).
 struct SlabPlan {
-    int tile_bytes, group_bytes, ngroups;
-    int whole_tiles;       // 1: a slab is `per` whole tiles; 0: a slab is `per` groups of the single tile (wr == 1)
+    int tile_bytes, chunk_bytes, groups_per_chunk, ngroups;
+    int whole_tiles;       // 1: a slab is `per` whole tiles; 0: a slab is `per` chunks of the single tile (wr == 1)
     int per, slabs_per_mat;
 };
-__host__ __device__ inline SlabPlan slab_plan(int tile_bytes, int group_bytes, int wr) {
+__host__ __device__ inline SlabPlan slab_plan(int tile_bytes, int chunk_bytes, int groups_per_chunk, int nb, int wr) {
     SlabPlan s;
-    s.tile_bytes = tile_bytes; s.group_bytes = group_bytes;
-    s.ngroups = (tile_bytes + group_bytes - 1) / group_bytes;
+    s.tile_bytes = tile_bytes; s.chunk_bytes = chunk_bytes; s.groups_per_chunk = groups_per_chunk;
+    s.ngroups = (nb + kGroupUnits - 1) / kGroupUnits;
     if (tile_bytes <= kSlabMax) {
         s.whole_tiles = 1;
         s.per = kSlabMax / tile_bytes; if (s.per > wr) s.per = wr;
         s.slabs_per_mat = (wr + s.per - 1) / s.per;
     } else {
         s.whole_tiles = 0;
-        s.per = kSlabMax / group_bytes;
-        s.slabs_per_mat = (s.ngroups + s.per - 1) / s.per;
+        s.per = kSlabMax / chunk_bytes;
+        const int nchunks = (tile_bytes + chunk_bytes - 1) / chunk_bytes;
+        s.slabs_per_mat = (nchunks + s.per - 1) / s.per;
     }
     return s;
 }
 
-struct StreamSmem { uint32_t bars, meta, red, act, ring, total; int nst; };
-// bars: full[nst] empty[nst] afull[2] aempty[2]; meta: 2 x 64 ints; red; act: 2 buffers; ring: nst stages
-__host__ __device__ inline StreamSmem stream_smem(int act_row_bytes, int wr, int wk, bool dual) {
+struct StreamSmem { uint32_t bars, meta, red, act, ring, total; int nst; uint32_t act_q_row, act_d_row, act_buf; };
+// bars: full[nst] empty[nst] afull[2] aempty[2]; meta: 2 x 64 ints; red; act: 2 buffers of 8 x (int8 row + f32 scale row)
+__host__ __device__ inline StreamSmem stream_smem(int ncols_max, int wr, int wk, bool dual) {
     StreamSmem s;
     uint32_t o = 0;
     s.bars = o; o += 256;
     s.meta = o; o += 2 * 64 * 4;
     s.red = o; o += (uint32_t)(dual ? 2 : 1) * wk * kMaxGroupTokens * 32 * wr * 4;
     o = (o + 127u) & ~127u;
-    s.act = o; o += 2u * kMaxGroupTokens * (uint32_t)act_row_bytes;
+    s.act_q_row = (uint32_t)ncols_max;
+    s.act_d_row = ((uint32_t)(ncols_max / 32) * 4 + 15u) & ~15u;
+    s.act_buf = kMaxGroupTokens * (s.act_q_row + s.act_d_row);
+    s.act = o; o += 2u * s.act_buf;
     o = (o + 127u) & ~127u;
     s.ring = o;
     int nst = (int)((220u * 1024u - o) / kSlabMax);
     if (nst > 6) nst = 6;
     s.nst = nst;
-    s.total = o + (uint32_t)nst * kSlabMax;
+    s.total = o + (uint32_t)(nst > 0 ? nst : 0) * kSlabMax;
     return s;
 }
 
 // acc[i] += sum over the units of one group of (scale_w * scale_x) * integer block dot, for up to M tokens.
-// Activations: Q8_1 rows in shared memory, row i at act + i * act_stride.
+// Activations in shared memory: int8 plane aq[i][qrow], f32 scale plane ad[i][drow / 4].
 template <int TYPE, int M>
-__device__ __forceinline__ void group_dot(const uint8_t* tile, int grp, int lane, int nu, const uint8_t* act, int act_stride,
-                                          int m, float (&acc)[M]) {
+__device__ __forceinline__ void group_dot(const uint8_t* tile, int grp, int lane, int nu, const uint8_t* aq, int qrow,
+                                          const float* ad, int drow_f, int m, float (&acc)[kMaxGroupTokens]) {
     using TT = Tiled<TYPE>;
     typename TT::Regs r;
     TT::load(tile, grp, lane, nu, r);
 #pragma unroll
-    for (int u = 0; u < TT::kGroupUnits; ++u) {
+    for (int u = 0; u < kGroupUnits; ++u) {
         if (u < nu) {
             int w[8];
             TT::decode(r, u, w);
             const float dw = TT::dscale(r, u);
-            const int b = grp * TT::kGroupUnits + u;
+            const int b = grp * kGroupUnits + u;
 #pragma unroll
             for (int i = 0; i < M; ++i) {
-                if (i < m) {
-                    const uint32_t* q = reinterpret_cast<const uint32_t*>(act + (size_t)i * act_stride + b * kQ81Bytes);
-                    int s = __dp4a(w[0], (int)q[1], 0);
-                    s = __dp4a(w[1], (int)q[2], s); s = __dp4a(w[2], (int)q[3], s); s = __dp4a(w[3], (int)q[4], s);
-                    s = __dp4a(w[4], (int)q[5], s); s = __dp4a(w[5], (int)q[6], s); s = __dp4a(w[6], (int)q[7], s);
-                    s = __dp4a(w[7], (int)q[8], s);
-                    acc[i] = fmaf(dw * h2f(q[0] & 0xFFFFu), (float)TT::finish(s, r, u), acc[i]);
+                if (M == 1 || i < m) {
+                    const int4* q = reinterpret_cast<const int4*>(aq + (size_t)i * qrow + b * 32);
+                    const int4 q0 = q[0], q1 = q[1];
+                    int s0 = __dp4a(w[0], q0.x, 0), s1 = __dp4a(w[4], q1.x, 0);   // two independent chains
+                    s0 = __dp4a(w[1], q0.y, s0); s1 = __dp4a(w[5], q1.y, s1);
+                    s0 = __dp4a(w[2], q0.z, s0); s1 = __dp4a(w[6], q1.z, s1);
+                    s0 = __dp4a(w[3], q0.w, s0); s1 = __dp4a(w[7], q1.w, s1);
+                    acc[i] = fmaf(dw * ad[i * drow_f + b], (float)TT::finish(s0 + s1, r, u, 0), acc[i]);
                 }
             }
         }
@@ -109,9 +114,8 @@ struct StreamGeom { int wk, wr; };
 
 template <int TYPE, int M>
 __device__ __forceinline__ void consume_slab(const uint8_t* stage, const SlabPlan& sp, int si, int wr_id, int wk_id, int wk,
-                                             int wr, int lane, int nb, bool row_tile_valid, const uint8_t* act, int act_stride,
-                                             int m, float (&acc)[M]) {
-    using TT = Tiled<TYPE>;
+                                             int wr, int lane, int nb, bool row_tile_valid, const uint8_t* aq, int qrow,
+                                             const float* ad, int drow_f, int m, float (&acc)[kMaxGroupTokens]) {
     if (!row_tile_valid) return;
     const uint8_t* tile;
     int g0, g1;
@@ -122,12 +126,12 @@ __device__ __forceinline__ void consume_slab(const uint8_t* stage, const SlabPla
         g0 = 0; g1 = sp.ngroups;
     } else {
         if (wr_id != 0) return;
-        g0 = si * sp.per; g1 = min(sp.ngroups, g0 + sp.per);
-        tile = stage - (size_t)g0 * sp.group_bytes;
+        g0 = si * sp.per * sp.groups_per_chunk; g1 = min(sp.ngroups, g0 + sp.per * sp.groups_per_chunk);
+        tile = stage - (size_t)(si * sp.per) * sp.chunk_bytes;
     }
     for (int g = g0 + wk_id; g < g1; g += wk) {
-        const int nu = min(TT::kGroupUnits, nb - g * TT::kGroupUnits);
-        group_dot<TYPE, M>(tile, g, lane, nu, act, act_stride, m, acc);
+        const int nu = min(kGroupUnits, nb - g * kGroupUnits);
+        group_dot<TYPE, M>(tile, g, lane, nu, aq, qrow, ad, drow_f, m, acc);
     }
 }
 
@@ -149,8 +153,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_kernel(const GemvPar
     const int nrows_r = p.nrows_routed, nrows_s = p.nrows_shared;
     const bool do_r = p.type_routed == TYPE, do_s = nrows_s > 0 && p.type_shared == TYPE;
     const int tiles_r = (nrows_r / 32 + wr - 1) / wr, tiles_s = nrows_s > 0 ? (nrows_s / 32 + wr - 1) / wr : 0;  // items per entry
-    const int act_row_bytes = (int)p.in_stride;
-    const StreamSmem ss = stream_smem(act_row_bytes, wr, wk, DUAL);
+    const StreamSmem ss = stream_smem(max(ncols_r, ncols_s), wr, wk, DUAL);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + ss.bars);
     uint64_t* empty = full + ss.nst;
     uint64_t* afull = empty + ss.nst;
@@ -171,32 +174,42 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_kernel(const GemvPar
     const int n_routed = __ldcg(p.group_list + 1), n_shared = __ldcg(p.group_list + 2);
     const int items_r = do_r ? n_routed * tiles_r : 0, items_s = do_s ? n_shared * tiles_s : 0;
     const int total = items_r + items_s;
-    const int it0 = (int)(((int64_t)blockIdx.x * total) / gridDim.x), it1 = (int)(((int64_t)(blockIdx.x + 1) * total) / gridDim.x);
     const int n_mats = DUAL ? 2 : 1;
+    // Items are handed out through a device-wide queue, the heavy ones (shared expert: every token) first.
+    int* queue = p.queue + (STAGE == kStageGateUp ? 0 : 2);   // [0] next item, [1] CTAs finished
 
     if (warp == kConsumerWarps) {
         // ================================ producer ================================
         if (lane != 0) return;
         int slab_seq = 0;
-        for (int it = it0; it < it1; ++it) {
-            const bool shared = it >= items_r;
-            const int rel = shared ? it - items_r : it;
+        for (int n = 0;; ++n) {
+            const int it = atomicAdd(queue, 1);
+            const int ab = n & 1, aphase = (n >> 1) & 1;
+            if (it >= total) {
+                // end marker for the consumers, then the last CTA to get here re-arms the queue
+                if (!mbar_wait(aempty + ab, aphase ^ 1)) { atomicOr(p.status, kStatusWaitTimeout); return; }
+                meta[ab * 64 + kMetaM] = -1;
+                mbar_arrive(afull + ab);
+                if (atomicAdd(queue + 1, 1) == (int)gridDim.x - 1) { queue[1] = 0; __threadfence(); queue[0] = 0; }
+                return;
+            }
+            const bool shared = it < items_s;
+            const int rel = shared ? it : it - items_s;
             const int tiles_e = shared ? tiles_s : tiles_r;
             const int eidx = (shared ? n_routed : 0) + rel / tiles_e, item_tile = rel % tiles_e;
             const int* ent = p.group_list + kListHeader + 4 * eidx;
             const int expert = __ldcg(ent), start = __ldcg(ent + 1), m = __ldcg(ent + 2);
             const int ncols = shared ? ncols_s : ncols_r, nrows = shared ? nrows_s : nrows_r;
             const int tb = (int)Tiled<TYPE>::tile_bytes(ncols);
-            const SlabPlan sp = slab_plan(tb, Tiled<TYPE>::kGroupBytes, wr);
+            const SlabPlan sp = slab_plan(tb, Tiled<TYPE>::kChunkBytes, Tiled<TYPE>::kGroupsPerChunk, ncols / 32, wr);
             const int tiles_total = nrows / 32, tile0 = item_tile * wr;
             const int ntiles_here = min(wr, tiles_total - tile0);
             // activations + meta of this item
-            const int ab = (it - it0) & 1, aphase = ((it - it0) >> 1) & 1;
             if (!mbar_wait(aempty + ab, aphase ^ 1)) { atomicOr(p.status, kStatusWaitTimeout); return; }
             int* mt = meta + ab * 64;
             mt[kMetaM] = m; mt[kMetaTile0] = tile0; mt[kMetaNTilesTotal] = tiles_total; mt[kMetaShared] = shared ? 1 : 0;
             mt[kMetaValid] = ntiles_here;
-            const uint32_t row_bytes = (uint32_t)(((ncols / 32) * kQ81Bytes + 15) & ~15);   // used part of the Q8_1 row, 16-byte granules
+            const uint32_t qbytes = (uint32_t)ncols, dbytes = ((uint32_t)(ncols / 32) * 4u + 15u) & ~15u;
             int irow[kMaxGroupTokens];
             for (int i = 0; i < m; ++i) {
                 int t, prow;
@@ -205,10 +218,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_kernel(const GemvPar
                 mt[kMetaOutRow + i] = prow; mt[kMetaTok + i] = t;
                 irow[i] = (STAGE == kStageGateUp) ? t : prow;
             }
-            mbar_expect_tx(afull + ab, (uint32_t)m * row_bytes);   // releases the meta words written above
-            for (int i = 0; i < m; ++i)
-                bulk_g2s(actbuf + (size_t)(ab * kMaxGroupTokens + i) * act_row_bytes, p.in_q8 + (size_t)irow[i] * p.in_stride,
-                         row_bytes, afull + ab);
+            mbar_expect_tx(afull + ab, (uint32_t)m * (qbytes + dbytes));   // releases the meta words written above
+            uint8_t* abuf = actbuf + (size_t)ab * ss.act_buf;
+            for (int i = 0; i < m; ++i) {
+                bulk_g2s(abuf + (size_t)i * ss.act_q_row, p.in_soa_q + (size_t)irow[i] * p.in_soa_q_stride, qbytes, afull + ab);
+                bulk_g2s(abuf + kMaxGroupTokens * ss.act_q_row + (size_t)i * ss.act_d_row,
+                         p.in_soa_d + (size_t)irow[i] * p.in_soa_d_stride, dbytes, afull + ab);
+            }
             // weight slabs: matrix A (up / down) first, then B (gate)
             for (int mat = 0; mat < n_mats; ++mat) {
                 const uint8_t* wbase = (mat == 0) ? (shared ? (STAGE == kStageGateUp ? p.sh_b : p.sh_a)
@@ -222,9 +238,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_kernel(const GemvPar
                         const int t0 = si * sp.per, nt = min(sp.per, ntiles_here - t0);
                         off = (size_t)t0 * tb; bytes = nt > 0 ? (uint32_t)nt * tb : 0u;
                     } else {
-                        const int g0 = si * sp.per;
-                        off = (size_t)g0 * sp.group_bytes;
-                        bytes = (uint32_t)min((int64_t)sp.per * sp.group_bytes, (int64_t)tb - (int64_t)off);
+                        off = (size_t)(si * sp.per) * sp.chunk_bytes;
+                        bytes = (uint32_t)min((int64_t)sp.per * sp.chunk_bytes, (int64_t)tb - (int64_t)off);
                     }
                     const int st = slab_seq % nst, ph = (slab_seq / nst) & 1;
                     if (!mbar_wait(empty + st, ph ^ 1)) { atomicOr(p.status, kStatusWaitTimeout); return; }
@@ -238,22 +253,24 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_kernel(const GemvPar
                 }
             }
         }
-        return;
     }
 
     // ================================ consumers ================================
     const int wr_id = warp / wk, wk_id = warp - wr_id * wk;
     const int width = 32 * wr;
     int slab_seq = 0;
-    for (int it = it0; it < it1; ++it) {
-        const int ab = (it - it0) & 1, aphase = ((it - it0) >> 1) & 1;
+    for (int n = 0;; ++n) {
+        const int ab = n & 1, aphase = (n >> 1) & 1;
         if (!mbar_wait(afull + ab, aphase)) { atomicOr(p.status, kStatusWaitTimeout); return; }
         const int* mt = meta + ab * 64;
         const int m = mt[kMetaM], tile0 = mt[kMetaTile0], tiles_total = mt[kMetaNTilesTotal];
+        if (m < 0) return;
         const bool shared = mt[kMetaShared] != 0;
         const int ncols = shared ? ncols_s : ncols_r, nb = ncols >> 5;
-        const SlabPlan sp = slab_plan((int)Tiled<TYPE>::tile_bytes(ncols), Tiled<TYPE>::kGroupBytes, wr);
-        const uint8_t* act = actbuf + (size_t)ab * kMaxGroupTokens * act_row_bytes;
+        const SlabPlan sp = slab_plan((int)Tiled<TYPE>::tile_bytes(ncols), Tiled<TYPE>::kChunkBytes, Tiled<TYPE>::kGroupsPerChunk, nb, wr);
+        const uint8_t* aq = actbuf + (size_t)ab * ss.act_buf;
+        const float* ad = reinterpret_cast<const float*>(aq + kMaxGroupTokens * ss.act_q_row);
+        const int qrow = (int)ss.act_q_row, drow_f = (int)(ss.act_d_row / 4);
         const bool tile_valid = tile0 + wr_id < tiles_total;
         float aa[kMaxGroupTokens], ab_[kMaxGroupTokens];
 #pragma unroll
@@ -263,18 +280,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_kernel(const GemvPar
                 const int st = slab_seq % nst, ph = (slab_seq / nst) & 1;
                 if (!mbar_wait(full + st, ph)) { atomicOr(p.status, kStatusWaitTimeout); return; }
                 const uint8_t* stage = ring + (size_t)st * kSlabMax;
-                float (&acc)[kMaxGroupTokens] = (mat == 0) ? aa : ab_;
-                if (m == 1) {
-                    float a1[1] = {acc[0]};
-                    consume_slab<TYPE, 1>(stage, sp, si, wr_id, wk_id, wk, wr, lane, nb, tile_valid, act, act_row_bytes, m, a1);
-                    acc[0] = a1[0];
-                } else if (m == 2) {
-                    float a2[2] = {acc[0], acc[1]};
-                    consume_slab<TYPE, 2>(stage, sp, si, wr_id, wk_id, wk, wr, lane, nb, tile_valid, act, act_row_bytes, m, a2);
-                    acc[0] = a2[0]; acc[1] = a2[1];
+#define CHIMERE_CONSUME(MM, ACC) consume_slab<TYPE, MM>(stage, sp, si, wr_id, wk_id, wk, wr, lane, nb, tile_valid, aq, qrow, ad, drow_f, m, ACC)
+                if (mat == 0) {
+                    if (m == 1) CHIMERE_CONSUME(1, aa); else if (m == 2) CHIMERE_CONSUME(2, aa); else CHIMERE_CONSUME(kMaxGroupTokens, aa);
                 } else {
-                    consume_slab<TYPE, kMaxGroupTokens>(stage, sp, si, wr_id, wk_id, wk, wr, lane, nb, tile_valid, act, act_row_bytes, m, acc);
+                    if (m == 1) CHIMERE_CONSUME(1, ab_); else if (m == 2) CHIMERE_CONSUME(2, ab_); else CHIMERE_CONSUME(kMaxGroupTokens, ab_);
                 }
+#undef CHIMERE_CONSUME
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty + st);
                 ++slab_seq;
@@ -309,12 +321,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_kernel(const GemvPar
                 const int8_t q = (amax == 0.0f) ? (int8_t)0 : (int8_t)roundf(v / d);
                 uint8_t* out = p.inter_q8 + (size_t)mt[kMetaOutRow + i] * p.inter_stride + (size_t)(tile0 + wq) * kQ81Bytes;
                 reinterpret_cast<int8_t*>(out)[4 + lane] = q;
-                if (lane == 0) *reinterpret_cast<__half2*>(out) = __halves2half2(__float2half(d), __float2half(sum));
+                const __half dh = __float2half(d);
+                if (lane == 0) *reinterpret_cast<__half2*>(out) = __halves2half2(dh, __float2half(sum));
+                // the same block as planes, the form the down stage streams
+                p.out_soa_q[(size_t)mt[kMetaOutRow + i] * p.out_soa_q_stride + (size_t)(tile0 + wq) * 32 + lane] = q;
+                if (lane == 0) p.out_soa_d[(size_t)mt[kMetaOutRow + i] * p.out_soa_d_stride + (tile0 + wq)] = __half2float(dh);
             }
         } else {
             const int H = p.H, r0 = tile0 * 32, rows_here = min(width, H - r0);
-            const int ctid = tid;  // 0..255 among consumers
-            for (int e = ctid; e < m * width; e += 256) {
+            const int ctid = tid;  // 0..511 among consumers
+            for (int e = ctid; e < m * width; e += 32 * kConsumerWarps) {
                 const int i = e / width, c = e - i * width;
                 if (c < rows_here) p.pair_out[(size_t)mt[kMetaOutRow + i] * H + r0 + c] = sum_slices(red, 0, wk, i, width, c);
             }
@@ -337,7 +353,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_kernel(const GemvPar
             for (int i = 0; i < m; ++i) {
                 if (!done[i]) continue;
                 const int t = mt[kMetaTok + i];
-                for (int r = ctid; r < rows_here; r += 256) {
+                for (int r = ctid; r < rows_here; r += 32 * kConsumerWarps) {
                     const int h = r0 + r;
                     float sum = 0.0f;   // weighted_combine_kernel (chimere_kernels.cu:1551-1565): slots ascending
                     for (int j = 0; j < k; ++j)
@@ -358,14 +374,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_kernel(const GemvPar
 
 // ------------------------------------------------------------------ launchers --------------
 static int ngroups_of(int type, int ncols) {
-    const int nb = ncols / 32;
-    const int gu = (type == CHIMERE_TYPE_Q8_0) ? 4 : 8;
-    return (nb + gu - 1) / gu;
+    (void)type;
+    return (ncols / 32 + kGroupUnits - 1) / kGroupUnits;
 }
 static StreamGeom geom_for(int ngroups_min) {
-    int wk = 8;
+    int wk = kConsumerWarps;
     while (wk > 1 && wk > ngroups_min) wk >>= 1;
-    return StreamGeom{wk, 8 / wk};
+    return StreamGeom{wk, kConsumerWarps / wk};
 }
 static int64_t host_tile_bytes(int type, int ncols) { return tiled_matrix_bytes(type, 32, ncols); }
 
@@ -374,14 +389,14 @@ TiledGeomHost tiled_gate_up_geom(int type_routed, int type_shared, int H, bool h
     if (has_shared) g = min(g, ngroups_of(type_shared, H));
     StreamGeom t = geom_for(g);
     // a tile too large for one ring stage is cut along K, which needs one row tile per CTA
-    if (host_tile_bytes(type_routed, H) > kSlabMax || (has_shared && host_tile_bytes(type_shared, H) > kSlabMax)) t = StreamGeom{8, 1};
+    if (host_tile_bytes(type_routed, H) > kSlabMax || (has_shared && host_tile_bytes(type_shared, H) > kSlabMax)) t = StreamGeom{kConsumerWarps, 1};
     return TiledGeomHost{t.wk, t.wr};
 }
 TiledGeomHost tiled_down_geom(int type_routed, int F, int type_shared, int F_s) {
     int g = ngroups_of(type_routed, F);
     if (F_s > 0) g = min(g, ngroups_of(type_shared, F_s));
     StreamGeom t = geom_for(g);
-    if (host_tile_bytes(type_routed, F) > kSlabMax || (F_s > 0 && host_tile_bytes(type_shared, F_s) > kSlabMax)) t = StreamGeom{8, 1};
+    if (host_tile_bytes(type_routed, F) > kSlabMax || (F_s > 0 && host_tile_bytes(type_shared, F_s) > kSlabMax)) t = StreamGeom{kConsumerWarps, 1};
     return TiledGeomHost{t.wk, t.wr};
 }
 
@@ -398,7 +413,7 @@ static int sm_count() {
 
 template <int TYPE, int STAGE, bool DUAL>
 static cudaError_t launch_stream_t(const GemvParams& p, int wk, int wr, cudaStream_t stream) {
-    const StreamSmem ss = stream_smem((int)p.in_stride, wr, wk, DUAL);
+    const StreamSmem ss = stream_smem(max(p.ncols_routed, p.ncols_shared), wr, wk, DUAL);
     if (ss.nst < 2) return cudaErrorInvalidValue;
     cudaError_t e = cudaFuncSetAttribute(stream_kernel<TYPE, STAGE, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
     if (e != cudaSuccess) return e;

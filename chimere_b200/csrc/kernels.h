@@ -7,6 +7,7 @@ namespace chimere {
 
 // layout of the workspace's integer scratch ("counters"); everything returns to zero after a call
 constexpr int kCtrRouteAll = 0;    // token tiles whose top-k is done
+constexpr int kCtrQueue = 4;       // [4] work queues of the streaming kernels
 constexpr int kCtrRouteTile = 16;  // [ceil(max_T/8)] row tiles done per token tile
 // the combine counters follow at ws-specific offset (one per token and output row tile)
 
@@ -22,6 +23,9 @@ struct RouteParams {
     int32_t* topk_idx;          // [T][k]
     float* topk_w;              // [T][k]
     uint8_t* x_q8;              // [T][H/32][36]
+    int8_t* x_soa_q;            // [T][H] the same quants as a plane
+    float* x_soa_d;             // [T][x_soa_d_stride] the same scales (f16-rounded) as f32
+    int x_soa_d_stride;
     int32_t* perm;              // [T*k]
     int32_t* offsets;           // [E+1]
     int32_t* group_list;
@@ -57,6 +61,12 @@ struct GemvParams {
     int32_t* combine_ctr;        // [T][row tiles]
     int tile_rows;               // down stage: output rows per CTA (multiple of 8, <= 64)
     int n_row_tiles;             // down stage: ceil(H / tile_rows)
+    // tiled path: the same Q8_1 rows as planes (int8 values / f32 scales), input and gate-up output
+    const int8_t* in_soa_q; int64_t in_soa_q_stride;   // bytes per row
+    const float* in_soa_d; int64_t in_soa_d_stride;     // floats per row
+    int8_t* out_soa_q; int64_t out_soa_q_stride;
+    float* out_soa_d; int64_t out_soa_d_stride;
+    int32_t* queue;              // streaming kernels: [0..1] gate/up work queue, [2..3] down work queue (zero between calls)
     int32_t* status;
 };
 

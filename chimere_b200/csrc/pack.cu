@@ -86,24 +86,24 @@ template <int TYPE>
 __global__ void block_sumi_tiled_kernel(const uint8_t* packed, const uint8_t* xq8, int32_t* out, int ncols, int nrows) {
     using TT = Tiled<TYPE>;
     const int nb = ncols >> 5;
-    const int ngroups = (nb + TT::kGroupUnits - 1) / TT::kGroupUnits;
+    const int ngroups = (nb + kGroupUnits - 1) / kGroupUnits;
     const int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;  // one warp per (tile, group)
     const int lane = threadIdx.x & 31;
     if (gw >= (int64_t)(nrows / 32) * ngroups) return;
     const int tile = (int)(gw / ngroups), grp = (int)(gw % ngroups);
-    const int nu = min(TT::kGroupUnits, nb - grp * TT::kGroupUnits);
+    const int nu = min(kGroupUnits, nb - grp * kGroupUnits);
     typename TT::Regs r;
     TT::load(packed + (size_t)tile * TT::tile_bytes(ncols), grp, lane, nu, r);
 #pragma unroll
-    for (int u = 0; u < TT::kGroupUnits; ++u) {
+    for (int u = 0; u < kGroupUnits; ++u) {
         if (u < nu) {
             int w[8];
             TT::decode(r, u, w);
-            const int b = grp * TT::kGroupUnits + u;
+            const int b = grp * kGroupUnits + u;
             int s = 0;
 #pragma unroll
             for (int g = 0; g < 8; ++g) s = __dp4a(w[g], *reinterpret_cast<const int*>(xq8 + (size_t)b * kQ81Bytes + 4 + 4 * g), s);
-            out[(size_t)(tile * 32 + lane) * nb + b] = TT::finish(s, r, u);
+            out[(size_t)(tile * 32 + lane) * nb + b] = TT::finish(s, r, u, 0);
         }
     }
 }
@@ -113,7 +113,7 @@ cudaError_t launch_block_sumi_tiled(int type, const void* packed, const void* xq
     const int nb = ncols / 32;
     auto run = [&](auto tag) {
         constexpr int TYPE = decltype(tag)::value;
-        const int ngroups = (nb + Tiled<TYPE>::kGroupUnits - 1) / Tiled<TYPE>::kGroupUnits;
+        const int ngroups = (nb + kGroupUnits - 1) / kGroupUnits;
         const int64_t warps = (int64_t)(nrows / 32) * ngroups;
         if (warps > 0)
             block_sumi_tiled_kernel<TYPE><<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>((const uint8_t*)packed, (const uint8_t*)xq8, sumi, ncols, nrows);

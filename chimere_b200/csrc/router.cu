@@ -29,7 +29,7 @@ __device__ __forceinline__ float tree256(const float* r, int lane) {
 }
 
 // Q8_1 of one 32-float block by one warp; lane = element.
-__device__ __forceinline__ void quantize_block_q8_1(float xi, uint8_t* out, int lane) {
+__device__ __forceinline__ void quantize_block_q8_1(float xi, uint8_t* out, int lane, int8_t* plane_q, float* plane_d) {
     float amax = fabsf(xi), sum = xi;
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) {
@@ -39,9 +39,11 @@ __device__ __forceinline__ void quantize_block_q8_1(float xi, uint8_t* out, int 
     const float d = amax / 127.0f;
     const int8_t q = (amax == 0.0f) ? (int8_t)0 : (int8_t)roundf(xi / d);
     reinterpret_cast<int8_t*>(out)[4 + lane] = q;
-    if (lane == 0) {
-        *reinterpret_cast<__half2*>(out) = __halves2half2(__float2half(d), __float2half(sum));
-    }
+    const __half dh = __float2half(d);
+    if (lane == 0) *reinterpret_cast<__half2*>(out) = __halves2half2(dh, __float2half(sum));
+    // the same block as planes (what the tiled GEMV kernels stream)
+    plane_q[lane] = q;
+    if (lane == 0) *plane_d = __half2float(dh);
 }
 
 // One token's scores -> top-k, by one warp.  Lane l owns experts l, l+32, ...
@@ -217,7 +219,8 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
         for (int q = blockIdx.x * 8 + warp; q < nt * nbH; q += n_rtiles * 8) {
             const int tt = q / nbH, b = q - tt * nbH;
             const float xi = p.x[(size_t)(t0 + tt) * H + b * 32 + lane];
-            quantize_block_q8_1(xi, p.x_q8 + ((size_t)(t0 + tt) * nbH + b) * kQ81Bytes, lane);
+            quantize_block_q8_1(xi, p.x_q8 + ((size_t)(t0 + tt) * nbH + b) * kQ81Bytes, lane,
+                                p.x_soa_q + (size_t)(t0 + tt) * H + b * 32, p.x_soa_d + (size_t)(t0 + tt) * p.x_soa_d_stride + b);
         }
     }
 

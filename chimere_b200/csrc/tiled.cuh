@@ -32,13 +32,16 @@ __device__ __forceinline__ uint4 ldg128(const uint8_t* p) { return *reinterpret_
 __device__ __forceinline__ uint32_t ldg_u16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }
 __device__ __forceinline__ uint32_t ldg_u32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
 
-// A "group" is kGroupUnits consecutive units of the 32 rows of a tile: what one lane keeps in
-// flight at a time (kGroupUnits x kVec 128-bit loads).
+// A "group" is kGroupUnits = 4 consecutive units of the 32 rows of a tile: what one lane decodes
+// at a time.  kChunkBytes is the smallest contiguous piece a tile may be cut into when it is
+// streamed in slabs (an IQ3_S super-block keeps its scales behind its eight units).
+constexpr int kGroupUnits = 4;
+
 template <int TYPE> struct Tiled;
 
 template <> struct Tiled<CHIMERE_TYPE_Q4_0> {
-    static constexpr int kGroupUnits = 8, kVec = 1, kUnitBytes = 576, kGroupBytes = 8 * 576;
-    struct Regs { uint4 v[8]; uint32_t d[8]; };
+    static constexpr int kUnitBytes = 576, kChunkBytes = 4 * 576, kGroupsPerChunk = 1;
+    struct Regs { uint4 v[4]; uint32_t d[4]; };
     __host__ __device__ static int64_t tile_bytes(int ncols) { return (int64_t)(ncols / 32) * kUnitBytes; }
     __device__ static __forceinline__ void load(const uint8_t* tile, int grp, int lane, int nu, Regs& r) {
         const uint8_t* g = tile + (size_t)grp * (kGroupUnits * kUnitBytes);
@@ -51,21 +54,22 @@ template <> struct Tiled<CHIMERE_TYPE_Q4_0> {
 #pragma unroll
         for (int j = 0; j < 4; ++j) { w[j] = (int)((x[j] << 4) & 0xF0F0F0F0u); w[4 + j] = (int)(x[j] & 0xF0F0F0F0u); }
     }
-    __device__ static __forceinline__ int finish(int s, const Regs&, int) { return s >> 4; }
+    __device__ static __forceinline__ int finish(int s, const Regs&, int, int) { return s >> 4; }
     __device__ static __forceinline__ float dscale(const Regs& r, int u) { return h2f(r.d[u]); }
 };
 
 template <> struct Tiled<CHIMERE_TYPE_IQ3_S> {
-    static constexpr int kGroupUnits = 8, kVec = 1, kGroupBytes = 4288;
-    struct Regs { uint4 v[8]; uint32_t d; uint32_t sc; };
-    __host__ __device__ static int64_t tile_bytes(int ncols) { return (int64_t)(ncols / 256) * kGroupBytes; }
+    static constexpr int kSuperBytes = 4288, kChunkBytes = 4288, kGroupsPerChunk = 2;
+    struct Regs { uint4 v[4]; uint32_t d; uint32_t sc; };
+    __host__ __device__ static int64_t tile_bytes(int ncols) { return (int64_t)(ncols / 256) * kSuperBytes; }
     __device__ static __forceinline__ void load(const uint8_t* tile, int grp, int lane, int nu, Regs& r) {
-        const uint8_t* g = tile + (size_t)grp * kGroupBytes;
+        const uint8_t* g = tile + (size_t)(grp >> 1) * kSuperBytes;
+        const int u0 = (grp & 1) * 4;
 #pragma unroll
         for (int u = 0; u < kGroupUnits; ++u)
-            if (u < nu) r.v[u] = ldg128(g + u * 512 + lane * 16);
+            if (u < nu) r.v[u] = ldg128(g + (u0 + u) * 512 + lane * 16);
         r.d = ldg_u16(g + 4096 + lane * 2);
-        r.sc = ldg_u32(g + 4160 + lane * 4);
+        r.sc = ldg_u32(g + 4160 + lane * 4) >> (16 * (grp & 1));   // this half's four scale nibbles
     }
     __device__ static __forceinline__ void decode(const Regs& r, int u, int (&w)[8]) {
         const uint32_t x[4] = {r.v[u].x, r.v[u].y, r.v[u].z, r.v[u].w};
@@ -76,14 +80,14 @@ template <> struct Tiled<CHIMERE_TYPE_IQ3_S> {
         }
     }
     // dp4a result = 8 * sum(+-magnitude * q); times the sub-block factor 1 + 2*scale (chimere_kernels.cu:860)
-    __device__ static __forceinline__ int finish(int s, const Regs& r, int u) {
+    __device__ static __forceinline__ int finish(int s, const Regs& r, int u, int) {
         return (s >> 3) * (int)(1u + 2u * ((r.sc >> (4 * u)) & 15u));
     }
     __device__ static __forceinline__ float dscale(const Regs& r, int) { return h2f(r.d); }
 };
 
 template <> struct Tiled<CHIMERE_TYPE_Q8_0> {
-    static constexpr int kGroupUnits = 4, kVec = 2, kUnitBytes = 1088, kGroupBytes = 4 * 1088;
+    static constexpr int kUnitBytes = 1088, kChunkBytes = 4 * 1088, kGroupsPerChunk = 1;
     struct Regs { uint4 v[8]; uint32_t d[4]; };
     __host__ __device__ static int64_t tile_bytes(int ncols) { return (int64_t)(ncols / 32) * kUnitBytes; }
     __device__ static __forceinline__ void load(const uint8_t* tile, int grp, int lane, int nu, Regs& r) {
@@ -100,7 +104,7 @@ template <> struct Tiled<CHIMERE_TYPE_Q8_0> {
         w[0] = (int)r.v[2 * u].x; w[1] = (int)r.v[2 * u].y; w[2] = (int)r.v[2 * u].z; w[3] = (int)r.v[2 * u].w;
         w[4] = (int)r.v[2 * u + 1].x; w[5] = (int)r.v[2 * u + 1].y; w[6] = (int)r.v[2 * u + 1].z; w[7] = (int)r.v[2 * u + 1].w;
     }
-    __device__ static __forceinline__ int finish(int s, const Regs&, int) { return s; }
+    __device__ static __forceinline__ int finish(int s, const Regs&, int, int) { return s; }
     __device__ static __forceinline__ float dscale(const Regs& r, int u) { return h2f(r.d[u]); }
 };
 

@@ -96,6 +96,10 @@ typedef struct chimere_moe_workspace {
     int32_t* counters;      /* small integer scratch; zero between calls */
     uint8_t* inter_q8;      /* [(T*top_k + T)] rows of F_max/32 Q8_1 blocks (row stride rounded up to 16 B) */
     float*   pair_out;      /* [(T*top_k + T)][H] down-projection rows before the combine */
+    int8_t*  x_q;           /* [T][H] the quants of x_q8 as a plane */
+    float*   x_d;           /* [T][ceil4(H/32)] the scales of x_q8 (f16-rounded) as f32 */
+    int8_t*  inter_q;       /* [(T*top_k + T)][F_max] the quants of inter_q8 as a plane */
+    float*   inter_d;       /* [(T*top_k + T)][ceil4(F_max/32)] the scales of inter_q8 as f32 */
     void*    prefill_arena; /* staging for the grouped int8 GEMM path */
     size_t   prefill_bytes;
     int32_t* status;        /* device status word: 0 = ok */

@@ -42,7 +42,7 @@ def test_constants(lib):
 
 def test_struct_sizes():
     assert C.sizeof(abi.MoeLayer) == 160
-    assert C.sizeof(abi.MoeWorkspace) == 8 + 14 * 8
+    assert C.sizeof(abi.MoeWorkspace) == 8 + 18 * 8
 
 
 def _layer(**kw):
