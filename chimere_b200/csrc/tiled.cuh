@@ -26,11 +26,26 @@
 
 namespace chimere {
 
-// The decode helpers read through plain pointers: global memory in the parity tap, the
-// shared-memory ring in the GEMV kernels (the compiler resolves the address space).
-__device__ __forceinline__ uint4 ldg128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
-__device__ __forceinline__ uint32_t ldg_u16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }
-__device__ __forceinline__ uint32_t ldg_u32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
+// Weight loads: read-only, streamed once, so they bypass L1 allocation.
+__device__ __forceinline__ uint4 ldg128(const uint8_t* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_u16(const uint8_t* p) { return __ldg(reinterpret_cast<const uint16_t*>(p)); }
+__device__ __forceinline__ uint32_t ldg_u32(const uint8_t* p) { return __ldg(reinterpret_cast<const uint32_t*>(p)); }
+__device__ __forceinline__ void prefetch_l2(const uint8_t* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+// Shared-memory loads by 32-bit shared address.
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
 
 // A "group" is kGroupUnits = 4 consecutive units of the 32 rows of a tile: what one lane decodes
 // at a time.  kChunkBytes is the smallest contiguous piece a tile may be cut into when it is
