@@ -55,7 +55,7 @@ struct Layout {
 
 int max_entries_for(const chimere_moe_layer* w, int T) {
     const int P = T * w->top_k;
-    return (w->E < P ? w->E : P) + P / kMaxGroupTokens + (w->F_s > 0 ? (T + kMaxGroupTokens - 1) / kMaxGroupTokens : 0);
+    return (w->E < P ? w->E : P) + P / kMaxGroupTokens + (w->F_s > 0 ? (T + kSharedGroupTokens - 1) / kSharedGroupTokens : 0);
 }
 
 Layout make_layout(const chimere_moe_layer* w, int T) {

@@ -14,6 +14,7 @@ namespace chimere {
 
 constexpr int kQ81Bytes = 36;
 constexpr int kMaxGroupTokens = 8;   // tokens one GEMV work entry carries
+constexpr int kSharedGroupTokens = 2;  // ... for the shared expert (every token uses it): smaller entries balance the grid
 constexpr int kMaxTopK = 8;
 constexpr int kMaxExperts = 256;
 

@@ -162,12 +162,12 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i) {
         ent[3] = 0;
     }
     // shared-expert entries: all tokens, identity order
-    const int nsh = p.has_shared ? (p.T + kMaxGroupTokens - 1) / kMaxGroupTokens : 0;
+    const int nsh = p.has_shared ? (p.T + kSharedGroupTokens - 1) / kSharedGroupTokens : 0;
     for (int i = tid; i < nsh; i += 256) {
         int* ent = p.group_list + kListHeader + 4 * (total_routed + i);
         ent[0] = -1;
-        ent[1] = i * kMaxGroupTokens;
-        ent[2] = min(kMaxGroupTokens, p.T - i * kMaxGroupTokens);
+        ent[1] = i * kSharedGroupTokens;
+        ent[2] = min(kSharedGroupTokens, p.T - i * kSharedGroupTokens);
         ent[3] = 0;
     }
     if (tid == 0) {
