@@ -59,6 +59,7 @@ PROTOTYPES = {
     "chimere_b200_moe_forward": (C.c_int, [_LAYER_P, _P, _P, C.c_int, _WS_P, _P]),
     "chimere_b200_moe_forward_host": (C.c_int, [_LAYER_P, _P, _P, C.c_int, _P, _P, _WS_P, _P]),
     "chimere_b200_moe_route": (C.c_int, [_LAYER_P, _P, C.c_int, _WS_P, _P]),
+    "chimere_b200_moe_route_noalloc": (C.c_int, [_LAYER_P, _P, C.c_int, _P, _P, _P]),
     "chimere_b200_moe_gate_up": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P]),
     "chimere_b200_moe_down_combine": (C.c_int, [_LAYER_P, _P, C.c_int, _WS_P, _P]),
     "chimere_b200_moe_permute": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P]),
@@ -98,7 +99,7 @@ def load() -> C.CDLL:
 
 
 ERRORS = {-1: "null pointer", -2: "bad dimension", -3: "unsupported weight type", -4: "workspace too small",
-          -5: "misaligned arena", -6: "entry not available"}
+          -5: "misaligned arena", -6: "entry not available", -7: "larger than the built-in scratch"}
 
 
 def check(rc: int, what: str) -> None:

@@ -315,3 +315,86 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
 }
 
 }  // namespace chimere
+
+// ------------------------------------------------------------------------------------------
+// Routing without any allocation by anyone: chimere_b200_moe_route_noalloc.
+//
+// Some hosts of this library cannot hand it scratch memory.  A serving process that gave all device
+// memory to its own pool at start-up (the reference's server sizes every buffer once, at model
+// load), or a caller already inside a region where cudaMalloc is not permitted, has the token rows
+// and somewhere to put the routing result, but no spare arena and no way to get one.  For them the
+// routing step's scratch lives in the library image itself: one fixed array per GPU, reserved when
+// the library is loaded on that GPU and held until the process ends.
+//
+// In host code the array's name is only a handle, not a device address, so the address is looked
+// up once per device with cudaGetSymbolAddress (with that device current) and cached.  The first
+// call on a device does this look-up; make that first call outside any stream capture.
+// Every call on a device shares the one array: calls that overlap on the GPU (two streams, two
+// threads) race.  Nothing here calls cudaMalloc, cudaFree or a library routine that allocates.
+namespace chimere {
+
+constexpr int kNoAllocMaxT = 64;        // tokens per call
+constexpr int kNoAllocMaxH = 4096;      // hidden size
+constexpr size_t kNoAllocCounters = 0;                                                        // 1 KiB of integer scratch
+constexpr size_t kNoAllocLogits = 1024;                                                       // [T][256] f32
+constexpr size_t kNoAllocShLogit = kNoAllocLogits + (size_t)kNoAllocMaxT * kMaxExperts * 4;   // [T] f32
+constexpr size_t kNoAllocXq8 = kNoAllocShLogit + 256;                                         // [T][H/32][36]
+constexpr size_t kNoAllocXq = kNoAllocXq8 + (size_t)kNoAllocMaxT * (kNoAllocMaxH / 32) * kQ81Bytes;
+constexpr size_t kNoAllocXd = kNoAllocXq + (size_t)kNoAllocMaxT * kNoAllocMaxH;               // [T][H/32] f32
+constexpr size_t kNoAllocPerm = kNoAllocXd + (size_t)kNoAllocMaxT * (kNoAllocMaxH / 32) * 4;  // [T*8] i32
+constexpr size_t kNoAllocOffsets = kNoAllocPerm + (size_t)kNoAllocMaxT * kMaxTopK * 4;        // [257] i32
+constexpr size_t kNoAllocList = kNoAllocOffsets + 1280;                                       // work list
+constexpr size_t kNoAllocBytes = kNoAllocList + (size_t)(kListHeader + 4 * (kMaxExperts + kNoAllocMaxT * kMaxTopK + kNoAllocMaxT)) * 4 + 256;
+
+static __device__ __align__(256) unsigned char g_route_scratch[kNoAllocBytes];   // ~680 KiB per GPU
+
+}  // namespace chimere
+
+extern "C" int chimere_b200_moe_route_noalloc(const chimere_moe_layer* w, const float* d_x, int T, int32_t* d_topk_idx,
+                                              float* d_topk_w, cudaStream_t stream) {
+    using namespace chimere;
+    if (!w || !d_x || !d_topk_idx || !d_topk_w || !w->router_w) return -1;
+    if (w->H <= 0 || w->H % 32 || w->E <= 0 || w->E > kMaxExperts || w->top_k <= 0 || w->top_k > kMaxTopK || w->top_k > w->E) return -2;
+    if (w->route_mode != CHIMERE_ROUTE_SOFTMAX_RENORM && w->route_mode != CHIMERE_ROUTE_SIGMOID_NORM_SCALE) return -2;
+    if (T <= 0) return -2;
+    if (T > kNoAllocMaxT || w->H > kNoAllocMaxH) return -7;   // larger than the built-in scratch: use chimere_b200_moe_route
+
+    // once per device, with that device current: the array's device address
+    static unsigned char* s_base[64] = {nullptr};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return -100 - (int)e;
+    if (dev < 0 || dev >= 64) return -2;
+    if (!s_base[dev]) {
+        unsigned char* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_route_scratch);
+        if (e != cudaSuccess || !ptr) return -100 - (int)e;
+        s_base[dev] = ptr;
+    }
+    unsigned char* base = s_base[dev];
+
+    // the integer scratch must start at zero; everything else is fully rewritten by the kernel
+    e = cudaMemsetAsync(base + kNoAllocCounters, 0, 1024, stream);
+    if (e != cudaSuccess) return -100 - (int)e;
+
+    RouteParams p{};
+    p.T = T; p.H = w->H; p.E = w->E; p.top_k = w->top_k; p.route_mode = w->route_mode;
+    p.has_shared = w->F_s > 0;
+    p.route_scale = w->route_scale;
+    p.x = d_x; p.router_w = w->router_w; p.router_bias = w->router_bias;
+    p.shexp_gate_w = (w->F_s > 0) ? w->shexp_gate_w : nullptr;
+    p.counters = (int32_t*)(base + kNoAllocCounters);
+    p.router_logits = (float*)(base + kNoAllocLogits);
+    p.sh_gate_logit = (float*)(base + kNoAllocShLogit);
+    p.x_q8 = base + kNoAllocXq8;
+    p.x_soa_q = (int8_t*)(base + kNoAllocXq);
+    p.x_soa_d = (float*)(base + kNoAllocXd);
+    p.x_soa_d_stride = (w->H / 32 + 3) & ~3;
+    p.perm = (int32_t*)(base + kNoAllocPerm);
+    p.offsets = (int32_t*)(base + kNoAllocOffsets);
+    p.group_list = (int32_t*)(base + kNoAllocList);
+    p.topk_idx = d_topk_idx;   // results go straight to the caller's buffers
+    p.topk_w = d_topk_w;
+    e = launch_route(p, stream);
+    return e == cudaSuccess ? 0 : -100 - (int)e;
+}

@@ -146,6 +146,19 @@ int chimere_b200_moe_forward_host(const chimere_moe_layer* w, const float* h_x, 
 int chimere_b200_moe_route(const chimere_moe_layer* w, const float* d_x, int T,
                            chimere_moe_workspace* ws, cudaStream_t stream);
 
+/* Routing for callers that cannot provide scratch memory and cannot allocate any: a serving process
+ * that handed all device memory to its own pool at start-up, or code running where cudaMalloc is not
+ * allowed.  Same computation as chimere_b200_moe_route, but the scratch is a fixed array inside the
+ * library (about 680 KiB per GPU, held from the moment the library is loaded on that GPU until the
+ * process exits) and the results go to the caller's buffers: d_topk_idx [T][top_k] int32 and
+ * d_topk_w [T][top_k] f32.  Limits: T <= 64 tokens, H <= 4096, E <= 256; anything larger returns -7.
+ * The first call on each device looks the array's address up (cudaGetSymbolAddress): make that call
+ * outside any stream capture.  All calls on a device share the array, so calls that overlap on the GPU
+ * race; run them on one stream or order them yourself.  No cudaMalloc / cudaFree, here or below.
+ * This entry has no counterpart in the reference. */
+int chimere_b200_moe_route_noalloc(const chimere_moe_layer* w, const float* d_x, int T,
+                                   int32_t* d_topk_idx, float* d_topk_w, cudaStream_t stream);
+
 /* The fused expert up/gate operator on its own: for every (token, selected expert) pair and the
  * shared expert, act(gate . x, up . x) quantized to Q8_1 into ws->inter_q8.  Needs the routing
  * results of chimere_b200_moe_route in `ws`.  Replaces moe_ffn.rs:1206-1323 (batched gate GEMV,
