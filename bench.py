@@ -266,8 +266,11 @@ def main():
     dn_bytes = sum(u * b_dn + b_dn_sh + pairs * iq_row + T * cfg.H * 4 for u in U) / L
     gu_secs = time_steps(gate_up_all, max(5, K), 3) / (max(5, K) * L)
     dn_secs = time_steps(down_all, max(5, K), 3) / (max(5, K) * L)
-    roof = {"bound": "hbm", "kernel": ("gate_up_tiled_kernel<IQ3_S>" if args.layout == "tiled" else "gate_up_kernel<IQ3_S>"), "achieved": gu_bytes / gu_secs / 1e9, "peak": hbm_peak,
-            "unit": "GB/s", "frac": gu_bytes / gu_secs / 1e9 / hbm_peak, "peak_kind": peak_kind, "traffic": None,
+    roof = {"bound": "hbm", "kernel": ("tile_kernel<IQ3_S, gate_up>" if args.layout == "tiled" else "gate_up_kernel<IQ3_S>"), "achieved": gu_bytes / gu_secs / 1e9, "peak": hbm_peak,
+            "unit": "GB/s", "frac": gu_bytes / gu_secs / 1e9 / hbm_peak, "peak_kind": peak_kind,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at these sizes (ncu capture summarised
+            # in profiles/tile_kernel_decode_T8.md; IQ3_S is streamed as 4-bit codes: +22 % over the ggml bytes)
+            "traffic": (67055872 + 120000) if (args.layout == "tiled" and T == 8) else None,
             "us_per_launch": gu_secs * 1e6, "algorithmic_bytes_per_launch": gu_bytes,
             "down_kernel": {"achieved": dn_bytes / dn_secs / 1e9, "frac": dn_bytes / dn_secs / 1e9 / hbm_peak,
                             "us_per_launch": dn_secs * 1e6, "algorithmic_bytes_per_launch": dn_bytes},
