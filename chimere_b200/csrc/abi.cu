@@ -172,11 +172,68 @@ int chimere_b200_moe_route(const chimere_moe_layer* w, const float* d_x, int T, 
     return cuda_rc(launch_route(route_params(w, d_x, T, ws), stream));
 }
 
+static GemvParams gate_up_params(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, const Layout& L);
+static GemvParams down_params(const chimere_moe_layer* w, float* d_y, int T, chimere_moe_workspace* ws, const Layout& L);
+
 int chimere_b200_moe_permute(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, cudaStream_t stream) {
-    // The routing launch already leaves perm / offsets / the work list behind; this entry exists for
-    // callers that rewrite ws->topk_idx themselves.  It re-runs only the dispatch step.
-    (void)w; (void)T; (void)ws; (void)stream;
-    return -6;  // not built yet
+    // The routing launch already leaves perm / offsets / the work list behind; this entry is for callers
+    // that write ws->topk_idx themselves.  It runs only the dispatch step (no shared-expert entries).
+    int rc = check_call(w, ws, ws, T, ws);
+    if (rc) return rc;
+    RouteParams p = route_params(w, nullptr, T, ws);
+    p.has_shared = 0;
+    return cuda_rc(launch_permute(p, stream));
+}
+
+// ---------------------------------------------------------------- expert-parallel pieces ----
+int chimere_b200_moe_route_home(const chimere_moe_layer* w, const float* d_x, int T, chimere_moe_workspace* ws,
+                                cudaStream_t stream) {
+    int rc = check_call(w, d_x, d_x, T, ws);
+    if (rc) return rc;
+    RouteParams p = route_params(w, d_x, T, ws);
+    p.list_mode = 1;   // work list: shared-expert entries only; the routed pairs go to their owners
+    return cuda_rc(launch_route(p, stream));
+}
+
+int chimere_b200_moe_shared_expert(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, cudaStream_t stream) {
+    int rc = check_call(w, ws, ws, T, ws);
+    if (rc) return rc;
+    if (w->layout != CHIMERE_LAYOUT_TILED32) return -2;
+    if (w->F_s <= 0) return 0;
+    const Layout L = make_layout(w, ws->max_T);
+    const int max_entries = max_entries_for(w, T);
+    cudaError_t e = launch_gate_up_tiled(gate_up_params(w, T, ws, L), max_entries, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    GemvParams g = down_params(w, nullptr, T, ws, L);
+    g.no_combine = 1;
+    return cuda_rc(launch_down_tiled(g, max_entries, stream));
+}
+
+int chimere_b200_moe_experts(const chimere_moe_layer* w_local, int n_rows, chimere_moe_workspace* ws, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    int rc = check_call(w_local, ws, ws, n_rows, ws);
+    if (rc) return rc;
+    if (w_local->layout != CHIMERE_LAYOUT_TILED32 || w_local->top_k != 1 || w_local->F_s != 0) return -2;
+    RouteParams p = route_params(w_local, nullptr, n_rows, ws);
+    p.has_shared = 0;
+    cudaError_t e = launch_permute(p, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    const Layout L = make_layout(w_local, ws->max_T);
+    const int max_entries = max_entries_for(w_local, n_rows);
+    e = launch_gate_up_tiled(gate_up_params(w_local, n_rows, ws, L), max_entries, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    GemvParams g = down_params(w_local, nullptr, n_rows, ws, L);
+    g.no_combine = 1;
+    return cuda_rc(launch_down_tiled(g, max_entries, stream));
+}
+
+int chimere_b200_moe_ep_finish(const chimere_moe_layer* w, const float* d_rows, int T, chimere_moe_workspace* ws, float* d_y,
+                               cudaStream_t stream) {
+    int rc = check_call(w, d_rows, d_y, T, ws);
+    if (rc) return rc;
+    const float* shared_rows = w->F_s > 0 ? ws->pair_out + (size_t)T * w->top_k * w->H : nullptr;
+    const float* logit = (w->F_s > 0 && w->shexp_gate_w) ? ws->sh_gate_logit : nullptr;
+    return cuda_rc(launch_ep_finish(d_rows, ws->topk_w, shared_rows, logit, d_y, T, w->H, w->top_k, stream));
 }
 
 static GemvParams gate_up_params(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, const Layout& L) {

@@ -204,6 +204,7 @@ __global__ void __launch_bounds__(kThreadsT, 4) tile_kernel(const GemvParams p, 
         const int i = e / width, c = e - i * width;
         if (c < rows_here) p.pair_out[(size_t)s_row[i] * H + r0 + c] = sum_slices(red, 0, wk, i, width, c);
     }
+    if (p.no_combine) return;
     // Whoever completes a token's contributions for this row tile adds them up.  The CTA barrier orders the rows
     // written above before thread 0's device-scope fence (fences are cumulative); its second fence, before the
     // next barrier, orders the reads below.

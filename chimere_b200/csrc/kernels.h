@@ -13,6 +13,7 @@ constexpr int kCtrRouteTile = 16;  // [ceil(max_T/8)] row tiles done per token t
 
 struct RouteParams {
     int T, H, E, top_k, route_mode, has_shared;
+    int list_mode;              // 0: work list for routed + shared entries; 1: shared-expert entries only (expert-parallel home rank)
     float route_scale;
     const float* x;             // [T][H]
     const float* router_w;      // [E][H]
@@ -68,9 +69,15 @@ struct GemvParams {
     float* out_soa_d; int64_t out_soa_d_stride;
     int32_t* queue;              // streaming kernels: [0..1] gate/up work queue, [2..3] down work queue (zero between calls)
     int32_t* status;
+    int no_combine;              // down stage: only write the per-pair rows (the caller combines)
 };
 
 cudaError_t launch_route(const RouteParams& p, cudaStream_t stream);
+// dispatch permutation + work list from p.topk_idx alone (no routing, no shared entries)
+cudaError_t launch_permute(const RouteParams& p, cudaStream_t stream);
+// y[t][h] = sum_j w[t][j] * rows[t*k+j][h] (+ shared[t][h] * sigmoid(logit[t]) or + shared[t][h])
+cudaError_t launch_ep_finish(const float* rows, const float* topk_w, const float* shared_rows, const float* sh_logit, float* y,
+                             int T, int H, int k, cudaStream_t stream);
 cudaError_t launch_gate_up(const GemvParams& p, int max_entries, cudaStream_t stream);
 cudaError_t launch_down(const GemvParams& p, int max_entries, cudaStream_t stream);
 

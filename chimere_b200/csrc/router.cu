@@ -154,7 +154,8 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i) {
     int total_routed = 0;
     for (int w = 0; w < 8; ++w) total_routed += scan[8 + w];
     // routed work entries
-    for (int i = 0; i < nent; ++i) {
+    if (p.list_mode == 1) total_routed = 0;
+    for (int i = 0; i < (p.list_mode == 1 ? 0 : nent); ++i) {
         int* ent = p.group_list + kListHeader + 4 * (ent0 + i);
         ent[0] = tid;
         ent[1] = off + i * kMaxGroupTokens;
@@ -289,10 +290,47 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
     build_dispatch(p, reinterpret_cast<int*>(smem_f));
 }
 
+// The dispatch step alone, for callers that bring their own expert ids in p.topk_idx.
+__global__ void __launch_bounds__(256) permute_kernel(const RouteParams p) {
+    extern __shared__ __align__(16) float smem_f[];
+    build_dispatch(p, reinterpret_cast<int*>(smem_f));
+}
+
+// Final step of an expert-parallel layer on the tokens' home rank: routing-weighted sum of the k expert
+// rows of every token in slot order (weighted_combine_kernel, chimere_kernels.cu:1551-1565) plus the
+// sigmoid-gated shared expert (sigmoid_gate_add_kernel, scratch_pool.rs:266-277).
+__global__ void ep_finish_kernel(const float* rows, const float* topk_w, const float* shared_rows, const float* sh_logit,
+                                 float* y, int T, int H, int k) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)T * H) return;
+    const int t = (int)(idx / H), h = (int)(idx - (int64_t)t * H);
+    float sum = 0.0f;
+    for (int j = 0; j < k; ++j) sum = fmaf(topk_w[(size_t)t * k + j], rows[((size_t)t * k + j) * H + h], sum);
+    if (shared_rows) {
+        const float sh = shared_rows[(size_t)t * H + h];
+        if (sh_logit) sum = fmaf(sh, sigmoid_ref(sh_logit[t]), sum);
+        else sum = sh + sum;
+    }
+    y[idx] = sum;
+}
+
 static size_t route_smem(int TT, int TE) {
     size_t a = (size_t)TT * TE * 256 * sizeof(float);
     size_t b = (512 + 2048 + 256) * sizeof(int);
     return a > b ? a : b;
+}
+
+cudaError_t launch_permute(const RouteParams& p, cudaStream_t stream) {
+    permute_kernel<<<1, 256, (512 + 2048 + 256) * sizeof(int), stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_ep_finish(const float* rows, const float* topk_w, const float* shared_rows, const float* sh_logit, float* y,
+                             int T, int H, int k, cudaStream_t stream) {
+    const int64_t n = (int64_t)T * H;
+    if (n <= 0) return cudaSuccess;
+    ep_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(rows, topk_w, shared_rows, sh_logit, y, T, H, k);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {

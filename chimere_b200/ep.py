@@ -1,0 +1,159 @@
+"""Expert parallelism for the MoE layer: experts sharded over the ranks of one node in contiguous
+ranges, router and shared expert replicated, tokens sharded (every rank routes its own tokens).
+
+The reference has no multi-GPU code (no collective library is linked, chimere-server/Cargo.toml:7-26);
+this is the design of its benchmark configuration "expert-parallel stack": one all-to-all before the
+expert products (dispatch: the Q8_1 planes of every (token, expert) pair go to the expert's owner;
+quantisation happens once on the home rank, so results are bit-identical to the single-GPU path) and
+one after (combine: the pairs' fp32 expert rows come home, where they are weighted and added in slot
+order together with the shared expert).  torch.distributed (NCCL over NVLink on GPUs, gloo in the CPU
+tests) carries the exchanges; all arithmetic is in the CUDA library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import abi
+from .layer import MoeScratch, MoeWeightsRaw, MoeWeightsTiled
+
+
+# ------------------------------------------------------------------ exchange plan (pure torch) ----
+@dataclass
+class DispatchPlan:
+    order: torch.Tensor        # [P] pair ids (t*k + j) sorted by destination rank, stable
+    send_counts: torch.Tensor  # [G] int64 pairs going to each rank
+    local_ids: torch.Tensor    # [P] int32 expert id within the owner's shard, in send order
+
+
+def plan_dispatch(topk_idx: torch.Tensor, experts_per_rank: int, world: int) -> DispatchPlan:
+    """Pairs in row-major (token, slot) order -> send order grouped by owner rank (stable)."""
+    flat = topk_idx.reshape(-1).to(torch.int64)
+    dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
+    order = torch.sort(dest, stable=True).indices
+    send_counts = torch.bincount(dest, minlength=world)
+    local_ids = (flat[order] - dest[order] * experts_per_rank).to(torch.int32)
+    return DispatchPlan(order, send_counts, local_ids)
+
+
+def exchange_counts(send_counts: torch.Tensor, group=None) -> torch.Tensor:
+    recv = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv, send_counts, group=group)
+    return recv
+
+
+def all_to_all_rows(send: torch.Tensor, send_counts: List[int], recv_counts: List[int], out: Optional[torch.Tensor] = None,
+                    group=None) -> torch.Tensor:
+    """Rows of `send` (grouped by destination) -> rows grouped by source, into `out[:sum(recv_counts)]`."""
+    n = sum(recv_counts)
+    if out is None:
+        out = torch.empty((n,) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+    dist.all_to_all_single(out[:n], send.contiguous(), output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
+    return out[:n]
+
+
+# ------------------------------------------------------------------ the layer on GPUs --------------
+class ExpertParallelMoE:
+    """One MoE layer on `world` GPUs.  `full_raw` is the whole layer (same on every rank, e.g. seeded);
+    only this rank's expert range is kept on the device after construction."""
+
+    def __init__(self, full_raw: MoeWeightsRaw, max_tokens: int, rank: int, world: int, device, group=None):
+        assert full_raw.E % world == 0
+        self.rank, self.world, self.group = rank, world, group
+        self.k, self.E, self.H = full_raw.top_k, full_raw.E, full_raw.H
+        self.E_loc = full_raw.E // world
+        lo, hi = rank * self.E_loc, (rank + 1) * self.E_loc
+        dev = torch.device(device)
+        sl = lambda t: None if t is None else t[lo:hi].contiguous().to(dev)
+        mv = lambda t: None if t is None else t.contiguous().to(dev)
+        local = MoeWeightsRaw(
+            H=full_raw.H, E=self.E_loc, F=full_raw.F, F_s=full_raw.F_s, top_k=min(full_raw.top_k, self.E_loc),
+            type_gate=full_raw.type_gate, type_up=full_raw.type_up, type_down=full_raw.type_down,
+            router_weight=mv(full_raw.router_weight[lo:hi]), up_exps_raw=sl(full_raw.up_exps_raw), down_exps_raw=sl(full_raw.down_exps_raw),
+            gate_exps_raw=sl(full_raw.gate_exps_raw), shexp_gate_proj=mv(full_raw.shexp_gate_proj),
+            shexp_gate_raw=mv(full_raw.shexp_gate_raw), shexp_up_raw=mv(full_raw.shexp_up_raw), shexp_down_raw=mv(full_raw.shexp_down_raw),
+            route_mode=full_raw.route_mode, route_scale=full_raw.route_scale, act=full_raw.act,
+            type_sh_gate=full_raw.type_sh_gate, type_sh_up=full_raw.type_sh_up, type_sh_down=full_raw.type_sh_down)
+        self.packed = MoeWeightsTiled(local, keep_raw=False)
+        self.router_weight = mv(full_raw.router_weight)
+        self.router_bias = mv(full_raw.router_bias)
+        # home view: the whole router, the shared expert; expert pointers are the local shard's (never used for routed pairs here)
+        self.home = abi.MoeLayer.from_buffer_copy(self.packed.as_struct())
+        self.home.E, self.home.top_k = self.E, self.k
+        self.home.router_w = self.router_weight.data_ptr()
+        self.home.router_bias = None if self.router_bias is None else self.router_bias.data_ptr()
+        # owner view: the local shard as a layer of E_loc experts, one expert per row, no shared expert
+        self.owner = abi.MoeLayer.from_buffer_copy(self.packed.as_struct())
+        self.owner.E, self.owner.top_k, self.owner.F_s = self.E_loc, 1, 0
+        self.max_tokens = max_tokens
+        self.max_rows = max_tokens * self.k * world   # worst case: every pair of every rank lands here
+        self.ws_home = _Scratch(self.home, full_raw, max_tokens, dev)
+        self.ws_owner = _Scratch(self.owner, full_raw, self.max_rows, dev)
+        self.rows_pair = torch.empty(max_tokens * self.k, self.H, dtype=torch.float32, device=dev)
+        self.back = torch.empty(max_tokens * self.k, self.H, dtype=torch.float32, device=dev)
+        self.lib = abi.load()
+        self.last_recv_rows = 0
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        lib, T, k, H = self.lib, x.shape[0], self.k, self.H
+        assert T <= self.max_tokens and x.is_contiguous()
+        if out is None:
+            out = torch.empty_like(x)
+        st = torch.cuda.current_stream(x.device).cuda_stream
+        abi.check(lib.chimere_b200_moe_route_home(C.byref(self.home), x.data_ptr(), T, C.byref(self.ws_home.ws), st), "route_home")
+        # the shared expert needs nothing from other ranks: enqueue it before the exchanges
+        abi.check(lib.chimere_b200_moe_shared_expert(C.byref(self.home), T, C.byref(self.ws_home.ws), st), "shared_expert")
+        plan = plan_dispatch(self.ws_home.topk_idx(T, k), self.E_loc, self.world)
+        recv_counts_t = exchange_counts(plan.send_counts, self.group)
+        send_counts, recv_counts = plan.send_counts.tolist(), recv_counts_t.tolist()   # host sync: split sizes
+        n = sum(recv_counts)
+        assert n <= self.max_rows
+        self.last_recv_rows = n
+        tok = torch.div(plan.order, k, rounding_mode="floor")
+        # dispatch: int8 plane, scale plane and local expert id of every pair, straight into the owner's workspace
+        all_to_all_rows(self.ws_home.x_q(T)[tok], send_counts, recv_counts, self.ws_owner.x_q(self.max_rows), self.group)
+        all_to_all_rows(self.ws_home.x_d(T)[tok], send_counts, recv_counts, self.ws_owner.x_d(self.max_rows), self.group)
+        all_to_all_rows(plan.local_ids, send_counts, recv_counts, self.ws_owner.topk_idx(self.max_rows, 1).reshape(-1), self.group)
+        abi.check(lib.chimere_b200_moe_experts(C.byref(self.owner), n, C.byref(self.ws_owner.ws), st), "experts")
+        # combine: the pairs' expert rows come home, back into (token, slot) order
+        back = all_to_all_rows(self.ws_owner.pair_out(self.max_rows)[:n], recv_counts, send_counts, self.back, self.group)
+        self.rows_pair[:T * k].index_copy_(0, plan.order, back)
+        abi.check(lib.chimere_b200_moe_ep_finish(C.byref(self.home), self.rows_pair.data_ptr(), T, C.byref(self.ws_home.ws),
+                                                 out.data_ptr(), st), "ep_finish")
+        return out
+
+
+class _Scratch:
+    """Workspace of one layer view plus typed views of the buffers the exchanges touch."""
+
+    def __init__(self, struct: abi.MoeLayer, dims: MoeWeightsRaw, max_T: int, dev):
+        lib = abi.load()
+        self.H = struct.H
+        self.dstride = (struct.H // 32 + 3) & ~3
+        nbytes = lib.chimere_b200_moe_workspace_bytes(C.byref(struct), max_T)
+        if nbytes == 0:
+            raise RuntimeError("workspace_bytes rejected the layer view")
+        self.arena = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.ws = abi.MoeWorkspace()
+        st = torch.cuda.current_stream(dev).cuda_stream
+        abi.check(lib.chimere_b200_moe_workspace_init(C.byref(self.ws), self.arena.data_ptr(), nbytes, C.byref(struct), max_T, st), "workspace_init")
+
+    def _view(self, ptr, nbytes):
+        off = ptr - self.arena.data_ptr()
+        return self.arena[off:off + nbytes]
+
+    def topk_idx(self, T, k):
+        return self._view(self.ws.topk_idx, T * k * 4).view(torch.int32).reshape(T, k)
+
+    def x_q(self, T):
+        return self._view(self.ws.x_q, T * self.H).view(torch.int8).reshape(T, self.H)
+
+    def x_d(self, T):
+        return self._view(self.ws.x_d, T * self.dstride * 4).view(torch.float32).reshape(T, self.dstride)
+
+    def pair_out(self, n):
+        return self._view(self.ws.pair_out, n * self.H * 4).view(torch.float32).reshape(n, self.H)

@@ -177,6 +177,32 @@ int chimere_b200_moe_down_combine(const chimere_moe_layer* w, float* d_y, int T,
 int chimere_b200_moe_permute(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws,
                              cudaStream_t stream);
 
+/* ------------------------------------------------------------ expert-parallel pieces ------ */
+/* Experts sharded over several GPUs (contiguous ranges), router and shared expert replicated.  The
+ * reference is single-GPU (no collective anywhere in its sources); these four entries are the local
+ * steps either side of the two all-to-all exchanges, which the host runs with NCCL.  All need the
+ * TILED32 layout.
+ *
+ * Home rank of a token:   route_home -> [send Q8_1 planes of the routed pairs] ... shared_expert ...
+ *                         [receive the pairs' expert rows] -> ep_finish
+ * Owner rank of experts:  [receive planes + local expert ids into ws->x_q, ws->x_d, ws->topk_idx]
+ *                         -> experts -> [send ws->pair_out rows back]                              */
+
+/* Router, top-k and Q8_1 as chimere_b200_moe_route, but the work list holds only the shared expert. */
+int chimere_b200_moe_route_home(const chimere_moe_layer* w, const float* d_x, int T,
+                                chimere_moe_workspace* ws, cudaStream_t stream);
+/* Shared expert of the T routed tokens: rows land in ws->pair_out[T*top_k + t]. */
+int chimere_b200_moe_shared_expert(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws,
+                                   cudaStream_t stream);
+/* n_rows (token, expert) pairs whose Q8_1 planes sit in ws->x_q / ws->x_d and whose local expert ids sit in
+ * ws->topk_idx[n_rows]; w_local describes the local shard (E = local experts, top_k = 1, F_s = 0).
+ * Expert outputs (down . act(gate/up . x), unweighted) land in ws->pair_out[row][H]. */
+int chimere_b200_moe_experts(const chimere_moe_layer* w_local, int n_rows, chimere_moe_workspace* ws,
+                             cudaStream_t stream);
+/* y[t] = sum_j topk_w[t][j] * d_rows[t*top_k + j] (slot order) + sigmoid-gated shared row. */
+int chimere_b200_moe_ep_finish(const chimere_moe_layer* w, const float* d_rows, int T,
+                               chimere_moe_workspace* ws, float* d_y, cudaStream_t stream);
+
 /* Parity tap: integer block dot products.  For `nrows` weight rows of type `wtype` with `ncols`
  * columns and one Q8_1 input row, writes sumi[nrows][ncols/32] (int32): the exact integer sum of
  * each 32-wide block (for IQ3_S including the (1 + 2*scale) factor, chimere_kernels.cu:860). */
