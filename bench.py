@@ -137,6 +137,110 @@ def workload_config(cfg, T, L):
             "l2": f"weights rotate over {L} layers; one cycle touches more than the 126 MB L2, inputs differ per layer"}
 
 
+def run_expert_parallel(args, cfg, dev, rank, world, local, dist, hbm_peak, peak_kind):
+    """N > 1: the same layer with its experts sharded over the ranks (E/N each, contiguous), router and shared
+    expert replicated, T tokens per rank (weak scaling), dispatch and combine by NCCL all-to-all."""
+    import torch
+    from chimere_b200 import configs, formats
+    from chimere_b200.ep import ExpertParallelMoE
+    T, L, K, W = args.tokens, args.layers, args.steps, args.warmup
+    layers = []
+    for i in range(L):
+        full = configs.make_layer(cfg, device=dev, seed=1000 + i)          # same weights on every rank, then sharded
+        layers.append(ExpertParallelMoE(full, max_tokens=T, rank=rank, world=world, device=dev))
+        del full
+    xs = [configs.make_input(cfg, T, device=dev, seed=31 * (rank + 1) + i) for i in range(L)]
+    ys = [torch.empty_like(x) for x in xs]
+
+    padded = T * cfg.top_k <= 1024          # decode-size: fixed-size exchange, no host sync per layer
+
+    def step():
+        for ep, x, y in zip(layers, xs, ys):
+            (ep.forward_padded if padded else ep.forward)(x, y)
+
+    # one step = one CUDA graph when the exchange is fixed-size (NCCL all-to-alls are captured with the kernels)
+    timing_note = "eager launches"
+    graph = None
+    if padded:
+        try:
+            step(); step()
+            torch.cuda.synchronize(); dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            torch.cuda.synchronize()
+            timing_note = "CUDA graph replay of one step (kernels and NCCL all-to-alls captured together)"
+        except Exception as exc:  # keep the eager path if this torch/NCCL pair cannot capture collectives
+            graph = None
+            timing_note = f"eager launches (graph capture failed: {type(exc).__name__})"
+            torch.cuda.synchronize()
+    run_step = graph.replay if graph is not None else step
+
+    def timed(fn, k, w):
+        for _ in range(w):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(k):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e-3], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local)
+    secs = timed(run_step, K, W)
+    clocks = sampler.stop()
+    value = world * T * L * K / secs
+
+    hx = [x.cpu().pin_memory() for x in xs]
+    hy = [torch.empty(T, cfg.H).pin_memory() for _ in xs]
+
+    def e2e_step():
+        for ep, a, b, x, y in zip(layers, hx, hy, xs, ys):
+            x.copy_(a, non_blocking=True)
+            (ep.forward_padded if padded else ep.forward)(x, y)
+            b.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_secs = timed(e2e_step, K, W)
+    recv = torch.tensor([float(sum(ep.last_recv_rows for ep in layers)) / L], device=dev)
+    rmax = recv.clone(); dist.all_reduce(rmax, op=dist.ReduceOp.MAX)
+    rsum = recv.clone(); dist.all_reduce(rsum, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        b_gu = cfg.F * formats.row_bytes(cfg.type_gate_up, cfg.H)
+        b_dn = cfg.H * formats.row_bytes(cfg.type_down, cfg.F)
+        rows_mean = float(rsum.item()) / world
+        layer_us = secs / (K * L) * 1e6
+        # per rank and layer call: every received pair's expert (upper bound on distinct experts: one per pair) + shared + router
+        alg = min(rows_mean, cfg.E / world) * (2 * b_gu + b_dn) + (2 * b_gu + b_dn) + 4 * cfg.E * cfg.H + 8 * T * cfg.H
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": 1e3 * secs / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "int8 block dots (dp4a), f32 accumulate", "data": "synthetic",
+                "config": dict(workload_config(cfg, T, L), parallelism=f"ep{world}: {cfg.E // world} experts per GPU, router + shared expert replicated, "
+                               f"{T} tokens per GPU; dispatch Q8_1 planes / combine fp32 rows by NCCL all-to-all",
+                               timing="CUDA events around K steps, max over ranks; " + timing_note,
+                               exchange=("fixed-size (padded to T*k rows per destination), no host sync" if padded
+                                         else "exact split sizes, one host sync per layer call"),
+                               weight_layout="tiled"),
+                "roofline": {"bound": "hbm", "kernel": "expert-parallel layer call (per rank)", "achieved": alg / (layer_us * 1e-6) / 1e9,
+                             "peak": hbm_peak, "unit": "GB/s", "frac": alg / (layer_us * 1e-6) / 1e9 / hbm_peak, "peak_kind": peak_kind,
+                             "traffic": None, "us_per_layer_call": layer_us,
+                             "pairs_received_per_rank_mean": rows_mean, "pairs_received_per_rank_max": float(rmax.item()),
+                             "nvlink_bytes_per_rank_per_call": rows_mean * (cfg.H + 4 * ((cfg.H // 32 + 3) & ~3) + 4 + 4 * cfg.H)},
+                "cpu_baseline": None,
+                "e2e": {"value": world * T * L * K / e2e_secs, "unit": UNIT, "h2d_bytes_per_step": L * T * cfg.H * 4,
+                        "d2h_bytes_per_step": L * T * cfg.H * 4, "ms_per_step": 1e3 * e2e_secs / K},
+                "gpu_launches": 7 * L * K, "clocks": clocks}
+        print(json.dumps(line))
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -174,6 +278,8 @@ def main():
     cfg = configs.QWEN_IQ3S
     T, L, K, W = args.tokens, args.layers, args.steps, args.warmup
     hbm_peak, peak_kind = peaks()
+    if world > 1:
+        return run_expert_parallel(args, cfg, dev, rank, world, local, dist, hbm_peak, peak_kind)
 
     # ---- resident state: L layers of weights, one scratch per (layer), inputs, outputs ----
     # each layer: seeded ggml blocks -> one-time load-side rewrite into the library's tiled32 layout

@@ -129,7 +129,11 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i) {
     hist[tid] = 0;
     for (int i = tid; i < 2048; i += 256) warp_cnt[i] = 0;
     __syncthreads();
-    for (int q = tid; q < P; q += 256) atomicAdd(&hist[__ldcg(p.topk_idx + q)], 1);
+    // ids outside [0, E) mark pairs that are not there (padding of a fixed-size exchange): they get no work
+    for (int q = tid; q < P; q += 256) {
+        const int e = __ldcg(p.topk_idx + q);
+        if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
+    }
     __syncthreads();
     // exclusive scans over the experts: pair offsets and work-entry offsets
     const int cnt = (tid < E) ? hist[tid] : 0;
@@ -149,7 +153,7 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i) {
     cursor[tid] = off;
     if (tid < E) p.offsets[tid] = off;
     if (tid == 255) {
-        p.offsets[E] = P;  // tid 255 holds the inclusive total (cnt = 0 beyond E)
+        p.offsets[E] = base_c + incl_c;  // tid 255 holds the inclusive total (cnt = 0 beyond E)
     }
     int total_routed = 0;
     for (int w = 0; w < 8; ++w) total_routed += scan[8 + w];
@@ -181,8 +185,10 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i) {
     // stable placement, 256 pairs per step
     for (int base = 0; base < P; base += 256) {
         const int q = base + tid;
-        const bool valid = q < P;
-        const int e = valid ? __ldcg(p.topk_idx + q) : (0x40000000 + tid);
+        bool valid = q < P;
+        int e = valid ? __ldcg(p.topk_idx + q) : -1;
+        valid = valid && e >= 0 && e < E;
+        if (!valid) e = 0x40000000 + tid;
         const unsigned same = __match_any_sync(0xffffffffu, e);
         const int rank = __popc(same & ((1u << lane) - 1u));
         const bool leader = valid && rank == 0;

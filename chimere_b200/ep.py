@@ -127,6 +127,52 @@ class ExpertParallelMoE:
         return out
 
 
+    # ---- decode-size batches: fixed-size exchange, no host synchronisation, CUDA-graph capturable ----
+    def forward_padded(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """Same result as forward().  Every rank sends every other rank room for all of its T*k pairs (rows that are
+        not there carry expert id -1 and cost the owner nothing), so no counts have to reach the host.  Meant for
+        small T; the padding grows with world * T * k rows."""
+        lib, T, k, H, G = self.lib, x.shape[0], self.k, self.H, self.world
+        assert T == self.max_tokens, "the padded path works on a fixed batch size"
+        C_ = T * k                                   # capacity per destination
+        dev = x.device
+        st = torch.cuda.current_stream(dev).cuda_stream
+        if not hasattr(self, "_pad"):
+            ds = self.ws_home.dstride
+            rb = (H + 4 * ds + 4 + 15) & ~15
+            self._pad = dict(ds=ds, rb=rb,
+                             send=torch.empty(G * C_, rb, dtype=torch.uint8, device=dev), recv=torch.empty(G * C_, rb, dtype=torch.uint8, device=dev),
+                             back=torch.empty(G * C_, H, dtype=torch.float32, device=dev), ar=torch.arange(T * k, device=dev))
+        pd = self._pad
+        ds, send, recv = pd["ds"], pd["send"], pd["recv"]
+        abi.check(lib.chimere_b200_moe_route_home(C.byref(self.home), x.data_ptr(), T, C.byref(self.ws_home.ws), st), "route_home")
+        abi.check(lib.chimere_b200_moe_shared_expert(C.byref(self.home), T, C.byref(self.ws_home.ws), st), "shared_expert")
+        flat = self.ws_home.topk_idx(T, k).reshape(-1).to(torch.int64)
+        dest = torch.div(flat, self.E_loc, rounding_mode="floor")
+        order = torch.sort(dest, stable=True).indices
+        sdest = dest[order]
+        counts = torch.bincount(dest, minlength=G)
+        starts = torch.cumsum(counts, 0) - counts
+        slot = sdest * C_ + (pd["ar"] - starts[sdest])            # where each pair sits in the padded send buffer
+        tok = torch.div(order, k, rounding_mode="floor")
+        ids = send[:, H + 4 * ds:H + 4 * ds + 4].view(torch.int32)
+        ids.fill_(-1)
+        ids.index_copy_(0, slot, (flat[order] - sdest * self.E_loc).to(torch.int32)[:, None])
+        send[:, :H].view(torch.int8).index_copy_(0, slot, self.ws_home.x_q(T)[tok])
+        send[:, H:H + 4 * ds].view(torch.float32).index_copy_(0, slot, self.ws_home.x_d(T)[tok])
+        dist.all_to_all_single(recv, send, group=self.group)
+        n = G * C_
+        self.ws_owner.x_q(n).copy_(recv[:, :H].view(torch.int8))
+        self.ws_owner.x_d(n).copy_(recv[:, H:H + 4 * ds].view(torch.float32))
+        self.ws_owner.topk_idx(n, 1).copy_(recv[:, H + 4 * ds:H + 4 * ds + 4].view(torch.int32))
+        abi.check(lib.chimere_b200_moe_experts(C.byref(self.owner), n, C.byref(self.ws_owner.ws), st), "experts")
+        dist.all_to_all_single(pd["back"], self.ws_owner.pair_out(n), group=self.group)
+        self.rows_pair[:T * k].index_copy_(0, order, pd["back"][slot])
+        abi.check(lib.chimere_b200_moe_ep_finish(C.byref(self.home), self.rows_pair.data_ptr(), T, C.byref(self.ws_home.ws),
+                                                 out.data_ptr(), st), "ep_finish")
+        return out
+
+
 class _Scratch:
     """Workspace of one layer view plus typed views of the buffers the exchanges touch."""
 

@@ -26,7 +26,7 @@ def main():
         ep = ExpertParallelMoE(full, max_tokens=T, rank=rank, world=world, device=dev)
         x = configs.make_input(cfg, T, device=dev, seed=50 + rank)     # this rank's tokens
         y_ep = ep.forward(x).clone()
-        y_ep2 = ep.forward(x).clone()                                  # second call: workspaces are reused
+        y_ep2 = ep.forward_padded(x, torch.empty_like(x)).clone()     # fixed-size exchange, workspaces reused
         packed = MoeWeightsTiled(full)
         y_ref = forward_moe(packed, MoeScratch(packed, T, device=dev), x)
         torch.cuda.synchronize()
