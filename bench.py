@@ -173,6 +173,7 @@ def run_expert_parallel(args, cfg, dev, rank, world, local, dist, hbm_peak, peak
         except Exception as exc:  # keep the eager path if this torch/NCCL pair cannot capture collectives
             graph = None
             timing_note = f"eager launches (graph capture failed: {type(exc).__name__})"
+            print(f"[bench] graph capture failed: {exc}", file=sys.stderr)
             torch.cuda.synchronize()
     run_step = graph.replay if graph is not None else step
 
@@ -237,8 +238,13 @@ def run_expert_parallel(args, cfg, dev, rank, world, local, dist, hbm_peak, peak
                 "e2e": {"value": world * T * L * K / e2e_secs, "unit": UNIT, "h2d_bytes_per_step": L * T * cfg.H * 4,
                         "d2h_bytes_per_step": L * T * cfg.H * 4, "ms_per_step": 1e3 * e2e_secs / K},
                 "gpu_launches": 7 * L * K, "clocks": clocks}
-        print(json.dumps(line))
-    dist.destroy_process_group()
+        print(json.dumps(line), flush=True)
+    # leave without tearing the communicator down: with a captured graph still holding NCCL work the
+    # teardown has been seen to wait for the watchdog; every rank is past its last collective here
+    torch.cuda.synchronize()
+    dist.barrier()
+    sys.stdout.flush()
+    os._exit(0)
 
 
 def main():

@@ -65,7 +65,9 @@ PROTOTYPES = {
     "chimere_b200_moe_route_home": (C.c_int, [_LAYER_P, _P, C.c_int, _WS_P, _P]),
     "chimere_b200_moe_shared_expert": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P]),
     "chimere_b200_moe_experts": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P]),
-    "chimere_b200_moe_ep_finish": (C.c_int, [_LAYER_P, _P, C.c_int, _WS_P, _P, _P]),
+    "chimere_b200_moe_experts_packed": (C.c_int, [_LAYER_P, C.c_int, _P, C.c_int, _WS_P, _P]),
+    "chimere_b200_moe_ep_pack": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
+    "chimere_b200_moe_ep_finish": (C.c_int, [_LAYER_P, _P, _P, C.c_int, _WS_P, _P, _P]),
     "chimere_b200_moe_permute": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P]),
     "chimere_b200_block_sumi": (C.c_int, [C.c_int, _P, _P, _P, C.c_int, C.c_int, _P]),
     "chimere_b200_rmsnorm": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_float, _P]),

@@ -209,31 +209,64 @@ int chimere_b200_moe_shared_expert(const chimere_moe_layer* w, int T, chimere_mo
     return cuda_rc(launch_down_tiled(g, max_entries, stream));
 }
 
-int chimere_b200_moe_experts(const chimere_moe_layer* w_local, int n_rows, chimere_moe_workspace* ws, cudaStream_t stream) {
+static int run_experts(const chimere_moe_layer* w_local, int n_rows, const void* d_packed, int row_bytes, chimere_moe_workspace* ws,
+                       cudaStream_t stream) {
     if (n_rows == 0) return 0;
     int rc = check_call(w_local, ws, ws, n_rows, ws);
     if (rc) return rc;
     if (w_local->layout != CHIMERE_LAYOUT_TILED32 || w_local->top_k != 1 || w_local->F_s != 0) return -2;
+    const int ds = (w_local->H / 32 + 3) & ~3;
+    if (d_packed && (row_bytes % 16 || row_bytes < w_local->H + 4 * ds + 4)) return -2;
     RouteParams p = route_params(w_local, nullptr, n_rows, ws);
     p.has_shared = 0;
+    if (d_packed) {   // ids sit behind the planes of every packed row
+        p.topk_idx = (int32_t*)((uint8_t*)d_packed + w_local->H + 4 * ds);
+        p.idx_stride = row_bytes / 4;
+    }
     cudaError_t e = launch_permute(p, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     const Layout L = make_layout(w_local, ws->max_T);
     const int max_entries = max_entries_for(w_local, n_rows);
-    e = launch_gate_up_tiled(gate_up_params(w_local, n_rows, ws, L), max_entries, stream);
+    GemvParams gu = gate_up_params(w_local, n_rows, ws, L);
+    if (d_packed) {
+        gu.in_soa_q = (const int8_t*)d_packed; gu.in_soa_q_stride = row_bytes;
+        gu.in_soa_d = (const float*)((const uint8_t*)d_packed + w_local->H); gu.in_soa_d_stride = row_bytes / 4;
+    }
+    e = launch_gate_up_tiled(gu, max_entries, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     GemvParams g = down_params(w_local, nullptr, n_rows, ws, L);
     g.no_combine = 1;
     return cuda_rc(launch_down_tiled(g, max_entries, stream));
 }
 
-int chimere_b200_moe_ep_finish(const chimere_moe_layer* w, const float* d_rows, int T, chimere_moe_workspace* ws, float* d_y,
-                               cudaStream_t stream) {
+int chimere_b200_moe_experts(const chimere_moe_layer* w_local, int n_rows, chimere_moe_workspace* ws, cudaStream_t stream) {
+    return run_experts(w_local, n_rows, nullptr, 0, ws, stream);
+}
+
+int chimere_b200_moe_experts_packed(const chimere_moe_layer* w_local, int n_rows, const void* d_rows, int row_bytes,
+                                    chimere_moe_workspace* ws, cudaStream_t stream) {
+    if (!d_rows) return -1;
+    return run_experts(w_local, n_rows, d_rows, row_bytes, ws, stream);
+}
+
+int chimere_b200_moe_ep_pack(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, void* d_send, int32_t* d_slot,
+                             int experts_per_rank, int world, int cap, int row_bytes, cudaStream_t stream) {
+    int rc = check_call(w, d_send, d_slot, T, ws);
+    if (rc) return rc;
+    const int ds = (w->H / 32 + 3) & ~3;
+    if (experts_per_rank <= 0 || world <= 0 || world * experts_per_rank != w->E || cap < T * w->top_k) return -2;
+    if (row_bytes % 16 || row_bytes < w->H + 4 * ds + 4 || w->H % 16) return -2;
+    return cuda_rc(launch_ep_pack(ws->topk_idx, ws->x_q, ws->x_d, ds, (uint8_t*)d_send, d_slot, T, w->top_k, w->H, experts_per_rank,
+                                  world, cap, row_bytes, stream));
+}
+
+int chimere_b200_moe_ep_finish(const chimere_moe_layer* w, const float* d_rows, const int32_t* d_slot, int T,
+                               chimere_moe_workspace* ws, float* d_y, cudaStream_t stream) {
     int rc = check_call(w, d_rows, d_y, T, ws);
     if (rc) return rc;
     const float* shared_rows = w->F_s > 0 ? ws->pair_out + (size_t)T * w->top_k * w->H : nullptr;
     const float* logit = (w->F_s > 0 && w->shexp_gate_w) ? ws->sh_gate_logit : nullptr;
-    return cuda_rc(launch_ep_finish(d_rows, ws->topk_w, shared_rows, logit, d_y, T, w->H, w->top_k, stream));
+    return cuda_rc(launch_ep_finish(d_rows, d_slot, ws->topk_w, shared_rows, logit, d_y, T, w->H, w->top_k, stream));
 }
 
 static GemvParams gate_up_params(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, const Layout& L) {

@@ -13,6 +13,7 @@ constexpr int kCtrRouteTile = 16;  // [ceil(max_T/8)] row tiles done per token t
 
 struct RouteParams {
     int T, H, E, top_k, route_mode, has_shared;
+    int idx_stride;             // permute only: distance in int32 between consecutive ids (0 or 1 = dense)
     int list_mode;              // 0: work list for routed + shared entries; 1: shared-expert entries only (expert-parallel home rank)
     float route_scale;
     const float* x;             // [T][H]
@@ -76,8 +77,11 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream);
 // dispatch permutation + work list from p.topk_idx alone (no routing, no shared entries)
 cudaError_t launch_permute(const RouteParams& p, cudaStream_t stream);
 // y[t][h] = sum_j w[t][j] * rows[t*k+j][h] (+ shared[t][h] * sigmoid(logit[t]) or + shared[t][h])
-cudaError_t launch_ep_finish(const float* rows, const float* topk_w, const float* shared_rows, const float* sh_logit, float* y,
-                             int T, int H, int k, cudaStream_t stream);
+cudaError_t launch_ep_finish(const float* rows, const int32_t* slot, const float* topk_w, const float* shared_rows, const float* sh_logit,
+                             float* y, int T, int H, int k, cudaStream_t stream);
+// fixed-size dispatch: fill send[world*cap][row_bytes] with the pairs of each destination rank in pair order
+cudaError_t launch_ep_pack(const int32_t* topk_idx, const int8_t* x_q, const float* x_d, int d_stride, uint8_t* send, int32_t* slot,
+                           int T, int k, int H, int experts_per_rank, int world, int cap, int row_bytes, cudaStream_t stream);
 cudaError_t launch_gate_up(const GemvParams& p, int max_entries, cudaStream_t stream);
 cudaError_t launch_down(const GemvParams& p, int max_entries, cudaStream_t stream);
 

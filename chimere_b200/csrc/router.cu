@@ -130,8 +130,9 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i) {
     for (int i = tid; i < 2048; i += 256) warp_cnt[i] = 0;
     __syncthreads();
     // ids outside [0, E) mark pairs that are not there (padding of a fixed-size exchange): they get no work
+    const int istr = p.idx_stride > 1 ? p.idx_stride : 1;
     for (int q = tid; q < P; q += 256) {
-        const int e = __ldcg(p.topk_idx + q);
+        const int e = __ldcg(p.topk_idx + (size_t)q * istr);
         if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
     }
     __syncthreads();
@@ -186,7 +187,7 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i) {
     for (int base = 0; base < P; base += 256) {
         const int q = base + tid;
         bool valid = q < P;
-        int e = valid ? __ldcg(p.topk_idx + q) : -1;
+        int e = valid ? __ldcg(p.topk_idx + (size_t)q * istr) : -1;
         valid = valid && e >= 0 && e < E;
         if (!valid) e = 0x40000000 + tid;
         const unsigned same = __match_any_sync(0xffffffffu, e);
@@ -305,19 +306,67 @@ __global__ void __launch_bounds__(256) permute_kernel(const RouteParams p) {
 // Final step of an expert-parallel layer on the tokens' home rank: routing-weighted sum of the k expert
 // rows of every token in slot order (weighted_combine_kernel, chimere_kernels.cu:1551-1565) plus the
 // sigmoid-gated shared expert (sigmoid_gate_add_kernel, scratch_pool.rs:266-277).
-__global__ void ep_finish_kernel(const float* rows, const float* topk_w, const float* shared_rows, const float* sh_logit,
-                                 float* y, int T, int H, int k) {
+__global__ void ep_finish_kernel(const float* rows, const int32_t* slot, const float* topk_w, const float* shared_rows,
+                                 const float* sh_logit, float* y, int T, int H, int k) {
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (int64_t)T * H) return;
     const int t = (int)(idx / H), h = (int)(idx - (int64_t)t * H);
     float sum = 0.0f;
-    for (int j = 0; j < k; ++j) sum = fmaf(topk_w[(size_t)t * k + j], rows[((size_t)t * k + j) * H + h], sum);
+    for (int j = 0; j < k; ++j) {
+        const size_t r = slot ? (size_t)slot[t * k + j] : (size_t)t * k + j;   // where pair (t, j) came back
+        sum = fmaf(topk_w[(size_t)t * k + j], rows[r * H + h], sum);
+    }
     if (shared_rows) {
         const float sh = shared_rows[(size_t)t * H + h];
         if (sh_logit) sum = fmaf(sh, sigmoid_ref(sh_logit[t]), sum);
         else sum = sh + sum;
     }
     y[idx] = sum;
+}
+
+// Fixed-size dispatch of an expert-parallel layer.  Slot s = (destination rank d, position i) of the send
+// buffer holds the i-th pair (in pair order) whose expert lives on rank d, or id -1 if there are fewer.
+// One CTA per slot finds its pair by scanning the T*k ids, copies the pair's Q8_1 planes and local expert
+// id, and notes the slot for the way back.  Row: [H int8][d_stride f32][int32 id], row_bytes a multiple of 16.
+__global__ void __launch_bounds__(128) ep_pack_kernel(const int32_t* topk_idx, const int8_t* x_q, const float* x_d, int d_stride,
+                                                      uint8_t* send, int32_t* slot, int T, int k, int H, int experts_per_rank, int cap,
+                                                      int row_bytes) {
+    __shared__ int s_pair;
+    const int s = blockIdx.x, d = s / cap, i = s - d * cap, P = T * k;
+    if (threadIdx.x < 32) {
+        // warp 0: the i-th pair with destination d, pairs in ascending order
+        int found = -1, seen = 0;
+        for (int base = 0; base < P && found < 0; base += 32) {
+            const int q = base + threadIdx.x;
+            const bool hit = q < P && (__ldcg(topk_idx + q) / experts_per_rank) == d;
+            const unsigned m = __ballot_sync(0xffffffffu, hit);
+            const int c = __popc(m);
+            if (seen + c > i) {
+                unsigned mm = m;
+                for (int r = 0; r < i - seen; ++r) mm &= mm - 1;   // drop the first i - seen hits
+                found = base + __ffs(mm) - 1;
+            }
+            seen += c;
+        }
+        if (threadIdx.x == 0) s_pair = found;
+    }
+    __syncthreads();
+    const int pair = s_pair;
+    uint8_t* row = send + (size_t)s * row_bytes;
+    int32_t* idp = reinterpret_cast<int32_t*>(row + H + 4 * d_stride);
+    if (pair < 0) {
+        if (threadIdx.x == 0) *idp = -1;
+        return;
+    }
+    const int t = pair / k;
+    const uint4* sq = reinterpret_cast<const uint4*>(x_q + (size_t)t * H);
+    for (int v = threadIdx.x; v < H / 16; v += blockDim.x) reinterpret_cast<uint4*>(row)[v] = sq[v];
+    const float* sd = x_d + (size_t)t * d_stride;
+    for (int v = threadIdx.x; v < d_stride; v += blockDim.x) reinterpret_cast<float*>(row + H)[v] = sd[v];
+    if (threadIdx.x == 0) {
+        *idp = __ldcg(topk_idx + pair) - d * experts_per_rank;
+        slot[pair] = s;
+    }
 }
 
 static size_t route_smem(int TT, int TE) {
@@ -331,11 +380,17 @@ cudaError_t launch_permute(const RouteParams& p, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
-cudaError_t launch_ep_finish(const float* rows, const float* topk_w, const float* shared_rows, const float* sh_logit, float* y,
-                             int T, int H, int k, cudaStream_t stream) {
+cudaError_t launch_ep_finish(const float* rows, const int32_t* slot, const float* topk_w, const float* shared_rows, const float* sh_logit,
+                             float* y, int T, int H, int k, cudaStream_t stream) {
     const int64_t n = (int64_t)T * H;
     if (n <= 0) return cudaSuccess;
-    ep_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(rows, topk_w, shared_rows, sh_logit, y, T, H, k);
+    ep_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(rows, slot, topk_w, shared_rows, sh_logit, y, T, H, k);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_ep_pack(const int32_t* topk_idx, const int8_t* x_q, const float* x_d, int d_stride, uint8_t* send, int32_t* slot,
+                           int T, int k, int H, int experts_per_rank, int world, int cap, int row_bytes, cudaStream_t stream) {
+    ep_pack_kernel<<<world * cap, 128, 0, stream>>>(topk_idx, x_q, x_d, d_stride, send, slot, T, k, H, experts_per_rank, cap, row_bytes);
     return cudaGetLastError();
 }
 

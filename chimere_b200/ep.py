@@ -122,10 +122,9 @@ class ExpertParallelMoE:
         # combine: the pairs' expert rows come home, back into (token, slot) order
         back = all_to_all_rows(self.ws_owner.pair_out(self.max_rows)[:n], recv_counts, send_counts, self.back, self.group)
         self.rows_pair[:T * k].index_copy_(0, plan.order, back)
-        abi.check(lib.chimere_b200_moe_ep_finish(C.byref(self.home), self.rows_pair.data_ptr(), T, C.byref(self.ws_home.ws),
+        abi.check(lib.chimere_b200_moe_ep_finish(C.byref(self.home), self.rows_pair.data_ptr(), None, T, C.byref(self.ws_home.ws),
                                                  out.data_ptr(), st), "ep_finish")
         return out
-
 
     # ---- decode-size batches: fixed-size exchange, no host synchronisation, CUDA-graph capturable ----
     def forward_padded(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -142,34 +141,22 @@ class ExpertParallelMoE:
             rb = (H + 4 * ds + 4 + 15) & ~15
             self._pad = dict(ds=ds, rb=rb,
                              send=torch.empty(G * C_, rb, dtype=torch.uint8, device=dev), recv=torch.empty(G * C_, rb, dtype=torch.uint8, device=dev),
-                             back=torch.empty(G * C_, H, dtype=torch.float32, device=dev), ar=torch.arange(T * k, device=dev))
+                             back=torch.empty(G * C_, H, dtype=torch.float32, device=dev),
+                             slot=torch.zeros(T * k, dtype=torch.int32, device=dev))
         pd = self._pad
-        ds, send, recv = pd["ds"], pd["send"], pd["recv"]
-        abi.check(lib.chimere_b200_moe_route_home(C.byref(self.home), x.data_ptr(), T, C.byref(self.ws_home.ws), st), "route_home")
-        abi.check(lib.chimere_b200_moe_shared_expert(C.byref(self.home), T, C.byref(self.ws_home.ws), st), "shared_expert")
-        flat = self.ws_home.topk_idx(T, k).reshape(-1).to(torch.int64)
-        dest = torch.div(flat, self.E_loc, rounding_mode="floor")
-        order = torch.sort(dest, stable=True).indices
-        sdest = dest[order]
-        counts = torch.bincount(dest, minlength=G)
-        starts = torch.cumsum(counts, 0) - counts
-        slot = sdest * C_ + (pd["ar"] - starts[sdest])            # where each pair sits in the padded send buffer
-        tok = torch.div(order, k, rounding_mode="floor")
-        ids = send[:, H + 4 * ds:H + 4 * ds + 4].view(torch.int32)
-        ids.fill_(-1)
-        ids.index_copy_(0, slot, (flat[order] - sdest * self.E_loc).to(torch.int32)[:, None])
-        send[:, :H].view(torch.int8).index_copy_(0, slot, self.ws_home.x_q(T)[tok])
-        send[:, H:H + 4 * ds].view(torch.float32).index_copy_(0, slot, self.ws_home.x_d(T)[tok])
-        dist.all_to_all_single(recv, send, group=self.group)
+        rb, send, recv, back, slot = pd["rb"], pd["send"], pd["recv"], pd["back"], pd["slot"]
         n = G * C_
-        self.ws_owner.x_q(n).copy_(recv[:, :H].view(torch.int8))
-        self.ws_owner.x_d(n).copy_(recv[:, H:H + 4 * ds].view(torch.float32))
-        self.ws_owner.topk_idx(n, 1).copy_(recv[:, H + 4 * ds:H + 4 * ds + 4].view(torch.int32))
-        abi.check(lib.chimere_b200_moe_experts(C.byref(self.owner), n, C.byref(self.ws_owner.ws), st), "experts")
-        dist.all_to_all_single(pd["back"], self.ws_owner.pair_out(n), group=self.group)
-        self.rows_pair[:T * k].index_copy_(0, order, pd["back"][slot])
-        abi.check(lib.chimere_b200_moe_ep_finish(C.byref(self.home), self.rows_pair.data_ptr(), T, C.byref(self.ws_home.ws),
+        abi.check(lib.chimere_b200_moe_route_home(C.byref(self.home), x.data_ptr(), T, C.byref(self.ws_home.ws), st), "route_home")
+        abi.check(lib.chimere_b200_moe_ep_pack(C.byref(self.home), T, C.byref(self.ws_home.ws), send.data_ptr(), slot.data_ptr(),
+                                               self.E_loc, G, C_, rb, st), "ep_pack")
+        dist.all_to_all_single(recv, send, group=self.group)
+        # the shared expert needs nothing from other ranks: it runs while the dispatch is in flight
+        abi.check(lib.chimere_b200_moe_shared_expert(C.byref(self.home), T, C.byref(self.ws_home.ws), st), "shared_expert")
+        abi.check(lib.chimere_b200_moe_experts_packed(C.byref(self.owner), n, recv.data_ptr(), rb, C.byref(self.ws_owner.ws), st), "experts")
+        dist.all_to_all_single(back, self.ws_owner.pair_out(n), group=self.group)
+        abi.check(lib.chimere_b200_moe_ep_finish(C.byref(self.home), back.data_ptr(), slot.data_ptr(), T, C.byref(self.ws_home.ws),
                                                  out.data_ptr(), st), "ep_finish")
+        self.last_recv_rows = n
         return out
 
 

@@ -199,8 +199,19 @@ int chimere_b200_moe_shared_expert(const chimere_moe_layer* w, int T, chimere_mo
  * Expert outputs (down . act(gate/up . x), unweighted) land in ws->pair_out[row][H]. */
 int chimere_b200_moe_experts(const chimere_moe_layer* w_local, int n_rows, chimere_moe_workspace* ws,
                              cudaStream_t stream);
-/* y[t] = sum_j topk_w[t][j] * d_rows[t*top_k + j] (slot order) + sigmoid-gated shared row. */
-int chimere_b200_moe_ep_finish(const chimere_moe_layer* w, const float* d_rows, int T,
+/* The same with the rows where a fixed-size exchange left them: row r = [H int8][ceil4(H/32) f32][int32 local
+ * expert id], row_bytes a multiple of 16; id -1 = no pair in this row (it costs nothing). */
+int chimere_b200_moe_experts_packed(const chimere_moe_layer* w_local, int n_rows, const void* d_rows,
+                                    int row_bytes, chimere_moe_workspace* ws, cudaStream_t stream);
+/* Home rank, fixed-size dispatch: fills d_send[world*cap][row_bytes] (rows in the format above; slot d*cap + i =
+ * i-th pair, in pair order, whose expert lives on rank d) and d_slot[T*top_k] = the slot of every pair.
+ * cap >= T*top_k.  Needs the results of route_home in `ws`. */
+int chimere_b200_moe_ep_pack(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, void* d_send,
+                             int32_t* d_slot, int experts_per_rank, int world, int cap, int row_bytes,
+                             cudaStream_t stream);
+/* y[t] = sum_j topk_w[t][j] * row(t, j) (slot order) + sigmoid-gated shared row, where row(t, j) is
+ * d_rows[d_slot[t*top_k + j]] or, with d_slot == NULL, d_rows[t*top_k + j]. */
+int chimere_b200_moe_ep_finish(const chimere_moe_layer* w, const float* d_rows, const int32_t* d_slot, int T,
                                chimere_moe_workspace* ws, float* d_y, cudaStream_t stream);
 
 /* Parity tap: integer block dot products.  For `nrows` weight rows of type `wtype` with `ncols`
