@@ -79,7 +79,7 @@ Layout make_layout(const chimere_moe_layer* w, int T) {
     L.x_q8 = o; o += up256((size_t)T * (H / 32) * kQ81Bytes);
     L.perm = o; o += up256((size_t)T * k * 4);
     L.offsets = o; o += up256((size_t)(E + 1) * 4);
-    L.group_list = o; o += up256((size_t)(kListHeader + 4 * L.max_entries) * 4);
+    L.group_list = o; o += up256((size_t)(kListHeader + kListEntry * L.max_entries) * 4);
     L.counters = o; o += up256((size_t)L.n_counters * 4);
     L.inter_q8 = o; o += up256(pairs * L.inter_stride);
     L.pair_out = o; o += up256(pairs * H * 4);
@@ -139,7 +139,7 @@ int chimere_b200_moe_workspace_init(chimere_moe_workspace* ws, void* d_arena, si
     ws->status = (int32_t*)(base + L.status);
     cudaError_t e = cudaMemsetAsync(ws->counters, 0, (size_t)L.n_counters * 4, stream);
     if (e == cudaSuccess) e = cudaMemsetAsync(ws->status, 0, 256, stream);
-    if (e == cudaSuccess) e = cudaMemsetAsync(ws->group_list, 0, (size_t)(kListHeader + 4 * L.max_entries) * 4, stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(ws->group_list, 0, (size_t)(kListHeader + kListEntry * L.max_entries) * 4, stream);
     return cuda_rc(e);
 }
 

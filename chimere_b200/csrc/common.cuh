@@ -18,11 +18,14 @@ constexpr int kSharedGroupTokens = 2;  // ... for the shared expert (every token
 constexpr int kMaxTopK = 8;
 constexpr int kMaxExperts = 256;
 
-// Work list the routing kernel leaves for the grouped GEMV kernels:
-// word 0 = number of entries, entries start at word 4, four words each:
-// { expert id (-1 = shared expert), start, m, 0 }.  Routed entry: pairs perm[start .. start+m).
-// Shared entry: tokens start .. start+m.
+// Work list the routing kernel leaves for the grouped GEMV kernels: word 0 = number of entries, word 1 = routed
+// entries, word 2 = shared-expert entries; entries start at word 4, kListEntry words each:
+// { expert id (-1 = shared expert), start, m, 0, pair row of token 0 .. 7 }.  Routed entry: pairs
+// perm[start .. start+m) (the pair rows repeat them so a kernel needs no second look-up); shared entry:
+// tokens start .. start+m, pair rows T*top_k + token.  The shared expert's entries come first: they carry the
+// most tokens and should start early.
 constexpr int kListHeader = 4;
+constexpr int kListEntry = 12;
 
 // status bits a kernel may raise in the workspace status word
 constexpr int kStatusWaitTimeout = 1;

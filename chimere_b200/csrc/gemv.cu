@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(kThreads) gate_up_kernel(const GemvParams p) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n_entries = __ldcg(p.group_list);
     if ((int)blockIdx.y >= n_entries) return;
-    const int* ent = p.group_list + kListHeader + 4 * blockIdx.y;
+    const int* ent = p.group_list + kListHeader + kListEntry * blockIdx.y;
     const int expert = __ldcg(ent), start = __ldcg(ent + 1), m = __ldcg(ent + 2);
     const bool shared = expert < 0;
     if ((shared ? p.type_shared : p.type_routed) != TYPE) return;
@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(kThreads) down_kernel(const GemvParams p, cons
     } else {
         const int n_entries = __ldcg(p.group_list);
         if ((int)blockIdx.y >= n_entries) return;
-        const int* ent = p.group_list + kListHeader + 4 * blockIdx.y;
+        const int* ent = p.group_list + kListHeader + kListEntry * blockIdx.y;
         expert = __ldcg(ent); start = __ldcg(ent + 1); m = __ldcg(ent + 2);
         shared = expert < 0;
         if ((shared ? p.type_shared : p.type_routed) != TYPE) return;

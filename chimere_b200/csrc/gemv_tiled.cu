@@ -90,11 +90,12 @@ __global__ void __launch_bounds__(kThreadsT, 4) tile_kernel(const GemvParams p, 
     __shared__ int s_tok[kMaxGroupTokens];
     __shared__ int s_done[kMaxGroupTokens];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // entries are taken from the end of the list: the shared expert's (every token: the most work) start first
+    // one look-up names everything the CTA needs: the entry (expert, token count, pair rows)
+    const int4* entv = reinterpret_cast<const int4*>(p.group_list + kListHeader + kListEntry * blockIdx.y);
     const int n_entries = __ldcg(p.group_list);
+    const int4 e0 = __ldcg(entv), e1 = __ldcg(entv + 1), e2 = __ldcg(entv + 2);
     if ((int)blockIdx.y >= n_entries) return;
-    const int* ent = p.group_list + kListHeader + 4 * (n_entries - 1 - (int)blockIdx.y);
-    const int expert = __ldcg(ent), start = __ldcg(ent + 1), m = __ldcg(ent + 2);
+    const int expert = e0.x, m = e0.z;
     const bool shared = expert < 0;
     if ((shared ? p.type_shared : p.type_routed) != TYPE) return;
     const int nrows = shared ? p.nrows_shared : p.nrows_routed;
@@ -113,16 +114,22 @@ __global__ void __launch_bounds__(kThreadsT, 4) tile_kernel(const GemvParams p, 
     const uint8_t* wa = (STAGE == kStageGateUp ? (shared ? p.sh_b : p.w_b + (size_t)expert * p.stride_b)
                                                : (shared ? p.sh_a : p.w_a + (size_t)expert * p.stride_a)) + (size_t)(tile0 + wr_id) * tb;
     const uint8_t* wb = DUAL ? (shared ? p.sh_a : p.w_a + (size_t)expert * p.stride_a) + (size_t)(tile0 + wr_id) * tb : nullptr;
+    const int ngroups = (nb + kGroupUnits - 1) / kGroupUnits;
     if (tile_valid) {
-        prefetch_l2(wa + (size_t)wk_id * Tiled<TYPE>::kChunkBytes / Tiled<TYPE>::kGroupsPerChunk + lane * 16);
-        if (DUAL) prefetch_l2(wb + (size_t)wk_id * Tiled<TYPE>::kChunkBytes / Tiled<TYPE>::kGroupsPerChunk + lane * 16);
+        // ask for the warp's units now: they arrive in L2 while the activations are staged
+        for (int g = wk_id; g < ngroups; g += wk) {
+            const int nu = min(kGroupUnits, nb - g * kGroupUnits);
+            Tiled<TYPE>::prefetch(wa, g, lane, nu);
+            if (DUAL) Tiled<TYPE>::prefetch(wb, g, lane, nu);
+        }
     }
-
-    if (tid < m) {
-        int t, prow;
-        if (shared) { t = start + tid; prow = p.T * p.top_k + t; }
-        else { prow = __ldcg(p.perm + start + tid); t = prow / p.top_k; }
-        s_row[tid] = prow; s_tok[tid] = t;
+    if (tid < kMaxGroupTokens) {
+        const int rows[kMaxGroupTokens] = {e1.x, e1.y, e1.z, e1.w, e2.x, e2.y, e2.z, e2.w};
+        int prow = 0;
+#pragma unroll
+        for (int j = 0; j < kMaxGroupTokens; ++j) if (j == tid) prow = rows[j];
+        s_row[tid] = prow;
+        s_tok[tid] = shared ? prow - p.T * p.top_k : prow / p.top_k;
     }
     __syncthreads();
     // activations of the entry's tokens: int8 plane and f32 scale plane, 16 bytes per thread and step
@@ -135,7 +142,6 @@ __global__ void __launch_bounds__(kThreadsT, 4) tile_kernel(const GemvParams p, 
     }
     __syncthreads();
 
-    const int ngroups = (nb + kGroupUnits - 1) / kGroupUnits;
 #pragma unroll
     for (int mat = 0; mat < (DUAL ? 2 : 1); ++mat) {
         // one set of accumulators: the partial sums of a matrix go to shared memory before the next starts

@@ -158,25 +158,24 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i) {
     }
     int total_routed = 0;
     for (int w = 0; w < 8; ++w) total_routed += scan[8 + w];
-    // routed work entries
+    // shared-expert entries first (all tokens, identity order), then the routed ones
+    const int nsh = p.has_shared ? (p.T + kSharedGroupTokens - 1) / kSharedGroupTokens : 0;
     if (p.list_mode == 1) total_routed = 0;
+    for (int i = tid; i < nsh; i += 256) {
+        int* ent = p.group_list + kListHeader + kListEntry * i;
+        const int t0 = i * kSharedGroupTokens, mm = min(kSharedGroupTokens, p.T - t0);
+        ent[0] = -1; ent[1] = t0; ent[2] = mm; ent[3] = 0;
+        for (int j = 0; j < kMaxGroupTokens; ++j) ent[4 + j] = j < mm ? p.T * p.top_k + t0 + j : 0;
+    }
     for (int i = 0; i < (p.list_mode == 1 ? 0 : nent); ++i) {
-        int* ent = p.group_list + kListHeader + 4 * (ent0 + i);
+        int* ent = p.group_list + kListHeader + kListEntry * (nsh + ent0 + i);
         ent[0] = tid;
         ent[1] = off + i * kMaxGroupTokens;
         ent[2] = min(kMaxGroupTokens, cnt - i * kMaxGroupTokens);
         ent[3] = 0;
     }
-    // shared-expert entries: all tokens, identity order
-    const int nsh = p.has_shared ? (p.T + kSharedGroupTokens - 1) / kSharedGroupTokens : 0;
-    for (int i = tid; i < nsh; i += 256) {
-        int* ent = p.group_list + kListHeader + 4 * (total_routed + i);
-        ent[0] = -1;
-        ent[1] = i * kSharedGroupTokens;
-        ent[2] = min(kSharedGroupTokens, p.T - i * kSharedGroupTokens);
-        ent[3] = 0;
-    }
     if (tid == 0) {
+        for (int i = 0; i < 4; ++i) p.counters[kCtrQueue + i] = 0;
         p.group_list[0] = total_routed + nsh;
         p.group_list[1] = total_routed;
         p.group_list[2] = nsh;
@@ -206,6 +205,12 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i) {
             warp_cnt[warp * 256 + e] = 0;
         }
         __syncthreads();
+    }
+    // the pair rows of every routed entry (perm was written by this CTA: visible after the barrier above)
+    for (int i = 0; i < (p.list_mode == 1 ? 0 : nent); ++i) {
+        int* ent = p.group_list + kListHeader + kListEntry * (nsh + ent0 + i);
+        const int mm = min(kMaxGroupTokens, cnt - i * kMaxGroupTokens);
+        for (int j = 0; j < kMaxGroupTokens; ++j) ent[4 + j] = j < mm ? p.perm[off + i * kMaxGroupTokens + j] : 0;
     }
 }
 
@@ -443,7 +448,7 @@ constexpr size_t kNoAllocXd = kNoAllocXq + (size_t)kNoAllocMaxT * kNoAllocMaxH; 
 constexpr size_t kNoAllocPerm = kNoAllocXd + (size_t)kNoAllocMaxT * (kNoAllocMaxH / 32) * 4;  // [T*8] i32
 constexpr size_t kNoAllocOffsets = kNoAllocPerm + (size_t)kNoAllocMaxT * kMaxTopK * 4;        // [257] i32
 constexpr size_t kNoAllocList = kNoAllocOffsets + 1280;                                       // work list
-constexpr size_t kNoAllocBytes = kNoAllocList + (size_t)(kListHeader + 4 * (kMaxExperts + kNoAllocMaxT * kMaxTopK + kNoAllocMaxT)) * 4 + 256;
+constexpr size_t kNoAllocBytes = kNoAllocList + (size_t)(kListHeader + kListEntry * (kMaxExperts + kNoAllocMaxT * kMaxTopK + kNoAllocMaxT)) * 4 + 256;
 
 static __device__ __align__(256) unsigned char g_route_scratch[kNoAllocBytes];   // ~680 KiB per GPU
 

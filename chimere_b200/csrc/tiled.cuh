@@ -64,6 +64,12 @@ template <> struct Tiled<CHIMERE_TYPE_Q4_0> {
         for (int u = 0; u < kGroupUnits; ++u)
             if (u < nu) { r.v[u] = ldg128(g + u * kUnitBytes + lane * 16); r.d[u] = ldg_u16(g + u * kUnitBytes + 512 + lane * 2); }
     }
+    __device__ static __forceinline__ void prefetch(const uint8_t* tile, int grp, int lane, int nu) {
+        const uint8_t* g = tile + (size_t)grp * (kGroupUnits * kUnitBytes);
+#pragma unroll
+        for (int u = 0; u < kGroupUnits; ++u)
+            if (u < nu) prefetch_l2(g + u * kUnitBytes + lane * 16);
+    }
     __device__ static __forceinline__ void decode(const Regs& r, int u, int (&w)[8]) {
         const uint32_t x[4] = {r.v[u].x, r.v[u].y, r.v[u].z, r.v[u].w};
 #pragma unroll
@@ -85,6 +91,13 @@ template <> struct Tiled<CHIMERE_TYPE_IQ3_S> {
             if (u < nu) r.v[u] = ldg128(g + (u0 + u) * 512 + lane * 16);
         r.d = ldg_u16(g + 4096 + lane * 2);
         r.sc = ldg_u32(g + 4160 + lane * 4) >> (16 * (grp & 1));   // this half's four scale nibbles
+    }
+    __device__ static __forceinline__ void prefetch(const uint8_t* tile, int grp, int lane, int nu) {
+        const uint8_t* g = tile + (size_t)(grp >> 1) * kSuperBytes;
+        const int u0 = (grp & 1) * 4;
+#pragma unroll
+        for (int u = 0; u < kGroupUnits; ++u)
+            if (u < nu) prefetch_l2(g + (u0 + u) * 512 + lane * 16);
     }
     __device__ static __forceinline__ void decode(const Regs& r, int u, int (&w)[8]) {
         const uint32_t x[4] = {r.v[u].x, r.v[u].y, r.v[u].z, r.v[u].w};
@@ -114,6 +127,12 @@ template <> struct Tiled<CHIMERE_TYPE_Q8_0> {
                 r.v[2 * u + 1] = ldg128(g + u * kUnitBytes + 512 + lane * 16);
                 r.d[u] = ldg_u16(g + u * kUnitBytes + 1024 + lane * 2);
             }
+    }
+    __device__ static __forceinline__ void prefetch(const uint8_t* tile, int grp, int lane, int nu) {
+        const uint8_t* g = tile + (size_t)grp * (kGroupUnits * kUnitBytes);
+#pragma unroll
+        for (int u = 0; u < kGroupUnits; ++u)
+            if (u < nu) { prefetch_l2(g + u * kUnitBytes + lane * 16); prefetch_l2(g + u * kUnitBytes + 512 + lane * 16); }
     }
     __device__ static __forceinline__ void decode(const Regs& r, int u, int (&w)[8]) {
         w[0] = (int)r.v[2 * u].x; w[1] = (int)r.v[2 * u].y; w[2] = (int)r.v[2 * u].z; w[3] = (int)r.v[2 * u].w;
