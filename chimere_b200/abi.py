@@ -70,6 +70,9 @@ PROTOTYPES = {
     "chimere_b200_moe_ep_finish": (C.c_int, [_LAYER_P, _P, _P, C.c_int, _WS_P, _P, _P]),
     "chimere_b200_moe_permute": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P]),
     "chimere_b200_block_sumi": (C.c_int, [C.c_int, _P, _P, _P, C.c_int, C.c_int, _P]),
+    "chimere_b200_mma128_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "chimere_b200_pack_mma128": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, _P]),
+    "chimere_b200_gemm_i8": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P]),
     "chimere_b200_rmsnorm": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_float, _P]),
     "chimere_b200_abi_version": (C.c_int, []),
     "chimere_b200_built_for_sm": (C.c_int, []),

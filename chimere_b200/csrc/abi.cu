@@ -7,6 +7,7 @@
 // memory or synchronises, except chimere_b200_moe_forward_host which waits for its stream.
 #include <cstdio>
 #include <cstring>
+#include <vector>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -450,6 +451,44 @@ int chimere_b200_block_sumi(int wtype, const void* d_w, const void* d_xq8, int32
     if (!type_ok(wtype)) return -3;
     if (ncols <= 0 || nrows < 0 || ncols % type_cols_multiple(wtype)) return -2;
     return cuda_rc(launch_block_sumi(wtype, d_w, d_xq8, d_sumi, ncols, nrows, stream));
+}
+
+// ---------------------------------------------------------------- tcgen05 block-scaled GEMM --
+size_t chimere_b200_mma128_bytes(int rows, int cols) {
+    if (rows <= 0 || cols <= 0 || cols % 32) return 0;
+    return (size_t)((rows + 127) / 128) * (cols / 32) * (4096 + 512);
+}
+
+int chimere_b200_pack_mma128(const int8_t* d_q, const float* d_scales, void* d_out, int rows, int cols, cudaStream_t stream) {
+    if (!d_q || !d_scales || !d_out) return -1;
+    if (rows <= 0 || cols <= 0 || cols % 32) return -2;
+    return cuda_rc(launch_pack_mma128(d_q, d_scales, (uint8_t*)d_out, rows, cols, stream));
+}
+
+int chimere_b200_gemm_i8(const void* d_a, const void* d_b, int rows, int tokens, int cols, float* d_out, void* d_items,
+                         int32_t* d_status, cudaStream_t stream) {
+    if (!d_a || !d_b || !d_out || !d_items || !d_status) return -1;
+    if (rows <= 0 || tokens <= 0 || cols <= 0 || cols % 32) return -2;
+    const int rt = (rows + 127) / 128, tt = (tokens + 127) / 128, nb = cols / 32;
+    std::vector<GemmItem> items;
+    for (int i = 0; i < rt; ++i)
+        for (int j = 0; j < tt; ++j) {
+            GemmItem it{};
+            it.a_offset = (int64_t)i * nb * (4096 + 512);
+            it.b_offset = (int64_t)j * nb * (4096 + 512);
+            it.n_valid = tokens - j * 128 < 128 ? tokens - j * 128 : 128;
+            it.rows_valid = rows - i * 128 < 128 ? rows - i * 128 : 128;
+            it.out_row0 = i * 128; it.out_col0 = j * 128;
+            items.push_back(it);
+        }
+    cudaError_t e = cudaMemcpyAsync(d_items, items.data(), items.size() * sizeof(GemmItem), cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    e = cudaStreamSynchronize(stream);   // the host vector goes away; this entry is a test primitive, not the hot path
+    if (e != cudaSuccess) return cuda_rc(e);
+    GemmParams p{};
+    p.a_base = (const uint8_t*)d_a; p.b_base = (const uint8_t*)d_b; p.items = (const GemmItem*)d_items; p.nblocks = nb;
+    p.out = d_out; p.ldo = tokens; p.status = d_status;
+    return cuda_rc(launch_gemm_i8_f32(p, (int)items.size(), stream));
 }
 
 int chimere_b200_rmsnorm(const float* d_x, float* d_y, int T, int H, float eps, cudaStream_t stream) {

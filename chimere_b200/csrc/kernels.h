@@ -95,6 +95,18 @@ cudaError_t launch_quantize_q8_1(const float* x, void* out, int64_t ncols, int64
 cudaError_t launch_rmsnorm(const float* x, float* y, int T, int H, float eps, cudaStream_t stream);
 int down_tile_rows(int type_routed, int ncols_routed, int type_shared, int ncols_shared);
 
+// block-scaled int8 GEMM on tcgen05 (gemm_i8.cu); operands in the mma128 layout
+struct GemmItem { int64_t a_offset, b_offset; int n_valid, rows_valid, out_row0, out_col0; };
+struct GemmParams {
+    const uint8_t* a_base; const uint8_t* b_base;   // mma128 tiles; an item's operands start at base + offset
+    const GemmItem* items;
+    int nblocks;                                    // 32-wide K blocks
+    float* out; int64_t ldo;                        // f32 output, row pitch in floats
+    int32_t* status;
+};
+cudaError_t launch_gemm_i8_f32(const GemmParams& p, int n_items, cudaStream_t stream);
+cudaError_t launch_pack_mma128(const int8_t* q, const float* scales, uint8_t* out, int rows, int cols, cudaStream_t stream);
+
 // tiled32 layout (tiled.cuh): pack, kernels on packed weights, parity tap
 struct TiledGeomHost { int wk, wr; };  // warps along K x row tiles per CTA (wk * wr = 8)
 TiledGeomHost tiled_gate_up_geom(int type_routed, int type_shared, int H, bool has_shared);

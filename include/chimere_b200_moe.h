@@ -224,6 +224,21 @@ int chimere_b200_block_sumi(int wtype, const void* d_w, const void* d_xq8, int32
 int chimere_b200_block_sumi_tiled(int wtype, const void* d_packed, const void* d_xq8,
                                   int32_t* d_sumi, int ncols, int nrows, cudaStream_t stream);
 
+/* ------------------------------------------------- block-scaled int8 GEMM (tensor cores) ---- */
+/* The prefill-size primitive: out[rows][tokens] (f32, row-major) with
+ *   out[r][t] = sum over 32-wide blocks b of sa[r][b] * sb[t][b] * (int8 dot of block b of row r and token t),
+ * on tcgen05 kind::i8 MMAs (one per block, int32 accumulators in TMEM read back and scaled per block) -- the
+ * block arithmetic of the reference's Q8_0 x Q8_1 dot (src/kernels/gemv_q8_0.rs:230-255) for many tokens at
+ * once.  The reference has no prefill kernel of its own (it loops tokens, compute_graph.rs:1787-1808).
+ * Operands are int8 matrices [rows][cols] / [tokens][cols] with f32 block scales, rewritten by
+ * chimere_b200_pack_mma128 into the MMA's shared-memory order.  d_items: scratch for ceil(rows/128) *
+ * ceil(tokens/128) * 32 bytes.  This entry synchronises the stream once (it stages its tile list). */
+size_t chimere_b200_mma128_bytes(int rows, int cols);
+int chimere_b200_pack_mma128(const int8_t* d_q, const float* d_scales, void* d_out, int rows, int cols,
+                             cudaStream_t stream);
+int chimere_b200_gemm_i8(const void* d_a, const void* d_b, int rows, int tokens, int cols, float* d_out,
+                         void* d_items, int32_t* d_status, cudaStream_t stream);
+
 /* RMSNorm with unit weight over rows of length H: y = x / sqrt(mean(x^2) + eps). Used between
  * stacked layers. */
 int chimere_b200_rmsnorm(const float* d_x, float* d_y, int T, int H, float eps, cudaStream_t stream);
