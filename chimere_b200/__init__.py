@@ -4,4 +4,4 @@ The computation lives in libchimere_b200_moe.so (CUDA, built in-tree by chimere_
 is reached through the C ABI of include/chimere_b200_moe.h; this package is the thin host side.
 """
 from . import abi, formats  # noqa: F401
-from .layer import MoeScratch, MoeWeightsRaw, MoeWeightsTiled, forward_moe, forward_moe_host, route_only  # noqa: F401
+from .layer import MoeScratch, MoeWeightsPrefill, MoeWeightsRaw, MoeWeightsTiled, forward_moe_prefill, forward_moe, forward_moe_host, route_only  # noqa: F401

@@ -44,6 +44,12 @@ class MoeWorkspace(C.Structure):
     ]
 
 
+class PrefillWeights(C.Structure):
+    """struct chimere_moe_prefill_weights"""
+    _fields_ = [("gu_exps", C.c_void_p), ("stride_gu", C.c_int64), ("down_exps", C.c_void_p), ("stride_down", C.c_int64),
+                ("sh_gu", C.c_void_p), ("sh_down", C.c_void_p), ("rows_per_gu_tile", C.c_int32), ("reserved", C.c_int32)]
+
+
 _P = C.c_void_p
 _LAYER_P, _WS_P = C.POINTER(MoeLayer), C.POINTER(MoeWorkspace)
 
@@ -73,6 +79,10 @@ PROTOTYPES = {
     "chimere_b200_mma128_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "chimere_b200_pack_mma128": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, _P]),
     "chimere_b200_gemm_i8": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P]),
+    "chimere_b200_moe_pack_prefill_bytes": (C.c_size_t, [_LAYER_P]),
+    "chimere_b200_moe_pack_prefill": (C.c_int, [_LAYER_P, _P, C.c_size_t, C.POINTER(PrefillWeights), _P]),
+    "chimere_b200_moe_prefill_bytes": (C.c_size_t, [_LAYER_P, C.c_int]),
+    "chimere_b200_moe_forward_prefill": (C.c_int, [_LAYER_P, C.POINTER(PrefillWeights), _P, _P, C.c_int, _WS_P, _P]),
     "chimere_b200_rmsnorm": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_float, _P]),
     "chimere_b200_abi_version": (C.c_int, []),
     "chimere_b200_built_for_sm": (C.c_int, []),

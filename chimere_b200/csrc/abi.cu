@@ -491,6 +491,146 @@ int chimere_b200_gemm_i8(const void* d_a, const void* d_b, int rows, int tokens,
     return cuda_rc(launch_gemm_i8_f32(p, (int)items.size(), stream));
 }
 
+// ---------------------------------------------------------------- prefill path ----
+namespace {
+constexpr int kGemmMin = 32;          // pairs an expert needs to go to the GEMM
+constexpr size_t kMmaTile = 4096 + 512;
+int n_tiles_max_for(const chimere_moe_layer* w, int T) {
+    const int P = T * w->top_k;
+    int big = P / kGemmMin; if (big > w->E) big = w->E;
+    return P / 128 + big + (w->F_s > 0 ? (T + 127) / 128 : 0) + 1;
+}
+struct PrefillPlan { size_t gu, down, sh_gu, sh_down, total; int64_t sgu, sdown; int rows_per_tile; };
+PrefillPlan prefill_plan(const chimere_moe_layer* w) {
+    PrefillPlan P{};
+    const bool dual = w->act == CHIMERE_ACT_SWIGLU;
+    P.rows_per_tile = dual ? 64 : 128;
+    const size_t nbH = w->H / 32;
+    P.sgu = (int64_t)(w->F / P.rows_per_tile) * nbH * kMmaTile;
+    P.sdown = (int64_t)(w->H / 128) * (w->F / 32) * kMmaTile;
+    size_t o = 0;
+    P.gu = o; o += up256((size_t)P.sgu * w->E);
+    P.down = o; o += up256((size_t)P.sdown * w->E);
+    if (w->F_s > 0) {
+        P.sh_gu = o; o += up256((size_t)(w->F_s / P.rows_per_tile) * nbH * kMmaTile);
+        P.sh_down = o; o += up256((size_t)(w->H / 128) * (w->F_s / 32) * kMmaTile);
+    }
+    P.total = o;
+    return P;
+}
+int prefill_dims_ok(const chimere_moe_layer* w) {
+    const int rpt = w->act == CHIMERE_ACT_SWIGLU ? 64 : 128;
+    if (w->H % 128 || w->F % rpt || w->F_s % rpt) return 0;
+    return 1;
+}
+struct PrefillArena { size_t tiles, bx, b2, total; int64_t bx_stride, b2_stride; int n_tiles_max; };
+PrefillArena prefill_arena(const chimere_moe_layer* w, int T) {
+    PrefillArena A{};
+    A.n_tiles_max = n_tiles_max_for(w, T);
+    const int Fmax = w->F > w->F_s ? w->F : w->F_s;
+    A.bx_stride = (int64_t)(w->H / 32) * kMmaTile;
+    A.b2_stride = (int64_t)(Fmax / 32) * kMmaTile;
+    size_t o = 0;
+    A.tiles = o; o += up256((size_t)(4 + 4 * A.n_tiles_max) * 4);
+    A.bx = o; o += up256((size_t)A.n_tiles_max * A.bx_stride);
+    A.b2 = o; o += up256((size_t)A.n_tiles_max * A.b2_stride);
+    A.total = o;
+    return A;
+}
+}  // namespace
+
+size_t chimere_b200_moe_pack_prefill_bytes(const chimere_moe_layer* raw) {
+    if (validate_layer(raw) != 0 || raw->layout != CHIMERE_LAYOUT_GGML || !prefill_dims_ok(raw)) return 0;
+    return prefill_plan(raw).total;
+}
+
+int chimere_b200_moe_pack_prefill(const chimere_moe_layer* raw, void* d_arena, size_t bytes, chimere_moe_prefill_weights* out,
+                                  cudaStream_t stream) {
+    int rc = validate_layer(raw);
+    if (rc) return rc;
+    if (!d_arena || !out) return -1;
+    if (raw->layout != CHIMERE_LAYOUT_GGML || !prefill_dims_ok(raw)) return -2;
+    if ((uintptr_t)d_arena & 255) return -5;
+    const PrefillPlan P = prefill_plan(raw);
+    if (bytes < P.total) return -4;
+    const bool dual = raw->act == CHIMERE_ACT_SWIGLU;
+    uint8_t* base = (uint8_t*)d_arena;
+    cudaError_t e = cudaSuccess;
+    if (dual) e = launch_pack_mma128_ggml(raw->type_gate, raw->gate_exps, base + P.gu, raw->E, raw->F, raw->H, 1, raw->stride_gate, P.sgu, stream);
+    if (e == cudaSuccess) e = launch_pack_mma128_ggml(raw->type_up, raw->up_exps, base + P.gu, raw->E, raw->F, raw->H, dual ? 2 : 0, raw->stride_up, P.sgu, stream);
+    if (e == cudaSuccess) e = launch_pack_mma128_ggml(raw->type_down, raw->down_exps, base + P.down, raw->E, raw->H, raw->F, 0, raw->stride_down, P.sdown, stream);
+    if (raw->F_s > 0) {
+        if (dual && e == cudaSuccess) e = launch_pack_mma128_ggml(raw->type_sh_gate, raw->sh_gate, base + P.sh_gu, 1, raw->F_s, raw->H, 1, 0, 0, stream);
+        if (e == cudaSuccess) e = launch_pack_mma128_ggml(raw->type_sh_up, raw->sh_up, base + P.sh_gu, 1, raw->F_s, raw->H, dual ? 2 : 0, 0, 0, stream);
+        if (e == cudaSuccess) e = launch_pack_mma128_ggml(raw->type_sh_down, raw->sh_down, base + P.sh_down, 1, raw->H, raw->F_s, 0, 0, 0, stream);
+    }
+    out->gu_exps = base + P.gu; out->stride_gu = P.sgu;
+    out->down_exps = base + P.down; out->stride_down = P.sdown;
+    out->sh_gu = raw->F_s > 0 ? base + P.sh_gu : nullptr;
+    out->sh_down = raw->F_s > 0 ? base + P.sh_down : nullptr;
+    out->rows_per_gu_tile = P.rows_per_tile; out->reserved = 0;
+    return cuda_rc(e);
+}
+
+size_t chimere_b200_moe_prefill_bytes(const chimere_moe_layer* w, int max_T) {
+    if (validate_layer(w) != 0 || max_T <= 0 || !prefill_dims_ok(w)) return 0;
+    return prefill_arena(w, max_T).total;
+}
+
+int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, const float* d_x, float* d_y,
+                                     int T, chimere_moe_workspace* ws, cudaStream_t stream) {
+    int rc = check_call(w, d_x, d_y, T, ws);
+    if (rc) return rc;
+    if (!pw || !ws->prefill_arena) return -1;
+    if (w->layout != CHIMERE_LAYOUT_TILED32 || !prefill_dims_ok(w)) return -2;
+    const PrefillArena A = prefill_arena(w, ws->max_T);
+    if (ws->prefill_bytes < A.total || ((uintptr_t)ws->prefill_arena & 255)) return -4;
+    uint8_t* base = (uint8_t*)ws->prefill_arena;
+    int32_t* tiles = (int32_t*)(base + A.tiles);
+    const Layout L = make_layout(w, ws->max_T);
+    const int n_tiles_max = n_tiles_max_for(w, T);
+    const bool dual = w->act == CHIMERE_ACT_SWIGLU;
+
+    cudaError_t e = launch_route(route_params(w, d_x, T, ws), stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    e = launch_build_tiles(ws->offsets, ws->perm, tiles, ws->group_list, w->E, T, w->top_k, w->F_s > 0, kGemmMin, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    e = launch_gather_tiles(tiles, ws->perm, ws->x_q, ws->x_d, L.x_d_stride, base + A.bx, A.bx_stride, w->H, w->top_k, n_tiles_max, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    // the small experts: GEMV kernels on the rewritten work list, per-pair rows only
+    const int max_entries = max_entries_for(w, T);
+    e = launch_gate_up_tiled(gate_up_params(w, T, ws, L), max_entries, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    GemvParams dn = down_params(w, d_y, T, ws, L);
+    dn.no_combine = 1;
+    e = launch_down_tiled(dn, max_entries, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    // the large experts and the shared expert: grouped GEMMs
+    PrefillGemmParams g{};
+    g.tiles = tiles; g.perm = ws->perm; g.status = ws->status;
+    g.act = w->act; g.T = T; g.top_k = w->top_k; g.H = w->H;
+    g.a_exps = (const uint8_t*)pw->gu_exps; g.stride_a = pw->stride_gu; g.sh_a = (const uint8_t*)pw->sh_gu;
+    g.b_tiles = base + A.bx; g.b_tile_stride = A.bx_stride;
+    g.out_tiles = base + A.b2; g.out_tile_stride = A.b2_stride;
+    g.row_tiles_routed = w->F / pw->rows_per_gu_tile; g.row_tiles_shared = w->F_s / pw->rows_per_gu_tile;
+    g.row_tiles_max = g.row_tiles_routed > g.row_tiles_shared ? g.row_tiles_routed : g.row_tiles_shared;
+    g.ncols_in = w->H; g.ncols_in_shared = w->H;
+    (void)dual;
+    e = launch_prefill_gemm(g, false, n_tiles_max, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    g.a_exps = (const uint8_t*)pw->down_exps; g.stride_a = pw->stride_down; g.sh_a = (const uint8_t*)pw->sh_down;
+    g.b_tiles = base + A.b2; g.b_tile_stride = A.b2_stride;
+    g.out_tiles = nullptr; g.pair_out = ws->pair_out;
+    g.row_tiles_routed = g.row_tiles_shared = g.row_tiles_max = w->H / 128;
+    g.ncols_in = w->F; g.ncols_in_shared = w->F_s;
+    e = launch_prefill_gemm(g, true, n_tiles_max, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    // routing-weighted sum of every token's pair rows in slot order + the sigmoid-gated shared expert
+    const float* shared_rows = w->F_s > 0 ? ws->pair_out + (size_t)T * w->top_k * w->H : nullptr;
+    const float* logit = (w->F_s > 0 && w->shexp_gate_w) ? ws->sh_gate_logit : nullptr;
+    return cuda_rc(launch_ep_finish(ws->pair_out, nullptr, ws->topk_w, shared_rows, logit, d_y, T, w->H, w->top_k, stream));
+}
+
 int chimere_b200_rmsnorm(const float* d_x, float* d_y, int T, int H, float eps, cudaStream_t stream) {
     if (!d_x || !d_y) return -1;
     if (T < 0 || H <= 0) return -2;

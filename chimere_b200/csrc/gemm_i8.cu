@@ -69,17 +69,25 @@ struct GemmShared {
     int failed;
 };
 
-// One CTA per (row tile, token tile).  a_tiles / b_tiles: mma128 operands; nblocks K blocks.
-// out[(row0 + r) * ldo + col0 + c] = D[r][c] for r < rows_valid, c < n_valid.
-template <class Epilogue>
-__global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const GemmParams p) {
+// What a CTA works on: its operands (mma128 tiles), the number of K blocks and of valid token columns.
+struct GemmWork {
+    const uint8_t* a_src; const uint8_t* b_src;
+    int nblocks, n_valid;
+    int aux0, aux1, aux2, aux3;   // policy specific
+};
+
+// One CTA per output tile (128 rows x up to 128 tokens).  Policy::work() names the tile (or says there is none:
+// the CTA leaves before touching TMEM); Policy::store() consumes the fp32 accumulators, thread = row.
+template <class Policy, class Params>
+__global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ GemmShared sh;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const GemmItem item = p.items[blockIdx.x];
-    const uint8_t* a_src = p.a_base + item.a_offset;
-    const uint8_t* b_src = p.b_base + item.b_offset;
-    const int nblocks = p.nblocks;
+    GemmWork item;
+    if (!Policy::work(p, blockIdx.x, item)) return;
+    const uint8_t* a_src = item.a_src;
+    const uint8_t* b_src = item.b_src;
+    const int nblocks = item.nblocks;
     const int nstages_total = (nblocks + kG_BlocksPerStage - 1) / kG_BlocksPerStage;
 
     if (tid == 0) {
@@ -173,7 +181,7 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const GemmParams
                 if (j == kG_BlocksPerStage - 1 || blk == nblocks - 1) mbar_arrive_cta(&sh.empty[st]);   // scales of the stage read
             }
         }
-        if (ok) Epilogue::store(p, item, row, acc);
+        Policy::store(p, item, row, q, lane, acc, smem, ok);
     }
 
     tc_fence_before();
@@ -184,13 +192,111 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const GemmParams
     }
 }
 
-// plain fp32 tile store (primitive test and the down projection's per-pair rows)
-struct StoreF32 {
-    __device__ static __forceinline__ void store(const GemmParams& p, const GemmItem& it, int row, const float (&acc)[128]) {
-        if (row >= it.rows_valid) return;
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// plain fp32 tile store: out[(row0 + r) * ldo + col0 + c] = D[r][c]  (the primitive)
+struct PlainPolicy {
+    __device__ static __forceinline__ bool work(const GemmParams& p, int idx, GemmWork& w) {
+        const GemmItem it = p.items[idx];
+        w.a_src = p.a_base + it.a_offset; w.b_src = p.b_base + it.b_offset;
+        w.nblocks = p.nblocks; w.n_valid = it.n_valid;
+        w.aux0 = it.rows_valid; w.aux1 = it.out_row0; w.aux2 = it.out_col0; w.aux3 = 0;
+        return true;
+    }
+    __device__ static __forceinline__ void store(const GemmParams& p, const GemmWork& w, int row, int, int, const float (&acc)[128],
+                                                 uint8_t*, bool ok) {
+        if (!ok || row >= w.aux0) return;
 #pragma unroll
         for (int c = 0; c < 128; ++c)
-            if (c < it.n_valid) p.out[(size_t)(it.out_row0 + row) * p.ldo + it.out_col0 + c] = acc[c];
+            if (c < w.n_valid) p.out[(size_t)(w.aux1 + row) * p.ldo + w.aux2 + c] = acc[c];
+    }
+};
+
+// ------------------------------------------------------------------ MoE prefill policies ----
+// Token tiles (built on the device after routing): {expert (-1 = shared expert), start, n_valid, 0}; word 0 of the
+// list = number of tiles.  Routed tile: pairs perm[start .. start + n_valid); shared tile: tokens start .. .
+constexpr int kTileHeader = 4;
+
+// gate/up: A tile = 64 gate rows | 64 up rows of the same 64 intermediate rows (or 128 up rows when there is no
+// gate).  The up half hands its sums to the gate half through shared memory; the activation is quantised to
+// Q8_1 (32 consecutive rows = one warp) straight into the down GEMM's token tile.
+struct GateUpPolicy {
+    __device__ static __forceinline__ bool work(const PrefillGemmParams& p, int idx, GemmWork& w) {
+        const int n_tiles = __ldcg(p.tiles);
+        const int j = idx / p.row_tiles_max, rt = idx - j * p.row_tiles_max;
+        if (j >= n_tiles) return false;
+        const int4 t = __ldcg(reinterpret_cast<const int4*>(p.tiles + kTileHeader) + j);
+        const bool shared = t.x < 0;
+        const int row_tiles = shared ? p.row_tiles_shared : p.row_tiles_routed;
+        if (rt >= row_tiles) return false;
+        const int nb = p.ncols_in / 32;
+        w.a_src = (shared ? p.sh_a : p.a_exps + (size_t)t.x * p.stride_a) + (size_t)rt * nb * kG_TileBytes;
+        w.b_src = p.b_tiles + (size_t)j * p.b_tile_stride;
+        w.nblocks = nb; w.n_valid = t.z;
+        w.aux0 = j; w.aux1 = rt; w.aux2 = shared ? 1 : 0; w.aux3 = t.y;
+        return true;
+    }
+    __device__ static __forceinline__ void store(const PrefillGemmParams& p, const GemmWork& w, int row, int q, int lane,
+                                                 float (&acc)[128], uint8_t* smem, bool ok) {
+        const bool dual = p.act == CHIMERE_ACT_SWIGLU;
+        float* xch = reinterpret_cast<float*>(smem);   // [128][129] floats in the ring, which is idle once ...
+        epilogue_sync();                                // ... every epilogue warp has read its last scales from it
+#pragma unroll
+        for (int c = 0; c < 128; ++c) xch[row * 129 + c] = acc[c];
+        epilogue_sync();
+        if (!ok || (dual && q >= 2)) return;
+        // this warp's 32 rows form Q8_1 block `blk` of the intermediate
+        const int blk = dual ? w.aux1 * 2 + q : w.aux1 * 4 + q;
+        uint8_t* dst = p.out_tiles + (size_t)w.aux0 * p.out_tile_stride + (size_t)blk * kG_TileBytes;
+        const int khalf = lane >> 4, kin = lane & 15;
+        for (int c = 0; c < w.n_valid; ++c) {
+            const float a = xch[row * 129 + c];
+            float v;
+            if (dual) v = silu_mul_ref(a, xch[(row + 64) * 129 + c]);
+            else { const float r = fmaxf(a, 0.0f); v = r * r; }
+            float amax = fabsf(v);
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+            const float d = amax / 127.0f;
+            const int8_t qv = (amax == 0.0f) ? (int8_t)0 : (int8_t)roundf(v / d);
+            reinterpret_cast<int8_t*>(dst)[khalf * 2048 + (c >> 3) * 128 + (c & 7) * 16 + kin] = qv;
+            if (lane == 0) *reinterpret_cast<float*>(dst + 4096 + c * 4) = __half2float(__float2half(d));
+        }
+        // columns past n_valid: zero quants and scales, so that the down GEMM's unused columns stay finite
+        for (int c = w.n_valid; c < 128; ++c) {
+            reinterpret_cast<int8_t*>(dst)[khalf * 2048 + (c >> 3) * 128 + (c & 7) * 16 + kin] = 0;
+            if (lane == 0) *reinterpret_cast<float*>(dst + 4096 + c * 4) = 0.0f;
+        }
+    }
+};
+
+// down: rows of H; the tile's columns are pairs, written to pair_out[pair row][H]
+struct DownPolicy {
+    __device__ static __forceinline__ bool work(const PrefillGemmParams& p, int idx, GemmWork& w) {
+        const int n_tiles = __ldcg(p.tiles);
+        const int j = idx / p.row_tiles_max, rt = idx - j * p.row_tiles_max;
+        if (j >= n_tiles) return false;
+        const int4 t = __ldcg(reinterpret_cast<const int4*>(p.tiles + kTileHeader) + j);
+        const bool shared = t.x < 0;
+        const int nb = (shared ? p.ncols_in_shared : p.ncols_in) / 32;
+        w.a_src = (shared ? p.sh_a : p.a_exps + (size_t)t.x * p.stride_a) + (size_t)rt * nb * kG_TileBytes;
+        w.b_src = p.b_tiles + (size_t)j * p.b_tile_stride;
+        w.nblocks = nb; w.n_valid = t.z;
+        w.aux0 = j; w.aux1 = rt; w.aux2 = shared ? 1 : 0; w.aux3 = t.y;
+        return true;
+    }
+    __device__ static __forceinline__ void store(const PrefillGemmParams& p, const GemmWork& w, int row, int, int,
+                                                 float (&acc)[128], uint8_t*, bool ok) {
+        if (!ok) return;
+        const int h = w.aux1 * 128 + row;
+        if (h >= p.H) return;
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+            if (c < w.n_valid) {
+                const int prow = w.aux2 ? p.T * p.top_k + w.aux3 + c : __ldcg(p.perm + w.aux3 + c);
+                p.pair_out[(size_t)prow * p.H + h] = acc[c];
+            }
+        }
     }
 };
 
@@ -226,10 +332,148 @@ cudaError_t launch_pack_mma128(const int8_t* q, const float* scales, uint8_t* ou
 cudaError_t launch_gemm_i8_f32(const GemmParams& p, int n_items, cudaStream_t stream) {
     if (n_items <= 0) return cudaSuccess;
     const size_t smem = (size_t)kG_Stages * kG_StageBytes + 1024;
-    cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<StoreF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<PlainPolicy, GemmParams>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    gemm_i8_kernel<StoreF32><<<n_items, kG_Threads, smem, stream>>>(p);
+    gemm_i8_kernel<PlainPolicy, GemmParams><<<n_items, kG_Threads, smem, stream>>>(p);
     return cudaGetLastError();
 }
+
+cudaError_t launch_prefill_gemm(const PrefillGemmParams& p, bool down, int n_tiles_max, cudaStream_t stream) {
+    const size_t smem = (size_t)kG_Stages * kG_StageBytes + 1024;
+    const int grid = n_tiles_max * p.row_tiles_max;
+    if (grid <= 0) return cudaSuccess;
+    cudaError_t e;
+    if (down) {
+        e = cudaFuncSetAttribute(gemm_i8_kernel<DownPolicy, PrefillGemmParams>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        gemm_i8_kernel<DownPolicy, PrefillGemmParams><<<grid, kG_Threads, smem, stream>>>(p);
+    } else {
+        e = cudaFuncSetAttribute(gemm_i8_kernel<GateUpPolicy, PrefillGemmParams>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        gemm_i8_kernel<GateUpPolicy, PrefillGemmParams><<<grid, kG_Threads, smem, stream>>>(p);
+    }
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ prefill plumbing kernels ----
+// ggml blocks -> mma128 tiles: int8 values and f32 block scales (IQ3_S: scale = d * (1 + 2*sub-scale), exact in f32).
+// dst row of source row r: plain (mode 0), gate half (mode 1: (r/64)*128 + r%64) or up half (mode 2: ... + 64).
+// One thread per (row, block); blockIdx.y = expert.
+template <int TYPE>
+__global__ void pack_mma128_ggml_kernel(const uint8_t* raw, uint8_t* out, int nrows, int ncols, int mode, int64_t raw_stride,
+                                        int64_t out_stride, const uint32_t* grid) {
+    const int nb = ncols >> 5;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)nrows * nb) return;
+    const int r = (int)(idx % nrows), b = (int)(idx / nrows);
+    int w[8], mul;
+    float dw;
+    Unit<TYPE>::load(raw + (size_t)blockIdx.y * raw_stride + (size_t)r * Unit<TYPE>::row_bytes(ncols), b, grid, w, dw, mul);
+    if (TYPE == CHIMERE_TYPE_Q4_0) {
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {   // bytes hold 16 * (nibble - 8): arithmetic shift of every byte
+            const int x = w[g];
+            w[g] = (int)(((uint32_t)((int8_t)(x) >> 4) & 0xFFu) | (((uint32_t)((int8_t)(x >> 8) >> 4) & 0xFFu) << 8) |
+                         (((uint32_t)((int8_t)(x >> 16) >> 4) & 0xFFu) << 16) | (((uint32_t)((int8_t)(x >> 24) >> 4) & 0xFFu) << 24));
+        }
+    }
+    const int dr = mode == 0 ? r : (r >> 6) * 128 + (r & 63) + (mode == 2 ? 64 : 0);
+    const int tile = dr >> 7, rr = dr & 127;
+    uint8_t* dst = out + (size_t)blockIdx.y * out_stride + ((size_t)tile * nb + b) * kG_TileBytes;
+    *reinterpret_cast<uint4*>(dst + (rr >> 3) * 128 + (rr & 7) * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(dst + 2048 + (rr >> 3) * 128 + (rr & 7) * 16) = make_uint4(w[4], w[5], w[6], w[7]);
+    *reinterpret_cast<float*>(dst + 4096 + rr * 4) = dw * (float)mul;
+}
+
+static __device__ const uint32_t g_iq3s_grid_mma[512] = {
+#include "iq3s_grid.inc"
+};
+
+cudaError_t launch_pack_mma128_ggml(int type, const void* raw, void* out, int n_mats, int nrows, int ncols, int mode,
+                                    int64_t raw_stride, int64_t out_stride, cudaStream_t stream) {
+    if (n_mats <= 0) return cudaSuccess;
+    const int64_t n = (int64_t)nrows * (ncols / 32);
+    const dim3 grid((unsigned)((n + 255) / 256), (unsigned)n_mats);
+    const uint32_t* g = nullptr;
+    cudaGetSymbolAddress((void**)&g, g_iq3s_grid_mma);
+    switch (type) {
+        case CHIMERE_TYPE_Q4_0: pack_mma128_ggml_kernel<CHIMERE_TYPE_Q4_0><<<grid, 256, 0, stream>>>((const uint8_t*)raw, (uint8_t*)out, nrows, ncols, mode, raw_stride, out_stride, g); break;
+        case CHIMERE_TYPE_Q8_0: pack_mma128_ggml_kernel<CHIMERE_TYPE_Q8_0><<<grid, 256, 0, stream>>>((const uint8_t*)raw, (uint8_t*)out, nrows, ncols, mode, raw_stride, out_stride, g); break;
+        case CHIMERE_TYPE_IQ3_S: pack_mma128_ggml_kernel<CHIMERE_TYPE_IQ3_S><<<grid, 256, 0, stream>>>((const uint8_t*)raw, (uint8_t*)out, nrows, ncols, mode, raw_stride, out_stride, g); break;
+        default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+// After routing: token tiles for the experts with at least `gemm_min` pairs (and for the shared expert), and the
+// GEMV work list rewritten to hold only the smaller experts.  One CTA of 256 threads, thread e = expert e.
+__global__ void __launch_bounds__(256) build_tiles_kernel(const int32_t* offsets, const int32_t* perm, int32_t* tiles, int32_t* list,
+                                                          int E, int T, int top_k, int has_shared, int gemm_min) {
+    __shared__ int scan_t[8], scan_e[8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cnt = tid < E ? offsets[tid + 1] - offsets[tid] : 0, off = tid < E ? offsets[tid] : 0;
+    const bool big = cnt >= gemm_min;
+    const int nt = big ? (cnt + 127) / 128 : 0;
+    const int ne = big ? 0 : (cnt + kMaxGroupTokens - 1) / kMaxGroupTokens;
+    int it = nt, ie = ne;
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+        const int a = __shfl_up_sync(0xffffffffu, it, s), b = __shfl_up_sync(0xffffffffu, ie, s);
+        if (lane >= s) { it += a; ie += b; }
+    }
+    if (lane == 31) { scan_t[warp] = it; scan_e[warp] = ie; }
+    __syncthreads();
+    int bt = 0, be = 0, tot_t = 0, tot_e = 0;
+    for (int w = 0; w < 8; ++w) { if (w < warp) { bt += scan_t[w]; be += scan_e[w]; } tot_t += scan_t[w]; tot_e += scan_e[w]; }
+    const int nsh = has_shared ? (T + 127) / 128 : 0;
+    int4* tv = reinterpret_cast<int4*>(tiles + kTileHeader);
+    for (int i = tid; i < nsh; i += 256) tv[i] = make_int4(-1, i * 128, min(128, T - i * 128), 0);
+    const int t0 = nsh + bt + it - nt;
+    for (int i = 0; i < nt; ++i) tv[t0 + i] = make_int4(tid, off + i * 128, min(128, cnt - i * 128), 0);
+    const int e0 = be + ie - ne;
+    for (int i = 0; i < ne; ++i) {
+        int* ent = list + kListHeader + kListEntry * (e0 + i);
+        const int mm = min(kMaxGroupTokens, cnt - i * kMaxGroupTokens);
+        ent[0] = tid; ent[1] = off + i * kMaxGroupTokens; ent[2] = mm; ent[3] = 0;
+        for (int j = 0; j < kMaxGroupTokens; ++j) ent[4 + j] = j < mm ? perm[off + i * kMaxGroupTokens + j] : 0;
+    }
+    if (tid == 0) {
+        tiles[0] = nsh + tot_t; tiles[1] = nsh; tiles[2] = tot_t; tiles[3] = 0;
+        list[0] = tot_e; list[1] = tot_e; list[2] = 0; list[3] = 0;
+    }
+}
+
+// Token tiles of the gate/up GEMM: the Q8_1 planes of each tile's tokens in mma128 order.
+// grid = (max tiles, 128 token slots), 128 threads = the 16-byte chunks of a row.
+__global__ void __launch_bounds__(128) gather_tiles_kernel(const int32_t* tiles, const int32_t* perm, const int8_t* x_q, const float* x_d,
+                                                           int x_d_stride, uint8_t* b_tiles, int64_t b_tile_stride, int H, int top_k) {
+    const int j = blockIdx.x, c = blockIdx.y;
+    if (j >= __ldcg(tiles)) return;
+    const int4 t = __ldcg(reinterpret_cast<const int4*>(tiles + kTileHeader) + j);
+    const bool valid = c < t.z;
+    const int tok = !valid ? 0 : (t.x < 0 ? t.y + c : __ldcg(perm + t.y + c) / top_k);
+    uint8_t* base = b_tiles + (size_t)j * b_tile_stride;
+    for (int ch = threadIdx.x; ch < H / 16; ch += 128) {
+        const uint4 v = valid ? __ldcg(reinterpret_cast<const uint4*>(x_q + (size_t)tok * H) + ch) : make_uint4(0, 0, 0, 0);
+        const int b = ch >> 1, khalf = ch & 1;
+        *reinterpret_cast<uint4*>(base + (size_t)b * kG_TileBytes + khalf * 2048 + (c >> 3) * 128 + (c & 7) * 16) = v;
+    }
+    for (int b = threadIdx.x; b < H / 32; b += 128)
+        *reinterpret_cast<float*>(base + (size_t)b * kG_TileBytes + 4096 + c * 4) = valid ? __ldcg(x_d + (size_t)tok * x_d_stride + b) : 0.0f;
+}
+
+cudaError_t launch_build_tiles(const int32_t* offsets, const int32_t* perm, int32_t* tiles, int32_t* list, int E, int T, int top_k,
+                               int has_shared, int gemm_min, cudaStream_t stream) {
+    build_tiles_kernel<<<1, 256, 0, stream>>>(offsets, perm, tiles, list, E, T, top_k, has_shared, gemm_min);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gather_tiles(const int32_t* tiles, const int32_t* perm, const int8_t* x_q, const float* x_d, int x_d_stride,
+                                uint8_t* b_tiles, int64_t b_tile_stride, int H, int top_k, int n_tiles_max, cudaStream_t stream) {
+    if (n_tiles_max <= 0) return cudaSuccess;
+    gather_tiles_kernel<<<dim3(n_tiles_max, 128), 128, 0, stream>>>(tiles, perm, x_q, x_d, x_d_stride, b_tiles, b_tile_stride, H, top_k);
+    return cudaGetLastError();
+}
+
 
 }  // namespace chimere

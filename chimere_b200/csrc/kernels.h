@@ -105,6 +105,28 @@ struct GemmParams {
     int32_t* status;
 };
 cudaError_t launch_gemm_i8_f32(const GemmParams& p, int n_items, cudaStream_t stream);
+
+// MoE prefill on the GEMM: token tiles built on the device, weights in mma128 form
+struct PrefillGemmParams {
+    const int32_t* tiles;            // tile list (word 0 = count)
+    const int32_t* perm;
+    const uint8_t* a_exps; int64_t stride_a;   // routed experts' mma128 matrices
+    const uint8_t* sh_a;                       // shared expert's
+    const uint8_t* b_tiles; int64_t b_tile_stride;   // token tiles (input)
+    uint8_t* out_tiles; int64_t out_tile_stride;     // gate/up: token tiles of the down GEMM (output)
+    float* pair_out;                                 // down: per-pair rows [pairs][H]
+    int row_tiles_routed, row_tiles_shared, row_tiles_max;
+    int ncols_in, ncols_in_shared;   // K of the routed / shared matrices
+    int act, T, top_k, H;
+    int32_t* status;
+};
+cudaError_t launch_prefill_gemm(const PrefillGemmParams& p, bool down, int n_tiles_max, cudaStream_t stream);
+cudaError_t launch_pack_mma128_ggml(int type, const void* raw, void* out, int n_mats, int nrows, int ncols, int mode,
+                                    int64_t raw_stride, int64_t out_stride, cudaStream_t stream);
+cudaError_t launch_build_tiles(const int32_t* offsets, const int32_t* perm, int32_t* tiles, int32_t* list, int E, int T, int top_k,
+                               int has_shared, int gemm_min, cudaStream_t stream);
+cudaError_t launch_gather_tiles(const int32_t* tiles, const int32_t* perm, const int8_t* x_q, const float* x_d, int x_d_stride,
+                                uint8_t* b_tiles, int64_t b_tile_stride, int H, int top_k, int n_tiles_max, cudaStream_t stream);
 cudaError_t launch_pack_mma128(const int8_t* q, const float* scales, uint8_t* out, int rows, int cols, cudaStream_t stream);
 
 // tiled32 layout (tiled.cuh): pack, kernels on packed weights, parity tap

@@ -128,6 +128,23 @@ class MoeWeightsTiled:
         return self.arena.numel() + sum(t.numel() * t.element_size() for t in self._keep if t is not None)
 
 
+class MoeWeightsPrefill:
+    """The GEMM copy of a layer's expert matrices (chimere_b200_moe_pack_prefill): int8 values and f32 block scales in
+    the tensor-core operand order.  Built from the raw ggml form; used together with the tiled32 form."""
+
+    def __init__(self, raw: MoeWeightsRaw):
+        lib = abi.load()
+        rs = raw.as_struct()
+        nbytes = lib.chimere_b200_moe_pack_prefill_bytes(C.byref(rs))
+        if nbytes == 0:
+            raise RuntimeError("chimere_b200_moe_pack_prefill_bytes rejected the layer (needs H % 128 == 0, F % 64 (128 without gate) == 0)")
+        self.arena = torch.zeros(nbytes, dtype=torch.uint8, device=raw.router_weight.device)
+        self.struct = abi.PrefillWeights()
+        stream = torch.cuda.current_stream(self.arena.device).cuda_stream
+        abi.check(lib.chimere_b200_moe_pack_prefill(C.byref(rs), self.arena.data_ptr(), nbytes, C.byref(self.struct), stream),
+                  "chimere_b200_moe_pack_prefill")
+
+
 class MoeScratch:
     """Device scratch for one stream, allocated once (the library itself never allocates)."""
 
@@ -142,8 +159,18 @@ class MoeScratch:
         stream = torch.cuda.current_stream(self.device).cuda_stream
         abi.check(lib.chimere_b200_moe_workspace_init(C.byref(self.ws), self.arena.data_ptr(), nbytes,
                                                        C.byref(w.as_struct()), max_T, stream), "workspace_init")
+        self.prefill = None
         self.x_dev = torch.empty(max_T, w.H, dtype=torch.float32, device=self.device)
         self.y_dev = torch.empty(max_T, w.H, dtype=torch.float32, device=self.device)
+
+    def enable_prefill(self) -> None:
+        """Adds the scratch of the GEMM path (token tiles) to this workspace."""
+        lib = abi.load()
+        n = lib.chimere_b200_moe_prefill_bytes(C.byref(self.w.as_struct()), self.max_T)
+        if n == 0:
+            raise RuntimeError("chimere_b200_moe_prefill_bytes rejected the layer")
+        self.prefill = torch.zeros(n, dtype=torch.uint8, device=self.device)
+        self.ws.prefill_arena, self.ws.prefill_bytes = self.prefill.data_ptr(), n
 
     # ---- parity taps: views into the arena -------------------------------------------------
     def _view(self, ptr: int, nbytes: int) -> torch.Tensor:
@@ -192,6 +219,19 @@ def forward_moe(w, scratch: MoeScratch, x: torch.Tensor, out: Optional[torch.Ten
     stream = torch.cuda.current_stream(x.device).cuda_stream
     abi.check(lib.chimere_b200_moe_forward(C.byref(w.as_struct()), x.data_ptr(), out.data_ptr(), T,
                                             C.byref(scratch.ws), stream), "chimere_b200_moe_forward")
+    return out
+
+
+def forward_moe_prefill(w, pw: MoeWeightsPrefill, scratch: MoeScratch, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = MoE(x) with the large experts on the tensor-core GEMM (w: tiled32 layer, pw: its GEMM copy)."""
+    lib = abi.load()
+    if scratch.prefill is None:
+        scratch.enable_prefill()
+    if out is None:
+        out = torch.empty_like(x)
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    abi.check(lib.chimere_b200_moe_forward_prefill(C.byref(w.as_struct()), C.byref(pw.struct), x.data_ptr(), out.data_ptr(), x.shape[0],
+                                                   C.byref(scratch.ws), stream), "chimere_b200_moe_forward_prefill")
     return out
 
 

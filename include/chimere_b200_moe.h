@@ -239,6 +239,30 @@ int chimere_b200_pack_mma128(const int8_t* d_q, const float* d_scales, void* d_o
 int chimere_b200_gemm_i8(const void* d_a, const void* d_b, int rows, int tokens, int cols, float* d_out,
                          void* d_items, int32_t* d_status, cudaStream_t stream);
 
+/* ------------------------------------------------------------ prefill-size batches -------- */
+/* For many tokens per call the expert products run as grouped block-scaled int8 GEMMs on the tensor cores
+ * (the primitive above): experts with at least 32 routed tokens and the shared expert go to the GEMM, the rest
+ * stay on the GEMV kernels.  The GEMM needs a second weight copy in its own layout (int8 values + f32 block
+ * scales, gate and up rows interleaved per 64 rows): about 1.06x the Q8_0 bytes, 2x Q4_0, 2.3x IQ3_S. */
+typedef struct chimere_moe_prefill_weights {
+    const void* gu_exps;   int64_t stride_gu;     /* routed: gate|up tiles */
+    const void* down_exps; int64_t stride_down;
+    const void* sh_gu;     const void* sh_down;   /* shared expert */
+    int32_t rows_per_gu_tile;                     /* 64 with a gate matrix, 128 without */
+    int32_t reserved;
+} chimere_moe_prefill_weights;
+
+size_t chimere_b200_moe_pack_prefill_bytes(const chimere_moe_layer* raw);
+/* raw: layout GGML.  F and F_s multiples of 128 (64 with a gate), H a multiple of 128. */
+int chimere_b200_moe_pack_prefill(const chimere_moe_layer* raw, void* d_arena, size_t bytes,
+                                  chimere_moe_prefill_weights* out, cudaStream_t stream);
+/* Extra scratch the prefill path needs for up to max_T tokens; pass it with ws->prefill_arena / prefill_bytes. */
+size_t chimere_b200_moe_prefill_bytes(const chimere_moe_layer* w, int max_T);
+/* y = MoE(x) like chimere_b200_moe_forward; `w` TILED32 (used for the small experts), `pw` its GEMM copy. */
+int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw,
+                                     const float* d_x, float* d_y, int T, chimere_moe_workspace* ws,
+                                     cudaStream_t stream);
+
 /* RMSNorm with unit weight over rows of length H: y = x / sqrt(mean(x^2) + eps). Used between
  * stacked layers. */
 int chimere_b200_rmsnorm(const float* d_x, float* d_y, int T, int H, float eps, cudaStream_t stream);

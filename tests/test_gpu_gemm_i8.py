@@ -52,3 +52,38 @@ def test_block_scaled_result(rows, tokens, cols):
     out, ref = _run(rows, tokens, cols, unit_scales=False)
     rel = (out.double() - ref).abs().max() / ref.abs().max()
     assert rel < 1e-5, float(rel)
+
+
+# ---------------------------------------------------------------- the MoE layer on the GEMM path ----
+import numpy as np  # noqa: E402
+
+import oracle  # noqa: E402
+from chimere_b200 import configs  # noqa: E402
+from chimere_b200.layer import MoeScratch, MoeWeightsPrefill, MoeWeightsTiled, forward_moe, forward_moe_prefill  # noqa: E402
+
+PREFILL_CASES = [
+    (configs.scaled(configs.QWEN_Q8_0, E=16), 300),        # Zipf bias: a few experts get most tokens, the tail stays on the GEMV
+    (configs.scaled(configs.QWEN_Q4_0, E=8), 200),
+    (configs.scaled(configs.QWEN_IQ3S, E=8), 130),
+    (configs.scaled(configs.NEMOTRON_Q4_0, E=8, F=1792, F_s=3712 - 128), 96),   # no gate matrix: 128-row tiles
+]
+
+
+@pytest.mark.parametrize("cfg,T", PREFILL_CASES, ids=lambda v: getattr(v, "name", str(v)))
+def test_prefill_forward_matches_oracle_and_gemv_path(cfg, T):
+    raw = configs.make_layer(cfg, device="cuda")
+    tiled, pw = MoeWeightsTiled(raw), MoeWeightsPrefill(raw)
+    x = configs.make_input(cfg, T, device="cuda")
+    sc = MoeScratch(tiled, T)
+    y_gemv = forward_moe(tiled, sc, x).clone()
+    y = forward_moe_prefill(tiled, pw, sc, x)
+    torch.cuda.synchronize()
+    assert sc.status() == 0
+    o = oracle.moe_forward(raw.to("cpu"), x.cpu().numpy(), taps=False)
+    for name, got in (("gemm", y), ("gemv", y_gemv)):
+        g, ref = got.cpu().numpy().astype(np.float64), o["y"].astype(np.float64)
+        rel = np.abs(g - ref).max(axis=1) / np.abs(ref).max(axis=1)
+        cos = (g * ref).sum(1) / (np.linalg.norm(g, axis=1) * np.linalg.norm(ref, axis=1))
+        assert rel.max() <= 1e-2 and cos.min() >= 0.9999, (name, rel.max(), cos.min())
+    # the two GPU paths compute the same integer block dots; only fp32 summation order differs
+    assert (y - y_gemv).abs().max() <= 2e-3 * y_gemv.abs().max()
