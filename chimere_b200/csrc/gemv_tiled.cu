@@ -43,6 +43,48 @@ __host__ __device__ inline TileSmem tile_smem(int ncols_max, int wr, int wk, boo
 // One pass over groups g0, g0+gstep, ... < ngroups of the tile at `tile` (global memory) for M tokens whose int8
 // rows start at shared address aq (row pitch qrow) and whose f32 scales start at shared address ad (row pitch
 // drow bytes): acc[i] += (scale_w * scale_x) * integer block dot.
+// The units of one group against M tokens.  FULL: all kGroupUnits units are there (no per-unit test).
+// Types with one weight scale per group (Tiled<TYPE>::kGroupScale) multiply by it once per group.
+template <int TYPE, int M, bool FULL>
+__device__ __forceinline__ void group_units(const typename Tiled<TYPE>::Regs& r, int g, int nu, uint32_t aq, int qrow, uint32_t ad,
+                                            int drow, int mrem, float (&acc)[M]) {
+    using TT = Tiled<TYPE>;
+    float part[M];
+#pragma unroll
+    for (int i = 0; i < M; ++i) part[i] = 0.0f;
+#pragma unroll
+    for (int u = 0; u < kGroupUnits; ++u) {
+        if (FULL || u < nu) {
+            int w[8];
+            TT::decode(r, u, w);
+            const uint32_t qb = aq + (g * kGroupUnits + u) * 32, db = ad + (g * kGroupUnits + u) * 4;
+#pragma unroll
+            for (int i = 0; i < M; ++i) {
+                if (M == 1 || i < mrem) {
+                    const uint4 q0 = lds128(qb + i * qrow), q1 = lds128(qb + i * qrow + 16);
+                    int s0 = __dp4a(w[0], (int)q0.x, 0), s1 = __dp4a(w[4], (int)q1.x, 0);   // two independent chains
+                    s0 = __dp4a(w[1], (int)q0.y, s0); s1 = __dp4a(w[5], (int)q1.y, s1);
+                    s0 = __dp4a(w[2], (int)q0.z, s0); s1 = __dp4a(w[6], (int)q1.z, s1);
+                    s0 = __dp4a(w[3], (int)q0.w, s0); s1 = __dp4a(w[7], (int)q1.w, s1);
+                    const float dx = __uint_as_float(lds32(db + i * drow));
+                    const float t = (float)TT::finish(s0 + s1, r, u, 0);
+                    if (TT::kGroupScale) part[i] = fmaf(t, dx, part[i]);
+                    else acc[i] = fmaf(TT::dscale(r, u) * dx, t, acc[i]);
+                }
+            }
+        }
+    }
+    if (TT::kGroupScale) {
+        const float dw = TT::dscale(r, 0);
+#pragma unroll
+        for (int i = 0; i < M; ++i)
+            if (M == 1 || i < mrem) acc[i] = fmaf(dw, part[i], acc[i]);
+    }
+}
+
+// One pass over groups g0, g0+gstep, ... < ngroups of the tile at `tile` (global memory) for M tokens whose int8
+// rows start at shared address aq (row pitch qrow) and whose f32 scales start at shared address ad (row pitch
+// drow bytes): acc[i] += (scale_w * scale_x) * integer block dot.
 template <int TYPE, int M>
 __device__ __forceinline__ void dot_pass(const uint8_t* tile, int g0, int ngroups, int gstep, int lane, int nb, uint32_t aq,
                                          int qrow, uint32_t ad, int drow, int mrem, float (&acc)[M]) {
@@ -51,28 +93,8 @@ __device__ __forceinline__ void dot_pass(const uint8_t* tile, int g0, int ngroup
         const int nu = min(kGroupUnits, nb - g * kGroupUnits);
         typename TT::Regs r;
         TT::load(tile, g, lane, nu, r);
-#pragma unroll
-        for (int u = 0; u < kGroupUnits; ++u) {
-            if (u < nu) {
-                int w[8];
-                TT::decode(r, u, w);
-                const float dw = TT::dscale(r, u);
-                const int b = g * kGroupUnits + u;
-#pragma unroll
-                for (int i = 0; i < M; ++i) {
-                    if (M == 1 || i < mrem) {
-                        const uint32_t qp = aq + i * qrow + b * 32;
-                        const uint4 q0 = lds128(qp), q1 = lds128(qp + 16);
-                        int s0 = __dp4a(w[0], (int)q0.x, 0), s1 = __dp4a(w[4], (int)q1.x, 0);   // two independent chains
-                        s0 = __dp4a(w[1], (int)q0.y, s0); s1 = __dp4a(w[5], (int)q1.y, s1);
-                        s0 = __dp4a(w[2], (int)q0.z, s0); s1 = __dp4a(w[6], (int)q1.z, s1);
-                        s0 = __dp4a(w[3], (int)q0.w, s0); s1 = __dp4a(w[7], (int)q1.w, s1);
-                        const float dx = __uint_as_float(lds32(ad + i * drow + b * 4));
-                        acc[i] = fmaf(dw * dx, (float)TT::finish(s0 + s1, r, u, 0), acc[i]);
-                    }
-                }
-            }
-        }
+        if (nu == kGroupUnits) group_units<TYPE, M, true>(r, g, nu, aq, qrow, ad, drow, mrem, acc);
+        else group_units<TYPE, M, false>(r, g, nu, aq, qrow, ad, drow, mrem, acc);
     }
 }
 

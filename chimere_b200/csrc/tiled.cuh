@@ -56,6 +56,7 @@ template <int TYPE> struct Tiled;
 
 template <> struct Tiled<CHIMERE_TYPE_Q4_0> {
     static constexpr int kUnitBytes = 576, kChunkBytes = 4 * 576, kGroupsPerChunk = 1;
+    static constexpr bool kGroupScale = false;   // one scale per unit
     struct Regs { uint4 v[4]; uint32_t d[4]; };
     __host__ __device__ static int64_t tile_bytes(int ncols) { return (int64_t)(ncols / 32) * kUnitBytes; }
     __device__ static __forceinline__ void load(const uint8_t* tile, int grp, int lane, int nu, Regs& r) {
@@ -81,6 +82,7 @@ template <> struct Tiled<CHIMERE_TYPE_Q4_0> {
 
 template <> struct Tiled<CHIMERE_TYPE_IQ3_S> {
     static constexpr int kSuperBytes = 4288, kChunkBytes = 4288, kGroupsPerChunk = 2;
+    static constexpr bool kGroupScale = true;    // one f16 d per super-block: the same for the four units of a group
     struct Regs { uint4 v[4]; uint32_t d; uint32_t sc; };
     __host__ __device__ static int64_t tile_bytes(int ncols) { return (int64_t)(ncols / 256) * kSuperBytes; }
     __device__ static __forceinline__ void load(const uint8_t* tile, int grp, int lane, int nu, Regs& r) {
@@ -116,6 +118,7 @@ template <> struct Tiled<CHIMERE_TYPE_IQ3_S> {
 
 template <> struct Tiled<CHIMERE_TYPE_Q8_0> {
     static constexpr int kUnitBytes = 1088, kChunkBytes = 4 * 1088, kGroupsPerChunk = 1;
+    static constexpr bool kGroupScale = false;
     struct Regs { uint4 v[8]; uint32_t d[4]; };
     __host__ __device__ static int64_t tile_bytes(int ncols) { return (int64_t)(ncols / 32) * kUnitBytes; }
     __device__ static __forceinline__ void load(const uint8_t* tile, int grp, int lane, int nu, Regs& r) {
