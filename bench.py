@@ -137,6 +137,42 @@ def workload_config(cfg, T, L):
             "l2": f"weights rotate over {L} layers; one cycle touches more than the 126 MB L2, inputs differ per layer"}
 
 
+def measure_prefill(lib, dev, tokens_list):
+    """Secondary measurement: the prefill configuration (all experts Q8_0, Zipf-skewed routing) on one layer, with the
+    large experts on the tcgen05 grouped GEMM and, for comparison, everything on the GEMV kernels."""
+    import torch
+    from chimere_b200 import configs
+    from chimere_b200.layer import MoeScratch, MoeWeightsPrefill, MoeWeightsTiled, forward_moe, forward_moe_prefill
+    cfg = configs.QWEN_Q8_0
+    raw = configs.make_layer(cfg, device=dev)
+    tiled, pw = MoeWeightsTiled(raw), MoeWeightsPrefill(raw)
+    del raw
+    out = []
+    for T in tokens_list:
+        x = configs.make_input(cfg, T, device=dev)
+        sc = MoeScratch(tiled, T, device=dev)
+        sc.enable_prefill()
+        y = torch.empty_like(x)
+        res = {"T": T}
+        for name, fn in (("gemm", lambda: forward_moe_prefill(tiled, pw, sc, x, y)), ("gemv", lambda: forward_moe(tiled, sc, x, y))):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 5
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / reps
+            res[name] = {"us_per_layer_call": us, "tokens_per_s": T / (us * 1e-6), "int8_tops": configs.int8_ops(cfg, T) / (us * 1e-6) / 1e12}
+        res["device_status"] = sc.status()
+        out.append(res)
+        del sc, x, y
+    return {"workload": f"{cfg.name}: one layer, all experts Q8_0, Zipf(1.1) logit bias, weights 0.86 GB (> L2)", "results": out}
+
+
 def run_expert_parallel(args, cfg, dev, rank, world, local, dist, hbm_peak, peak_kind):
     """N > 1: the same layer with its experts sharded over the ranks (E/N each, contiguous), router and shared
     expert replicated, T tokens per rank (weak scaling), dispatch and combine by NCCL all-to-all."""
@@ -257,6 +293,7 @@ def main():
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--prefill-tokens", default="512,2048", help="comma list of T for the secondary prefill measurement ('' = skip)")
     ap.add_argument("--layout", default="tiled", choices=["tiled", "ggml"],
                     help="weight layout the layer entry runs on: the library's tiled32 repack (default) or raw ggml blocks")
     args = ap.parse_args()
@@ -451,6 +488,12 @@ def main():
            "d2h_bytes_per_step": L * T * cfg.H * 4, "ms_per_step": 1e3 * e2e_secs / K}
 
     status = max(sc.status() for sc in scratch)
+    prefill = None
+    if rank == 0 and args.prefill_tokens and args.layout == "tiled":
+        del graph
+        layers.clear(); scratch.clear(); xs.clear(); ys.clear()
+        torch.cuda.empty_cache()
+        prefill = measure_prefill(lib, dev, [int(t) for t in args.prefill_tokens.split(",") if t])
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -469,7 +512,7 @@ def main():
                            timing="CUDA graph replay of one step, CUDA events on the launching stream",
                            weight_layout=args.layout),
             "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": 3 * L * K, "clocks": clocks,
-            "sweep": sweep, "device_status": status}
+            "sweep": sweep, "prefill": prefill, "device_status": status}
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

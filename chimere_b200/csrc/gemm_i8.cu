@@ -13,10 +13,11 @@
 // followed by 128 f32 scales.  A plain bulk copy of a (tile, block range) lands MMA-ready in shared
 // memory: shared-memory descriptor with leading (K) byte offset 2048 and stride (row group) byte offset 128.
 //
-// CTA = 6 warps: warp 0 feeds a shared-memory ring with cp.async.bulk; warp 1 owns TMEM (512 columns =
+// CTA = 10 warps: warp 0 feeds a shared-memory ring with cp.async.bulk; warp 1 owns TMEM (512 columns =
 // four 128x128 int32 accumulators) and issues one tcgen05.mma kind::i8 (M 128, N 128, K 32) per block,
-// never accumulating across blocks; warps 2..5 read each block's accumulator back (tcgen05.ld), convert,
-// scale and add into fp32 registers (thread = output row), then write the tile.
+// never accumulating across blocks; warps 2..9 read each block's accumulator back (tcgen05.ld; two warps per
+// TMEM lane quarter, 64 token columns each), convert, scale and add into fp32 registers (thread = output row),
+// then write the tile.
 // All waits are bounded; a wait that runs out raises a status bit and the CTA still frees its TMEM.
 #include "common.cuh"
 #include "kernels.h"
@@ -27,7 +28,8 @@ constexpr int kG_TileBytes = 4096 + 512;     // one (128 x 32) int8 block + 128 
 constexpr int kG_BlocksPerStage = 4;
 constexpr int kG_Stages = 3;
 constexpr int kG_StageBytes = 2 * kG_BlocksPerStage * kG_TileBytes;   // A blocks then B blocks
-constexpr int kG_Threads = 192;
+constexpr int kG_EpiWarps = 8;                 // two per TMEM lane quarter: each takes 64 of the 128 token columns
+constexpr int kG_Threads = 32 * (2 + kG_EpiWarps);
 constexpr int kG_TmemCols = 512;
 
 __device__ __forceinline__ uint64_t smem_desc_kmajor(uint32_t saddr) {
@@ -60,6 +62,21 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, int (&v)[32]) {
         : "r"(taddr) : "memory");
 }
 
+__device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, int (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// int32 -> f32 without the conversion unit: |v| <= 32 * 127 * 128 < 2^22, so v + 0x4B400000 read as a float is
+// 12582912 + v exactly, and one fp32 subtraction gives v.  (Integer add and float add run at full rate.)
+__device__ __forceinline__ float i2f_exact(int v) { return __int_as_float(v + 0x4B400000) - 12582912.0f; }
+
 struct GemmShared {
     uint64_t full[kG_Stages];        // stage bytes have landed
     uint64_t empty[kG_Stages];       // stage read by the MMAs and by the epilogue (scales)
@@ -91,8 +108,8 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
     const int nstages_total = (nblocks + kG_BlocksPerStage - 1) / kG_BlocksPerStage;
 
     if (tid == 0) {
-        for (int i = 0; i < kG_Stages; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1 + 4); }
-        for (int i = 0; i < 4; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 4); }
+        for (int i = 0; i < kG_Stages; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1 + kG_EpiWarps); }
+        for (int i = 0; i < 4; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], kG_EpiWarps); }
         sh.failed = 0;
         mbar_fence_init();
     }
@@ -142,13 +159,14 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
             }
         }
     } else {
-        // ------------------------------ epilogue: thread = output row ------------------------------
+        // ------------------------------ epilogue: thread = output row, 64 token columns ------------------------------
         const int q = warp & 3;                      // TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;            // which 64 columns
         const int row = q * 32 + lane;
-        const int nchunks = (item.n_valid + 31) >> 5;
-        float acc[128];
+        const int ncols_here = min(64, max(0, item.n_valid - half * 64));
+        float acc[64];
 #pragma unroll
-        for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+        for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
         bool ok = true;
         for (int blk = 0; blk < nblocks && ok; ++blk) {
             const int s = blk / kG_BlocksPerStage, j = blk - s * kG_BlocksPerStage;
@@ -156,21 +174,31 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
             const int buf = blk & 3, tph = (blk >> 2) & 1;
             if (!mbar_wait(&sh.tfull[buf], tph)) { atomicOr(p.status, kStatusWaitTimeout); sh.failed = 1; ok = false; break; }
             tc_fence_after();
-            const uint8_t* stage = smem + (size_t)st * kG_StageBytes;
-            const float sa = *reinterpret_cast<const float*>(stage + j * kG_TileBytes + 4096 + row * 4);
-            const float4* sbv = reinterpret_cast<const float4*>(stage + (kG_BlocksPerStage + j) * kG_TileBytes + 4096);
+            if (ncols_here > 0) {
+                const uint8_t* stage = smem + (size_t)st * kG_StageBytes;
+                const float sa = *reinterpret_cast<const float*>(stage + j * kG_TileBytes + 4096 + row * 4);
+                const float4* sbv = reinterpret_cast<const float4*>(stage + (kG_BlocksPerStage + j) * kG_TileBytes + 4096) + half * 16;
+                int v0[32], v1[32];
+                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + buf * 128 + half * 64;
+                tc_ld32_nowait(taddr, v0);
+                if (ncols_here > 32) tc_ld32_nowait(taddr + 32, v1);
+                tc_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                if (c < nchunks) {
-                    int v[32];
-                    tc_ld32(tmem + ((uint32_t)(q * 32) << 16) + buf * 128 + c * 32, v);
+                for (int g = 0; g < 8; ++g) {
+                    const float4 sb4 = sbv[g];
+                    acc[4 * g + 0] = fmaf(i2f_exact(v0[4 * g + 0]) * sb4.x, sa, acc[4 * g + 0]);
+                    acc[4 * g + 1] = fmaf(i2f_exact(v0[4 * g + 1]) * sb4.y, sa, acc[4 * g + 1]);
+                    acc[4 * g + 2] = fmaf(i2f_exact(v0[4 * g + 2]) * sb4.z, sa, acc[4 * g + 2]);
+                    acc[4 * g + 3] = fmaf(i2f_exact(v0[4 * g + 3]) * sb4.w, sa, acc[4 * g + 3]);
+                }
+                if (ncols_here > 32) {
 #pragma unroll
                     for (int g = 0; g < 8; ++g) {
-                        const float4 sb4 = sbv[c * 8 + g];
-                        acc[c * 32 + 4 * g + 0] = fmaf((float)v[4 * g + 0] * sb4.x, sa, acc[c * 32 + 4 * g + 0]);
-                        acc[c * 32 + 4 * g + 1] = fmaf((float)v[4 * g + 1] * sb4.y, sa, acc[c * 32 + 4 * g + 1]);
-                        acc[c * 32 + 4 * g + 2] = fmaf((float)v[4 * g + 2] * sb4.z, sa, acc[c * 32 + 4 * g + 2]);
-                        acc[c * 32 + 4 * g + 3] = fmaf((float)v[4 * g + 3] * sb4.w, sa, acc[c * 32 + 4 * g + 3]);
+                        const float4 sb4 = sbv[8 + g];
+                        acc[32 + 4 * g + 0] = fmaf(i2f_exact(v1[4 * g + 0]) * sb4.x, sa, acc[32 + 4 * g + 0]);
+                        acc[32 + 4 * g + 1] = fmaf(i2f_exact(v1[4 * g + 1]) * sb4.y, sa, acc[32 + 4 * g + 1]);
+                        acc[32 + 4 * g + 2] = fmaf(i2f_exact(v1[4 * g + 2]) * sb4.z, sa, acc[32 + 4 * g + 2]);
+                        acc[32 + 4 * g + 3] = fmaf(i2f_exact(v1[4 * g + 3]) * sb4.w, sa, acc[32 + 4 * g + 3]);
                     }
                 }
             }
@@ -181,7 +209,7 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
                 if (j == kG_BlocksPerStage - 1 || blk == nblocks - 1) mbar_arrive_cta(&sh.empty[st]);   // scales of the stage read
             }
         }
-        Policy::store(p, item, row, q, lane, acc, smem, ok);
+        Policy::store(p, item, row, q, half, lane, acc, smem, ok);
     }
 
     tc_fence_before();
@@ -192,7 +220,7 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
     }
 }
 
-__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // plain fp32 tile store: out[(row0 + r) * ldo + col0 + c] = D[r][c]  (the primitive)
 struct PlainPolicy {
@@ -203,12 +231,12 @@ struct PlainPolicy {
         w.aux0 = it.rows_valid; w.aux1 = it.out_row0; w.aux2 = it.out_col0; w.aux3 = 0;
         return true;
     }
-    __device__ static __forceinline__ void store(const GemmParams& p, const GemmWork& w, int row, int, int, const float (&acc)[128],
-                                                 uint8_t*, bool ok) {
+    __device__ static __forceinline__ void store(const GemmParams& p, const GemmWork& w, int row, int, int half, int,
+                                                 const float (&acc)[64], uint8_t*, bool ok) {
         if (!ok || row >= w.aux0) return;
 #pragma unroll
-        for (int c = 0; c < 128; ++c)
-            if (c < w.n_valid) p.out[(size_t)(w.aux1 + row) * p.ldo + w.aux2 + c] = acc[c];
+        for (int c = 0; c < 64; ++c)
+            if (half * 64 + c < w.n_valid) p.out[(size_t)(w.aux1 + row) * p.ldo + w.aux2 + half * 64 + c] = acc[c];
     }
 };
 
@@ -236,20 +264,21 @@ struct GateUpPolicy {
         w.aux0 = j; w.aux1 = rt; w.aux2 = shared ? 1 : 0; w.aux3 = t.y;
         return true;
     }
-    __device__ static __forceinline__ void store(const PrefillGemmParams& p, const GemmWork& w, int row, int q, int lane,
-                                                 float (&acc)[128], uint8_t* smem, bool ok) {
+    __device__ static __forceinline__ void store(const PrefillGemmParams& p, const GemmWork& w, int row, int q, int half, int lane,
+                                                 float (&acc)[64], uint8_t* smem, bool ok) {
         const bool dual = p.act == CHIMERE_ACT_SWIGLU;
         float* xch = reinterpret_cast<float*>(smem);   // [128][129] floats in the ring, which is idle once ...
         epilogue_sync();                                // ... every epilogue warp has read its last scales from it
 #pragma unroll
-        for (int c = 0; c < 128; ++c) xch[row * 129 + c] = acc[c];
+        for (int c = 0; c < 64; ++c) xch[row * 129 + half * 64 + c] = acc[c];
         epilogue_sync();
         if (!ok || (dual && q >= 2)) return;
-        // this warp's 32 rows form Q8_1 block `blk` of the intermediate
+        // this warp's 32 rows form Q8_1 block `blk` of the intermediate; it quantises its half of the token columns
         const int blk = dual ? w.aux1 * 2 + q : w.aux1 * 4 + q;
         uint8_t* dst = p.out_tiles + (size_t)w.aux0 * p.out_tile_stride + (size_t)blk * kG_TileBytes;
         const int khalf = lane >> 4, kin = lane & 15;
-        for (int c = 0; c < w.n_valid; ++c) {
+        const int c_end = min(w.n_valid, half * 64 + 64);
+        for (int c = half * 64; c < c_end; ++c) {
             const float a = xch[row * 129 + c];
             float v;
             if (dual) v = silu_mul_ref(a, xch[(row + 64) * 129 + c]);
@@ -263,7 +292,7 @@ struct GateUpPolicy {
             if (lane == 0) *reinterpret_cast<float*>(dst + 4096 + c * 4) = __half2float(__float2half(d));
         }
         // columns past n_valid: zero quants and scales, so that the down GEMM's unused columns stay finite
-        for (int c = w.n_valid; c < 128; ++c) {
+        for (int c = max(w.n_valid, half * 64); c < half * 64 + 64; ++c) {
             reinterpret_cast<int8_t*>(dst)[khalf * 2048 + (c >> 3) * 128 + (c & 7) * 16 + kin] = 0;
             if (lane == 0) *reinterpret_cast<float*>(dst + 4096 + c * 4) = 0.0f;
         }
@@ -285,15 +314,16 @@ struct DownPolicy {
         w.aux0 = j; w.aux1 = rt; w.aux2 = shared ? 1 : 0; w.aux3 = t.y;
         return true;
     }
-    __device__ static __forceinline__ void store(const PrefillGemmParams& p, const GemmWork& w, int row, int, int,
-                                                 float (&acc)[128], uint8_t*, bool ok) {
+    __device__ static __forceinline__ void store(const PrefillGemmParams& p, const GemmWork& w, int row, int, int half, int,
+                                                 float (&acc)[64], uint8_t*, bool ok) {
         if (!ok) return;
         const int h = w.aux1 * 128 + row;
         if (h >= p.H) return;
 #pragma unroll
-        for (int c = 0; c < 128; ++c) {
-            if (c < w.n_valid) {
-                const int prow = w.aux2 ? p.T * p.top_k + w.aux3 + c : __ldcg(p.perm + w.aux3 + c);
+        for (int c = 0; c < 64; ++c) {
+            const int col = half * 64 + c;
+            if (col < w.n_valid) {
+                const int prow = w.aux2 ? p.T * p.top_k + w.aux3 + col : __ldcg(p.perm + w.aux3 + col);
                 p.pair_out[(size_t)prow * p.H + h] = acc[c];
             }
         }
