@@ -67,8 +67,7 @@ Layout make_layout(const chimere_moe_layer* w, int T) {
     L.max_entries = max_entries_for(w, T);
     L.tile_rows = down_tile_rows(w->type_down, w->F, w->type_sh_down, w->F_s);
     L.n_row_tiles = (H + L.tile_rows - 1) / L.tile_rows;
-    L.n_row_tiles_tiled = (H + 32 * tiled_down_geom(w->type_down, w->F, w->type_sh_down, w->F_s).wr - 1) /
-                          (32 * tiled_down_geom(w->type_down, w->F, w->type_sh_down, w->F_s).wr);
+    L.n_row_tiles_tiled = (H + 31) / 32;   // counters for the finest row tiling any batch size may choose
     const int max_tiles = L.n_row_tiles > L.n_row_tiles_tiled ? L.n_row_tiles : L.n_row_tiles_tiled;
     L.n_counters = kCtrRouteTile + (T + 7) / 8 + T * max_tiles;
     L.inter_stride = ((size_t)(Fmax / 32) * kQ81Bytes + 15) & ~(size_t)15;   // rows start on 16-byte boundaries (bulk copies)
@@ -309,7 +308,10 @@ static GemvParams down_params(const chimere_moe_layer* w, float* d_y, int T, chi
     g.y = d_y;
     g.combine_ctr = ws->counters + kCtrRouteTile + (ws->max_T + 7) / 8;
     g.tile_rows = L.tile_rows;
-    g.n_row_tiles = (w->layout == CHIMERE_LAYOUT_TILED32) ? L.n_row_tiles_tiled : L.n_row_tiles;
+    g.n_row_tiles = (w->layout == CHIMERE_LAYOUT_TILED32)
+                        ? (w->H + 32 * tiled_down_geom(w->type_down, w->F, w->type_sh_down, w->F_s, T).wr - 1) /
+                              (32 * tiled_down_geom(w->type_down, w->F, w->type_sh_down, w->F_s, T).wr)
+                        : L.n_row_tiles;
     return g;
 }
 

@@ -74,7 +74,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 // ---- per-type decode of one 32-weight unit into eight int8x4 words -----------------------
 // Unit b of a row = 32 consecutive weights (a Q4_0 / Q8_0 block, or sub-block b%8 of IQ3_S
 // super-block b/8).  load() returns the signed int8 weights packed four per word such that
-// sum_g dp4a(w[g], q8word[g]) is the integer block dot times `kDiv`; scale() gives the factor.
+// finish(sum_g dp4a(w[g], q8word[g]), mul) is the integer block dot (Q4_0 words carry 16x the weight,
+// IQ3_S units a per-sub-block multiplier `mul`).
 template <int TYPE> struct Unit;
 
 template <> struct Unit<CHIMERE_TYPE_Q8_0> {

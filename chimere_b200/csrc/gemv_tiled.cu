@@ -282,11 +282,15 @@ TiledGeomHost tiled_gate_up_geom(int type_routed, int type_shared, int H, bool h
     const Geom t = geom_for(ngroups_of(H));
     return TiledGeomHost{t.wk, t.wr};
 }
-TiledGeomHost tiled_down_geom(int type_routed, int F, int type_shared, int F_s) {
+// Down stage: rows are short (F columns), so a warp should keep a whole row tile to itself when there is enough
+// rows allow it (16 units per warp amortise the CTA's fixed work).
+TiledGeomHost tiled_down_geom(int type_routed, int F, int type_shared, int F_s, int T) {
     (void)type_routed; (void)type_shared;
     int g = ngroups_of(F);
     if (F_s > 0) g = min(g, ngroups_of(F_s));
-    const Geom t = geom_for(g);
+    Geom t = geom_for(g);
+    (void)T;   // the same split for every batch size: a token's sums are added in the same order whatever its batch
+    while (t.wk > 1 && g / t.wk < 4) { t.wk >>= 1; t.wr <<= 1; }   // at least four groups per warp
     return TiledGeomHost{t.wk, t.wr};
 }
 
@@ -326,7 +330,7 @@ cudaError_t launch_gate_up_tiled(const GemvParams& p, int max_entries, cudaStrea
 
 // p.n_row_tiles must be ceil(H / (32 * wr)) with the geometry of tiled_down_geom
 cudaError_t launch_down_tiled(const GemvParams& p, int max_entries, cudaStream_t stream) {
-    const TiledGeomHost g = tiled_down_geom(p.type_routed, p.ncols_routed, p.type_shared, p.nrows_shared > 0 ? p.ncols_shared : 0);
+    const TiledGeomHost g = tiled_down_geom(p.type_routed, p.ncols_routed, p.type_shared, p.nrows_shared > 0 ? p.ncols_shared : 0, p.T);
     cudaError_t e = dispatch_tile<kStageDown>(p.type_routed, p, max_entries, g.wk, g.wr, stream);
     if (e == cudaSuccess && p.nrows_shared > 0 && p.type_shared != p.type_routed)
         e = dispatch_tile<kStageDown>(p.type_shared, p, max_entries, g.wk, g.wr, stream);

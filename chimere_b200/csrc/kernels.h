@@ -132,7 +132,7 @@ cudaError_t launch_pack_mma128(const int8_t* q, const float* scales, uint8_t* ou
 // tiled32 layout (tiled.cuh): pack, kernels on packed weights, parity tap
 struct TiledGeomHost { int wk, wr; };  // warps along K x row tiles per CTA (wk * wr = 8)
 TiledGeomHost tiled_gate_up_geom(int type_routed, int type_shared, int H, bool has_shared);
-TiledGeomHost tiled_down_geom(int type_routed, int F, int type_shared, int F_s);
+TiledGeomHost tiled_down_geom(int type_routed, int F, int type_shared, int F_s, int T);
 cudaError_t launch_pack(int type, const void* raw, void* out, int n_mats, int nrows, int ncols, int64_t raw_stride,
                         int64_t out_stride, cudaStream_t stream);
 cudaError_t launch_gate_up_tiled(const GemvParams& p, int max_entries, cudaStream_t stream);
