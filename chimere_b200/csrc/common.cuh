@@ -71,6 +71,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start while its predecessor in the
+// stream still runs; griddep_wait() blocks until that predecessor has completed and its writes are visible
+// (a no-op for a normally launched kernel).  griddep_launch() lets the successor's CTAs start once every CTA
+// of this grid has called it or exited.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- per-type decode of one 32-weight unit into eight int8x4 words -----------------------
 // Unit b of a row = 32 consecutive weights (a Q4_0 / Q8_0 block, or sub-block b%8 of IQ3_S
 // super-block b/8).  load() returns the signed int8 weights packed four per word such that

@@ -112,6 +112,9 @@ __global__ void __launch_bounds__(kThreadsT, 4) tile_kernel(const GemvParams p, 
     __shared__ int s_tok[kMaxGroupTokens];
     __shared__ int s_done[kMaxGroupTokens];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nthreads = (int)blockDim.x, nwarps = nthreads >> 5;
+    griddep_wait();
+    griddep_launch();
     // one look-up names everything the CTA needs: the entry (expert, token count, pair rows)
     const int4* entv = reinterpret_cast<const int4*>(p.group_list + kListHeader + kListEntry * blockIdx.y);
     const int n_entries = __ldcg(p.group_list);
@@ -158,9 +161,9 @@ __global__ void __launch_bounds__(kThreadsT, 4) tile_kernel(const GemvParams p, 
     for (int i = 0; i < m; ++i) {
         const int irow = (STAGE == kStageGateUp) ? s_tok[i] : s_row[i];
         const uint4* sq = reinterpret_cast<const uint4*>(p.in_soa_q + (size_t)irow * p.in_soa_q_stride);
-        for (int v = tid; v < ncols / 16; v += kThreadsT) *reinterpret_cast<uint4*>(smem + ts.aq + i * qrow + v * 16) = __ldcg(sq + v);
+        for (int v = tid; v < ncols / 16; v += nthreads) *reinterpret_cast<uint4*>(smem + ts.aq + i * qrow + v * 16) = __ldcg(sq + v);
         const float* sd = p.in_soa_d + (size_t)irow * p.in_soa_d_stride;
-        for (int v = tid; v < nb; v += kThreadsT) *reinterpret_cast<float*>(smem + ts.ad + i * drow + v * 4) = __ldcg(sd + v);
+        for (int v = tid; v < nb; v += nthreads) *reinterpret_cast<float*>(smem + ts.ad + i * drow + v * 4) = __ldcg(sd + v);
     }
     __syncthreads();
 
@@ -200,7 +203,7 @@ __global__ void __launch_bounds__(kThreadsT, 4) tile_kernel(const GemvParams p, 
 
     if (STAGE == kStageGateUp) {
         // (token, row tile): sum the K slices, activation, Q8_1 of the 32 results (lane = element)
-        for (int pr = warp; pr < m * wr; pr += kWarpsT) {
+        for (int pr = warp; pr < m * wr; pr += nwarps) {
             const int i = pr / wr, wq = pr - i * wr;
             if (tile0 + wq >= tiles_total) continue;
             const float u = sum_slices(red, 0, wk, i, width, wq * 32 + lane);
@@ -228,7 +231,7 @@ __global__ void __launch_bounds__(kThreadsT, 4) tile_kernel(const GemvParams p, 
     }
 
     const int H = p.H, r0 = tile0 * 32, rows_here = min(width, H - r0);
-    for (int e = tid; e < m * width; e += kThreadsT) {
+    for (int e = tid; e < m * width; e += nthreads) {
         const int i = e / width, c = e - i * width;
         if (c < rows_here) p.pair_out[(size_t)s_row[i] * H + r0 + c] = sum_slices(red, 0, wk, i, width, c);
     }
@@ -253,7 +256,254 @@ __global__ void __launch_bounds__(kThreadsT, 4) tile_kernel(const GemvParams p, 
     for (int i = 0; i < m; ++i) {
         if (!s_done[i]) continue;
         const int t = s_tok[i];
-        for (int r = tid; r < rows_here; r += kThreadsT) {
+        for (int r = tid; r < rows_here; r += nthreads) {
+            const int h = r0 + r;
+            float sum = 0.0f;   // weighted_combine_kernel (chimere_kernels.cu:1551-1565): slots ascending
+            for (int j = 0; j < k; ++j)
+                sum = fmaf(p.topk_w[(size_t)t * k + j], __ldcg(p.pair_out + ((size_t)t * k + j) * H + h), sum);
+            if (p.nrows_shared > 0) {  // sigmoid_gate_add_kernel (scratch_pool.rs:266-277)
+                const float sh = __ldcg(p.pair_out + ((size_t)p.T * k + t) * H + h);
+                if (p.sh_gate_logit) sum = fmaf(sh, sigmoid_ref(__ldcg(p.sh_gate_logit + t)), sum);
+                else sum = sh + sum;
+            }
+            p.y[(size_t)t * H + h] = sum;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// The same work with the weights brought in by bulk asynchronous copies.
+//
+// A CTA's weights are one contiguous piece of the tiled layout per (matrix, row tile, K slice), so every warp
+// asks for its own pieces with one cp.async.bulk each as soon as the work entry is known and waits for them on
+// its own mbarrier: no address arithmetic, no register staging and no L2 prefetch in the inner loop, and the
+// copies run while the CTA stages the activations.  Units are then read from shared memory with the same
+// 128-bit-per-lane pattern (conflict-free).  A CTA holds all its weights at once; several CTAs per SM keep
+// enough bytes in flight.  Tokens are taken `mt` at a time so that the planes stay small.
+struct BulkSmem { uint32_t w_slot, aq, ad, red, total, q_row, d_row; };
+__host__ __device__ inline BulkSmem bulk_smem(uint32_t tile_bytes_max, int ncols_max, int wr, int wk, int nmat, int mt, bool need_red) {
+    BulkSmem s;
+    s.w_slot = (tile_bytes_max + 127u) & ~127u;
+    s.q_row = (uint32_t)ncols_max;
+    s.d_row = ((uint32_t)(ncols_max / 32) * 4 + 15u) & ~15u;
+    uint32_t o = (uint32_t)nmat * wr * s.w_slot;
+    s.aq = o; o += (uint32_t)mt * s.q_row;
+    s.ad = o; o += (uint32_t)mt * s.d_row;
+    s.red = o; o += need_red ? (uint32_t)nmat * wk * mt * 32 * wr * 4 : 0u;
+    s.total = o;
+    return s;
+}
+
+template <int TYPE, int M>
+__device__ __forceinline__ void dot_pass_s(uint32_t tile, int g0, int g1, int lane, int nb, uint32_t aq, int qrow, uint32_t ad, int drow,
+                                           int mrem, float (&acc)[M]) {
+    using TT = Tiled<TYPE>;
+    for (int g = g0; g < g1; ++g) {
+        const int nu = min(kGroupUnits, nb - g * kGroupUnits);
+        typename TT::Regs r;
+        TT::loads(tile, g, lane, nu, r);
+        if (nu == kGroupUnits) group_units<TYPE, M, true>(r, g, nu, aq, qrow, ad, drow, mrem, acc);
+        else group_units<TYPE, M, false>(r, g, nu, aq, qrow, ad, drow, mrem, acc);
+    }
+}
+
+// grid = (row items, max entries), block = 32 * wr * wk threads (wk = 1 << wk_shift, wr = 1 << wr_shift).
+template <int TYPE, int STAGE, bool DUAL, int MT>
+__global__ void __launch_bounds__(kThreadsT, 3) bulk_kernel(const GemvParams p, int wk_shift, int wr_shift, uint32_t tile_bytes_max) {
+    constexpr int mt = MT;   // tokens per pass
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int s_row[kMaxGroupTokens];
+    __shared__ int s_tok[kMaxGroupTokens];
+    __shared__ int s_done[kMaxGroupTokens];
+    __shared__ __align__(8) uint64_t s_bar[kWarpsT];
+    using TT = Tiled<TYPE>;
+    constexpr int kMat = DUAL ? 2 : 1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wk = 1 << wk_shift, wr = 1 << wr_shift, nwarps = wk * wr, nthreads = 32 * nwarps;
+    // Gate/up follows the kernel that writes the work list: wait for it, then let the down stage's CTAs come in
+    // behind this grid.  The down stage is launched after a gate/up grid whose CTAs all passed that wait, so the
+    // list is complete when its CTAs start: they look up their entry and ask for their weights first, and wait
+    // for the gate/up results only then.
+    if (STAGE == kStageGateUp) { griddep_wait(); griddep_launch(); }
+    const int4* entv = reinterpret_cast<const int4*>(p.group_list + kListHeader + kListEntry * blockIdx.y);
+    const int n_entries = __ldcg(p.group_list);
+    const int4 e0 = __ldcg(entv), e1 = __ldcg(entv + 1), e2 = __ldcg(entv + 2);
+    if ((int)blockIdx.y >= n_entries) return;
+    const int expert = e0.x, m = e0.z;
+    const bool shared = expert < 0;
+    if ((shared ? p.type_shared : p.type_routed) != TYPE) return;
+    const int nrows = shared ? p.nrows_shared : p.nrows_routed;
+    const int ncols = shared ? p.ncols_shared : p.ncols_routed, nb = ncols >> 5;
+    const int width = 32 * wr, tile0 = blockIdx.x << wr_shift, tiles_total = nrows >> 5;
+    if (tile0 >= tiles_total) return;
+    const bool need_red = STAGE == kStageGateUp || wk > 1;
+    const BulkSmem bs = bulk_smem(tile_bytes_max, max(p.ncols_routed, p.ncols_shared), wr, wk, kMat, mt, need_red);
+    float* red = reinterpret_cast<float*>(smem + bs.red);
+    const uint32_t aq = smem_u32(smem + bs.aq), ad = smem_u32(smem + bs.ad);
+    const int qrow = (int)bs.q_row, drow = (int)bs.d_row;
+
+    // ---- this warp's pieces: K slice [u0, u1) of row tile tile0 + wr_id, of one or two matrices ----
+    const int wr_id = warp >> wk_shift, wk_id = warp & (wk - 1);
+    const bool tile_valid = tile0 + wr_id < tiles_total;
+    const int upw = ((((nb + wk - 1) >> wk_shift) + TT::kChunkUnits - 1) / TT::kChunkUnits) * TT::kChunkUnits;
+    const int u0 = min(nb, wk_id * upw), u1 = min(nb, u0 + upw);
+    const uint32_t off = TT::unit_offset(u0), bytes = tile_valid ? TT::unit_offset(u1) - off : 0u;
+    const int64_t tb = TT::tile_bytes(ncols);
+    const uint32_t ws0 = smem_u32(smem) + (uint32_t)wr_id * bs.w_slot, ws1 = ws0 + (uint32_t)wr * bs.w_slot;
+    if (bytes > 0 && lane == 0) {
+        const uint8_t* wa = (STAGE == kStageGateUp ? (shared ? p.sh_b : p.w_b + (size_t)expert * p.stride_b)
+                                                   : (shared ? p.sh_a : p.w_a + (size_t)expert * p.stride_a)) + (size_t)(tile0 + wr_id) * tb;
+        mbar_init(&s_bar[warp], 1);
+        mbar_fence_init();
+        mbar_expect_tx(&s_bar[warp], bytes * kMat);
+        bulk_g2s(smem + (size_t)wr_id * bs.w_slot + off, wa + off, bytes, &s_bar[warp]);
+        if (DUAL) {
+            const uint8_t* wb = (shared ? p.sh_a : p.w_a + (size_t)expert * p.stride_a) + (size_t)(tile0 + wr_id) * tb;
+            bulk_g2s(smem + (size_t)(wr + wr_id) * bs.w_slot + off, wb + off, bytes, &s_bar[warp]);
+        }
+    }
+    if (tid < kMaxGroupTokens) {
+        const int rows[kMaxGroupTokens] = {e1.x, e1.y, e1.z, e1.w, e2.x, e2.y, e2.z, e2.w};
+        int prow = 0;
+#pragma unroll
+        for (int j = 0; j < kMaxGroupTokens; ++j) if (j == tid) prow = rows[j];
+        s_row[tid] = prow;
+        s_tok[tid] = shared ? prow - p.T * p.top_k : prow / p.top_k;
+    }
+    if (STAGE == kStageDown) griddep_wait();
+    __syncthreads();   // also orders lane 0's barrier set-up before the other lanes' wait
+
+    const int g0 = u0 / kGroupUnits, g1 = (u1 + kGroupUnits - 1) / kGroupUnits;
+    const int H = p.H, r0 = tile0 * 32, rows_here = min(width, H - r0);
+    bool arrived = false;
+    for (int i0 = 0; i0 < m; i0 += mt) {
+        const int mp = min(mt, m - i0);
+        if (i0 > 0) __syncthreads();   // the planes and partial sums of the previous tokens are no longer read
+        // activations of tokens i0 .. i0+mp: int8 plane and f32 scale plane
+        {
+            const int vq = ncols >> 4, vd = (nb + 3) >> 2;
+            for (int v = tid; v < mp * vq; v += nthreads) {
+                const int i = v / vq, c = v - i * vq;
+                const int irow = (STAGE == kStageGateUp) ? s_tok[i0 + i] : s_row[i0 + i];
+                *reinterpret_cast<uint4*>(smem + bs.aq + i * qrow + c * 16) =
+                    __ldcg(reinterpret_cast<const uint4*>(p.in_soa_q + (size_t)irow * p.in_soa_q_stride) + c);
+            }
+            for (int v = tid; v < mp * vd; v += nthreads) {
+                const int i = v / vd, c = v - i * vd;
+                const int irow = (STAGE == kStageGateUp) ? s_tok[i0 + i] : s_row[i0 + i];
+                *reinterpret_cast<uint4*>(smem + bs.ad + i * drow + c * 16) =
+                    __ldcg(reinterpret_cast<const uint4*>(p.in_soa_d + (size_t)irow * p.in_soa_d_stride) + c);
+            }
+        }
+        __syncthreads();
+        if (!arrived) {
+            if (bytes > 0 && !mbar_wait(&s_bar[warp], 0)) {
+                if (lane == 0 && p.status) atomicOr(p.status, kStatusWaitTimeout);
+                mbar_wait(&s_bar[warp], 0);   // give the copies in flight a second, equally bounded, chance before going on
+            }
+            arrived = true;
+        }
+#pragma unroll
+        for (int mat = 0; mat < kMat; ++mat) {
+            float acc[MT];
+#pragma unroll
+            for (int i = 0; i < MT; ++i) acc[i] = 0.0f;
+            const uint32_t tile = mat == 0 ? ws0 : ws1;
+            if (bytes > 0) {
+                if (MT == 1 || mp == 1) {
+                    float a1[1] = {0.0f};
+                    dot_pass_s<TYPE, 1>(tile, g0, g1, lane, nb, aq, qrow, ad, drow, 1, a1);
+                    acc[0] = a1[0];
+                } else if (MT == 2 || mp == 2) {
+                    float a2[2] = {0.0f, 0.0f};
+                    dot_pass_s<TYPE, 2>(tile, g0, g1, lane, nb, aq, qrow, ad, drow, 2, a2);
+                    acc[0] = a2[0]; acc[MT > 1 ? 1 : 0] = a2[1];
+                } else {
+                    // four tokens at a time; tokens 4..7 read the weights from shared memory again
+#pragma unroll
+                    for (int h = 0; h < MT / 4; ++h) {
+                        if (4 * h < mp) {
+                            float a4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                            dot_pass_s<TYPE, 4>(tile, g0, g1, lane, nb, aq + 4 * h * qrow, qrow, ad + 4 * h * drow, drow, mp - 4 * h, a4);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) acc[(4 * h + i) < MT ? 4 * h + i : 0] = a4[i];
+                        }
+                    }
+                }
+            }
+            if (need_red) {
+#pragma unroll
+                for (int i = 0; i < MT; ++i)
+                    if (i < mp) red[((mat * wk + wk_id) * mt + i) * width + wr_id * 32 + lane] = acc[i];
+            } else if (tile_valid) {
+                // a warp owns its rows' whole sums: straight to the per-pair rows
+#pragma unroll
+                for (int i = 0; i < MT; ++i)
+                    if (i < mp) p.pair_out[(size_t)s_row[i0 + i] * H + r0 + wr_id * 32 + lane] = acc[i];
+            }
+        }
+        if (!need_red) continue;
+        __syncthreads();
+        if (STAGE == kStageGateUp) {
+            // (token, row tile): sum the K slices, activation, Q8_1 of the 32 results (lane = element)
+            for (int pr = warp; pr < (mp << wr_shift); pr += nwarps) {
+                const int i = pr >> wr_shift, wq = pr & (wr - 1);
+                if (tile0 + wq >= tiles_total) continue;
+                float u = 0.0f, g = 0.0f;
+                for (int k = 0; k < wk; ++k) {
+                    u += red[(k * mt + i) * width + wq * 32 + lane];
+                    if (DUAL) g += red[((wk + k) * mt + i) * width + wq * 32 + lane];
+                }
+                float v;
+                if (DUAL) v = silu_mul_ref(g, u);
+                else { const float r = fmaxf(u, 0.0f); v = r * r; }
+                float amax = fabsf(v), sum = v;
+#pragma unroll
+                for (int s = 16; s > 0; s >>= 1) {
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+                    sum += __shfl_xor_sync(0xffffffffu, sum, s);
+                }
+                const float d = amax / 127.0f;
+                const int8_t q = (amax == 0.0f) ? (int8_t)0 : (int8_t)roundf(v / d);
+                const int orow = s_row[i0 + i];
+                uint8_t* out = p.inter_q8 + (size_t)orow * p.inter_stride + (size_t)(tile0 + wq) * kQ81Bytes;
+                reinterpret_cast<int8_t*>(out)[4 + lane] = q;
+                const __half dh = __float2half(d);
+                if (lane == 0) *reinterpret_cast<__half2*>(out) = __halves2half2(dh, __float2half(sum));
+                p.out_soa_q[(size_t)orow * p.out_soa_q_stride + (size_t)(tile0 + wq) * 32 + lane] = q;
+                if (lane == 0) p.out_soa_d[(size_t)orow * p.out_soa_d_stride + (tile0 + wq)] = __half2float(dh);
+            }
+        } else {
+            for (int e = tid; e < mp * width; e += nthreads) {
+                const int i = e / width, c = e - i * width;
+                if (c < rows_here) {
+                    float v = 0.0f;
+                    for (int k = 0; k < wk; ++k) v += red[(k * mt + i) * width + c];
+                    p.pair_out[(size_t)s_row[i0 + i] * H + r0 + c] = v;
+                }
+            }
+        }
+    }
+    if (STAGE == kStageGateUp || p.no_combine) return;
+    // Whoever completes a token's contributions for this row item adds them up (see tile_kernel).
+    __syncthreads();
+    if (tid == 0) {
+        const int expected = p.top_k + (p.nrows_shared > 0 ? 1 : 0);
+        __threadfence();
+        for (int i = 0; i < m; ++i) {
+            int* ctr = p.combine_ctr + (size_t)s_tok[i] * p.n_row_tiles + blockIdx.x;
+            const int c = atomicAdd(ctr, 1);
+            s_done[i] = (c == expected - 1);
+            if (c == expected - 1) *ctr = 0;
+        }
+        __threadfence();
+    }
+    __syncthreads();
+    const int k = p.top_k;
+    for (int i = 0; i < m; ++i) {
+        if (!s_done[i]) continue;
+        const int t = s_tok[i];
+        for (int r = tid; r < rows_here; r += nthreads) {
             const int h = r0 + r;
             float sum = 0.0f;   // weighted_combine_kernel (chimere_kernels.cu:1551-1565): slots ascending
             for (int j = 0; j < k; ++j)
@@ -271,27 +521,50 @@ __global__ void __launch_bounds__(kThreadsT, 4) tile_kernel(const GemvParams p, 
 // ------------------------------------------------------------------ launchers --------------
 struct Geom { int wk, wr; };
 static int ngroups_of(int ncols) { return (ncols / 32 + kGroupUnits - 1) / kGroupUnits; }
+static int64_t tile_bytes_of(int type, int ncols) { return tiled_matrix_bytes(type, 32, ncols); }
+static int log2i(int v) { int s = 0; while ((1 << s) < v) ++s; return s; }
+
+// Launch with programmatic stream serialization: the grid may start while the previous kernel of the stream is
+// still running; the kernels call griddep_wait() before they touch what that kernel writes.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, int threads, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// Gate/up: one row tile per CTA, its K range cut over the eight warps.
 static Geom geom_for(int ngroups_min) {
     int wk = kWarpsT;
     while (wk > 1 && wk > ngroups_min) wk >>= 1;
     return Geom{wk, kWarpsT / wk};
 }
-
 TiledGeomHost tiled_gate_up_geom(int type_routed, int type_shared, int H, bool has_shared) {
     (void)type_routed; (void)type_shared; (void)has_shared;
     const Geom t = geom_for(ngroups_of(H));
     return TiledGeomHost{t.wk, t.wr};
 }
-// Down stage: rows are short (F columns), so a warp should keep a whole row tile to itself when there is enough
-// rows allow it (16 units per warp amortise the CTA's fixed work).
+// Down stage: rows are short (F columns), so a warp keeps a whole row tile to itself when that leaves it at most
+// four groups; the CTA takes as many row tiles as keep its weights near 40 KB.  The same split for every batch
+// size: a token's sums are added in the same order whatever its batch.
 TiledGeomHost tiled_down_geom(int type_routed, int F, int type_shared, int F_s, int T) {
-    (void)type_routed; (void)type_shared;
+    (void)T;
     int g = ngroups_of(F);
-    if (F_s > 0) g = min(g, ngroups_of(F_s));
-    Geom t = geom_for(g);
-    (void)T;   // the same split for every batch size: a token's sums are added in the same order whatever its batch
-    while (t.wk > 1 && g / t.wk < 4) { t.wk >>= 1; t.wr <<= 1; }   // at least four groups per warp
-    return TiledGeomHost{t.wk, t.wr};
+    int64_t tb = tile_bytes_of(type_routed, F);
+    if (F_s > 0) { g = min(g, ngroups_of(F_s)); tb = max(tb, tile_bytes_of(type_shared, F_s)); }
+    int wk = 1;
+    while (wk < kWarpsT && g / wk > 4) wk <<= 1;
+    int wr = kWarpsT / wk;
+    while (wr > 1 && (int64_t)wr * tb > 40 * 1024) wr >>= 1;
+    return TiledGeomHost{wk, wr};
 }
 
 template <int TYPE, int STAGE, bool DUAL>
@@ -302,22 +575,77 @@ static cudaError_t launch_tile_t(const GemvParams& p, int max_entries, int wk, i
     if (e != cudaSuccess) return e;
     const int rows = max(p.nrows_routed, p.nrows_shared);
     const int items = (rows / 32 + wr - 1) / wr;
-    tile_kernel<TYPE, STAGE, DUAL><<<dim3(items, max_entries), kThreadsT, ts.total, stream>>>(p, wk, wr);
-    return cudaGetLastError();
+    return launch_pdl(tile_kernel<TYPE, STAGE, DUAL>, dim3(items, max_entries), 32 * wk * wr, ts.total, stream, p, wk, wr);
+}
+
+// How the bulk-copy kernel fits an SM: CTAs per SM and tokens per pass.  ok = false: the weights of one CTA do not
+// fit, or something is not 16-byte aligned; the caller then takes the kernel that loads through registers.
+struct BulkPlan { bool ok; int mt; uint32_t tile_bytes_max, smem; };
+static BulkPlan plan_bulk(const GemvParams& p, int stage, bool dual, int wk, int wr) {
+    BulkPlan b{false, 0, 0, 0};
+    const bool gu = stage == kStageGateUp;
+    int64_t tb = tile_bytes_of(p.type_routed, p.ncols_routed);
+    if (p.nrows_shared > 0) tb = max(tb, tile_bytes_of(p.type_shared, p.ncols_shared));
+    const uintptr_t ptrs = (uintptr_t)p.w_a | (uintptr_t)p.w_b | (uintptr_t)p.sh_a | (uintptr_t)p.sh_b | (uintptr_t)p.in_soa_q |
+                           (uintptr_t)p.in_soa_d | (uintptr_t)p.stride_a | (uintptr_t)p.stride_b | (uintptr_t)p.in_soa_q_stride |
+                           (uintptr_t)(p.in_soa_d_stride * 4);
+    if (ptrs & 15) return b;
+    const int nmat = dual ? 2 : 1;
+    const bool need_red = gu || wk > 1;
+    const int ncols_max = max(p.ncols_routed, p.ncols_shared);
+    const int threads = 32 * wk * wr;
+    const int sm_bytes = 227 * 1024, per_cta = 1024 + 256;   // the system's reserve and the kernel's static variables
+    const int max_ctas = min(8, 1536 / threads);
+    // decode-size batches: as many CTAs per SM as fit one token per pass, then as many tokens as still fit;
+    // larger batches: at least four tokens per pass if that fits at all
+    const int mt_floor = (p.T > 16) ? 4 : 1;
+    for (int floor_mt = mt_floor; floor_mt >= 1 && !b.ok; floor_mt = (floor_mt == 1 ? 0 : 1)) {
+        int ctas = 0;
+        for (int c = max_ctas; c >= 1; --c)
+            if ((int64_t)bulk_smem((uint32_t)tb, ncols_max, wr, wk, nmat, floor_mt, need_red).total <= sm_bytes / c - per_cta) { ctas = c; break; }
+        if (!ctas) continue;
+        for (int mt = kMaxGroupTokens; mt >= floor_mt; mt >>= 1)
+            if ((int64_t)bulk_smem((uint32_t)tb, ncols_max, wr, wk, nmat, mt, need_red).total <= sm_bytes / ctas - per_cta) {
+                b.ok = true; b.mt = mt; b.tile_bytes_max = (uint32_t)tb;
+                b.smem = bulk_smem((uint32_t)tb, ncols_max, wr, wk, nmat, mt, need_red).total;
+                break;
+            }
+    }
+    return b;
+}
+
+template <int TYPE, int STAGE, bool DUAL, int MT>
+static cudaError_t launch_bulk_m(const GemvParams& p, int max_entries, int wk, int wr, const BulkPlan& b, cudaStream_t stream) {
+    cudaError_t e = cudaFuncSetAttribute(bulk_kernel<TYPE, STAGE, DUAL, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    if (e != cudaSuccess) return e;
+    const int rows = max(p.nrows_routed, p.nrows_shared);
+    const int items = (rows / 32 + wr - 1) / wr;
+    return launch_pdl(bulk_kernel<TYPE, STAGE, DUAL, MT>, dim3(items, max_entries), 32 * wk * wr, b.smem, stream, p, log2i(wk), log2i(wr),
+                      b.tile_bytes_max);
+}
+template <int TYPE, int STAGE, bool DUAL>
+static cudaError_t launch_bulk_t(const GemvParams& p, int max_entries, int wk, int wr, const BulkPlan& b, cudaStream_t stream) {
+    switch (b.mt) {
+        case 1: return launch_bulk_m<TYPE, STAGE, DUAL, 1>(p, max_entries, wk, wr, b, stream);
+        case 2: return launch_bulk_m<TYPE, STAGE, DUAL, 2>(p, max_entries, wk, wr, b, stream);
+        case 4: return launch_bulk_m<TYPE, STAGE, DUAL, 4>(p, max_entries, wk, wr, b, stream);
+        default: return launch_bulk_m<TYPE, STAGE, DUAL, 8>(p, max_entries, wk, wr, b, stream);
+    }
 }
 
 template <int STAGE>
 static cudaError_t dispatch_tile(int type, const GemvParams& p, int max_entries, int wk, int wr, cudaStream_t stream) {
     const bool dual = STAGE == kStageGateUp && p.act == CHIMERE_ACT_SWIGLU;
+    const BulkPlan b = plan_bulk(p, STAGE, dual, wk, wr);
+#define CHIMERE_LAUNCH(T_, D_) \
+    (b.ok ? launch_bulk_t<T_, STAGE, D_>(p, max_entries, wk, wr, b, stream) : launch_tile_t<T_, STAGE, D_>(p, max_entries, wk, wr, stream))
     switch (type) {
-        case CHIMERE_TYPE_Q4_0: return dual ? launch_tile_t<CHIMERE_TYPE_Q4_0, STAGE, true>(p, max_entries, wk, wr, stream)
-                                            : launch_tile_t<CHIMERE_TYPE_Q4_0, STAGE, false>(p, max_entries, wk, wr, stream);
-        case CHIMERE_TYPE_Q8_0: return dual ? launch_tile_t<CHIMERE_TYPE_Q8_0, STAGE, true>(p, max_entries, wk, wr, stream)
-                                            : launch_tile_t<CHIMERE_TYPE_Q8_0, STAGE, false>(p, max_entries, wk, wr, stream);
-        case CHIMERE_TYPE_IQ3_S: return dual ? launch_tile_t<CHIMERE_TYPE_IQ3_S, STAGE, true>(p, max_entries, wk, wr, stream)
-                                             : launch_tile_t<CHIMERE_TYPE_IQ3_S, STAGE, false>(p, max_entries, wk, wr, stream);
+        case CHIMERE_TYPE_Q4_0: return dual ? CHIMERE_LAUNCH(CHIMERE_TYPE_Q4_0, true) : CHIMERE_LAUNCH(CHIMERE_TYPE_Q4_0, false);
+        case CHIMERE_TYPE_Q8_0: return dual ? CHIMERE_LAUNCH(CHIMERE_TYPE_Q8_0, true) : CHIMERE_LAUNCH(CHIMERE_TYPE_Q8_0, false);
+        case CHIMERE_TYPE_IQ3_S: return dual ? CHIMERE_LAUNCH(CHIMERE_TYPE_IQ3_S, true) : CHIMERE_LAUNCH(CHIMERE_TYPE_IQ3_S, false);
         default: return cudaErrorInvalidValue;
     }
+#undef CHIMERE_LAUNCH
 }
 
 cudaError_t launch_gate_up_tiled(const GemvParams& p, int max_entries, cudaStream_t stream) {

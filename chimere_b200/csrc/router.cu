@@ -224,6 +224,7 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
     const int nrows = E + (p.shexp_gate_w ? 1 : 0);
     const int t0 = blockIdx.y * TT, r0 = blockIdx.x * TE;
     const int n_rtiles = gridDim.x;
+    griddep_launch();   // the grouped GEMV that follows may bring its CTAs in; it waits for this grid before it reads anything
 
     // ---- Q8_1 of this token tile's input rows, blocks dealt round-robin to the row tiles ----
     {

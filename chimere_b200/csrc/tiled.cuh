@@ -41,6 +41,11 @@ __device__ __forceinline__ uint4 lds128(uint32_t a) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
     return v;
 }
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
 __device__ __forceinline__ uint32_t lds32(uint32_t a) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
@@ -71,6 +76,15 @@ template <> struct Tiled<CHIMERE_TYPE_Q4_0> {
         for (int u = 0; u < kGroupUnits; ++u)
             if (u < nu) prefetch_l2(g + u * kUnitBytes + lane * 16);
     }
+    // the same group from a copy of the tile in shared memory (shared address `tile`)
+    __device__ static __forceinline__ void loads(uint32_t tile, int grp, int lane, int nu, Regs& r) {
+        const uint32_t g = tile + (uint32_t)grp * (kGroupUnits * kUnitBytes);
+#pragma unroll
+        for (int u = 0; u < kGroupUnits; ++u)
+            if (u < nu) { r.v[u] = lds128(g + u * kUnitBytes + lane * 16); r.d[u] = lds16(g + u * kUnitBytes + 512 + lane * 2); }
+    }
+    static constexpr int kChunkUnits = 4;
+    __host__ __device__ static uint32_t unit_offset(int u) { return (uint32_t)u * kUnitBytes; }   // u: a chunk boundary or the row's end
     __device__ static __forceinline__ void decode(const Regs& r, int u, int (&w)[8]) {
         const uint32_t x[4] = {r.v[u].x, r.v[u].y, r.v[u].z, r.v[u].w};
 #pragma unroll
@@ -101,6 +115,17 @@ template <> struct Tiled<CHIMERE_TYPE_IQ3_S> {
         for (int u = 0; u < kGroupUnits; ++u)
             if (u < nu) prefetch_l2(g + (u0 + u) * 512 + lane * 16);
     }
+    __device__ static __forceinline__ void loads(uint32_t tile, int grp, int lane, int nu, Regs& r) {
+        const uint32_t g = tile + (uint32_t)(grp >> 1) * kSuperBytes;
+        const int u0 = (grp & 1) * 4;
+#pragma unroll
+        for (int u = 0; u < kGroupUnits; ++u)
+            if (u < nu) r.v[u] = lds128(g + (u0 + u) * 512 + lane * 16);
+        r.d = lds16(g + 4096 + lane * 2);
+        r.sc = lds32(g + 4160 + lane * 4) >> (16 * (grp & 1));
+    }
+    static constexpr int kChunkUnits = 8;
+    __host__ __device__ static uint32_t unit_offset(int u) { return (uint32_t)(u >> 3) * kSuperBytes; }
     __device__ static __forceinline__ void decode(const Regs& r, int u, int (&w)[8]) {
         const uint32_t x[4] = {r.v[u].x, r.v[u].y, r.v[u].z, r.v[u].w};
 #pragma unroll
@@ -137,6 +162,18 @@ template <> struct Tiled<CHIMERE_TYPE_Q8_0> {
         for (int u = 0; u < kGroupUnits; ++u)
             if (u < nu) { prefetch_l2(g + u * kUnitBytes + lane * 16); prefetch_l2(g + u * kUnitBytes + 512 + lane * 16); }
     }
+    __device__ static __forceinline__ void loads(uint32_t tile, int grp, int lane, int nu, Regs& r) {
+        const uint32_t g = tile + (uint32_t)grp * (kGroupUnits * kUnitBytes);
+#pragma unroll
+        for (int u = 0; u < kGroupUnits; ++u)
+            if (u < nu) {
+                r.v[2 * u] = lds128(g + u * kUnitBytes + lane * 16);
+                r.v[2 * u + 1] = lds128(g + u * kUnitBytes + 512 + lane * 16);
+                r.d[u] = lds16(g + u * kUnitBytes + 1024 + lane * 2);
+            }
+    }
+    static constexpr int kChunkUnits = 4;
+    __host__ __device__ static uint32_t unit_offset(int u) { return (uint32_t)u * kUnitBytes; }
     __device__ static __forceinline__ void decode(const Regs& r, int u, int (&w)[8]) {
         w[0] = (int)r.v[2 * u].x; w[1] = (int)r.v[2 * u].y; w[2] = (int)r.v[2 * u].z; w[3] = (int)r.v[2 * u].w;
         w[4] = (int)r.v[2 * u + 1].x; w[5] = (int)r.v[2 * u + 1].y; w[6] = (int)r.v[2 * u + 1].z; w[7] = (int)r.v[2 * u + 1].w;
