@@ -47,7 +47,7 @@ __device__ __forceinline__ void quantize_block_q8_1(float xi, uint8_t* out, int 
 }
 
 // One token's scores -> top-k, by one warp.  Lane l owns experts l, l+32, ...
-__device__ void topk_warp(const RouteParams& p, const float* logit_row, int t, int lane, float* tree_scratch) {
+__device__ void topk_warp(const RouteParams& p, const float* logit_row, int t, int lane, float* tree_scratch, int* ids_out) {
     const int E = p.E, k = p.top_k;
     float v[8], pr[8];
 #pragma unroll
@@ -115,24 +115,29 @@ __device__ void topk_warp(const RouteParams& p, const float* logit_row, int t, i
         if (p.route_mode != CHIMERE_ROUTE_SOFTMAX_RENORM || p.route_scale != 1.0f) w = w * p.route_scale;
         p.topk_idx[(size_t)t * k + lane] = isel;
         p.topk_w[(size_t)t * k + lane] = w;
+        if (ids_out) ids_out[lane] = isel;
     }
 }
 
 // Stable counting sort of the T*k pairs by expert, plus the GEMV work list.  One CTA of 256.
-__device__ void build_dispatch(const RouteParams& p, int* smem_i) {
+// s_ids: the T*k expert ids in shared memory if the caller has them there (else they are read from p.topk_idx).
+constexpr int kDispatchSmemInts = 512 + 2048 + 256 + 1024;
+__device__ void build_dispatch(const RouteParams& p, int* smem_i, const int* s_ids) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int E = p.E, P = p.T * p.top_k;
     int* hist = smem_i;              // [256]
     int* cursor = smem_i + 256;      // [256]
     int* warp_cnt = smem_i + 512;    // [8][256]
     int* scan = smem_i + 512 + 2048; // [256]
+    int* s_perm = smem_i + 512 + 2048 + 256;   // [1024] copy of the permutation when it is that short
+    const bool perm_in_smem = P <= 1024;
     hist[tid] = 0;
     for (int i = tid; i < 2048; i += 256) warp_cnt[i] = 0;
     __syncthreads();
     // ids outside [0, E) mark pairs that are not there (padding of a fixed-size exchange): they get no work
     const int istr = p.idx_stride > 1 ? p.idx_stride : 1;
     for (int q = tid; q < P; q += 256) {
-        const int e = __ldcg(p.topk_idx + (size_t)q * istr);
+        const int e = s_ids ? s_ids[q] : __ldcg(p.topk_idx + (size_t)q * istr);
         if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
     }
     __syncthreads();
@@ -186,7 +191,7 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i) {
     for (int base = 0; base < P; base += 256) {
         const int q = base + tid;
         bool valid = q < P;
-        int e = valid ? __ldcg(p.topk_idx + (size_t)q * istr) : -1;
+        int e = valid ? (s_ids ? s_ids[q] : __ldcg(p.topk_idx + (size_t)q * istr)) : -1;
         valid = valid && e >= 0 && e < E;
         if (!valid) e = 0x40000000 + tid;
         const unsigned same = __match_any_sync(0xffffffffu, e);
@@ -198,6 +203,7 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i) {
             int pos = cursor[e] + rank;
             for (int w = 0; w < warp; ++w) pos += warp_cnt[w * 256 + e];
             p.perm[pos] = q;
+            if (perm_in_smem) s_perm[pos] = q;
         }
         __syncthreads();
         if (leader) {
@@ -210,7 +216,8 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i) {
     for (int i = 0; i < (p.list_mode == 1 ? 0 : nent); ++i) {
         int* ent = p.group_list + kListHeader + kListEntry * (nsh + ent0 + i);
         const int mm = min(kMaxGroupTokens, cnt - i * kMaxGroupTokens);
-        for (int j = 0; j < kMaxGroupTokens; ++j) ent[4 + j] = j < mm ? p.perm[off + i * kMaxGroupTokens + j] : 0;
+        for (int j = 0; j < kMaxGroupTokens; ++j)
+            ent[4 + j] = j < mm ? (perm_in_smem ? s_perm[off + i * kMaxGroupTokens + j] : p.perm[off + i * kMaxGroupTokens + j]) : 0;
     }
 }
 
@@ -226,19 +233,8 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
     const int n_rtiles = gridDim.x;
     griddep_launch();   // the grouped GEMV that follows may bring its CTAs in; it waits for this grid before it reads anything
 
-    // ---- Q8_1 of this token tile's input rows, blocks dealt round-robin to the row tiles ----
-    {
-        const int nbH = H >> 5;
-        const int nt = min(TT, p.T - t0);
-        for (int q = blockIdx.x * 8 + warp; q < nt * nbH; q += n_rtiles * 8) {
-            const int tt = q / nbH, b = q - tt * nbH;
-            const float xi = p.x[(size_t)(t0 + tt) * H + b * 32 + lane];
-            quantize_block_q8_1(xi, p.x_q8 + ((size_t)(t0 + tt) * nbH + b) * kQ81Bytes, lane,
-                                p.x_soa_q + (size_t)(t0 + tt) * H + b * 32, p.x_soa_d + (size_t)(t0 + tt) * p.x_soa_d_stride + b);
-        }
-    }
-
-    // ---- partial dot products ----
+    // ---- partial dot products; the router rows come from DRAM, so their loads go out first and the Q8_1 of
+    //      this token tile's input rows (blocks dealt round-robin to the row tiles) runs while they are in flight ----
     float acc[TT][TE];
 #pragma unroll
     for (int a = 0; a < TT; ++a)
@@ -250,17 +246,41 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
         const int r = r0 + b;
         wrow[b] = (r < E) ? p.router_w + (size_t)r * H : ((r == E && r < nrows) ? p.shexp_gate_w : nullptr);
     }
-#pragma unroll 2
-    for (int j = tid; j < H; j += 256) {
-        float xv[TT], wv[TE];
+    constexpr int kStep = (TE <= 2) ? 8 : 2;   // elements per thread whose loads are in flight together
+    for (int j0 = 0; j0 < H; j0 += kStep * 256) {
+        float wv[kStep][TE];
 #pragma unroll
-        for (int a = 0; a < TT; ++a) xv[a] = (t0 + a < p.T) ? p.x[(size_t)(t0 + a) * H + j] : 0.0f;
+        for (int i = 0; i < kStep; ++i) {
+            const int j = j0 + i * 256 + tid;
 #pragma unroll
-        for (int b = 0; b < TE; ++b) wv[b] = wrow[b] ? __ldg(wrow[b] + j) : 0.0f;
+            for (int b = 0; b < TE; ++b) wv[i][b] = (j < H && wrow[b]) ? __ldg(wrow[b] + j) : 0.0f;
+        }
+        if (j0 == 0) {
+            const int nbH = H >> 5;
+            const int nt = min(TT, p.T - t0);
+            for (int q = blockIdx.x * 8 + warp; q < nt * nbH; q += n_rtiles * 8) {
+                const int tt = q / nbH, b = q - tt * nbH;
+                const float xi = p.x[(size_t)(t0 + tt) * H + b * 32 + lane];
+                quantize_block_q8_1(xi, p.x_q8 + ((size_t)(t0 + tt) * nbH + b) * kQ81Bytes, lane,
+                                    p.x_soa_q + (size_t)(t0 + tt) * H + b * 32, p.x_soa_d + (size_t)(t0 + tt) * p.x_soa_d_stride + b);
+            }
+        }
+        float xv[kStep][TT];
 #pragma unroll
-        for (int a = 0; a < TT; ++a)
+        for (int i = 0; i < kStep; ++i) {
+            const int j = j0 + i * 256 + tid;
 #pragma unroll
-            for (int b = 0; b < TE; ++b) acc[a][b] = fmaf(wv[b], xv[a], acc[a][b]);
+            for (int a = 0; a < TT; ++a) xv[i][a] = (j < H && t0 + a < p.T) ? p.x[(size_t)(t0 + a) * H + j] : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < kStep; ++i) {   // ascending j, one fused multiply-add each
+            if (j0 + i * 256 + tid < H) {
+#pragma unroll
+                for (int a = 0; a < TT; ++a)
+#pragma unroll
+                    for (int b = 0; b < TE; ++b) acc[a][b] = fmaf(wv[i][b], xv[i][a], acc[a][b]);
+            }
+        }
     }
     float* red = smem_f;  // [TT*TE][256]
 #pragma unroll
@@ -280,6 +300,7 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
 
     // ---- last CTA of the token tile: scores and top-k ----
     __shared__ int s_flag;
+    __shared__ int s_ids[TT * kMaxTopK];
     __threadfence();
     __syncthreads();
     if (tid == 0) s_flag = (atomicAdd(&p.counters[kCtrRouteTile + blockIdx.y], 1) == n_rtiles - 1);
@@ -289,10 +310,16 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
     if (tid == 0) p.counters[kCtrRouteTile + blockIdx.y] = 0;
     for (int a = warp; a < TT; a += 8) {
         const int t = t0 + a;
-        if (t < p.T) topk_warp(p, p.router_logits + (size_t)t * E, t, lane, red + warp * 256);
+        if (t < p.T) topk_warp(p, p.router_logits + (size_t)t * E, t, lane, red + warp * 256, s_ids + a * p.top_k);
     }
 
     // ---- last token tile overall: dispatch permutation and work list ----
+    if (gridDim.y == 1) {
+        // the only token tile: its ids are all in shared memory
+        __syncthreads();
+        build_dispatch(p, reinterpret_cast<int*>(smem_f), s_ids);
+        return;
+    }
     __threadfence();
     __syncthreads();
     if (tid == 0) s_flag = (atomicAdd(&p.counters[kCtrRouteAll], 1) == (int)gridDim.y - 1);
@@ -300,13 +327,13 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
     if (!s_flag) return;
     __threadfence();
     if (tid == 0) p.counters[kCtrRouteAll] = 0;
-    build_dispatch(p, reinterpret_cast<int*>(smem_f));
+    build_dispatch(p, reinterpret_cast<int*>(smem_f), nullptr);
 }
 
 // The dispatch step alone, for callers that bring their own expert ids in p.topk_idx.
 __global__ void __launch_bounds__(256) permute_kernel(const RouteParams p) {
     extern __shared__ __align__(16) float smem_f[];
-    build_dispatch(p, reinterpret_cast<int*>(smem_f));
+    build_dispatch(p, reinterpret_cast<int*>(smem_f), nullptr);
 }
 
 // Final step of an expert-parallel layer on the tokens' home rank: routing-weighted sum of the k expert
@@ -377,12 +404,12 @@ __global__ void __launch_bounds__(128) ep_pack_kernel(const int32_t* topk_idx, c
 
 static size_t route_smem(int TT, int TE) {
     size_t a = (size_t)TT * TE * 256 * sizeof(float);
-    size_t b = (512 + 2048 + 256) * sizeof(int);
+    size_t b = kDispatchSmemInts * sizeof(int);
     return a > b ? a : b;
 }
 
 cudaError_t launch_permute(const RouteParams& p, cudaStream_t stream) {
-    permute_kernel<<<1, 256, (512 + 2048 + 256) * sizeof(int), stream>>>(p);
+    permute_kernel<<<1, 256, kDispatchSmemInts * sizeof(int), stream>>>(p);
     return cudaGetLastError();
 }
 
