@@ -31,13 +31,41 @@ struct TileSmem { uint32_t aq, ad, red, total, q_row, d_row; };
 __host__ __device__ inline TileSmem tile_smem(int ncols_max, int wr, int wk, bool dual) {
     TileSmem s;
     s.q_row = (uint32_t)ncols_max;
-    s.d_row = ((uint32_t)(ncols_max / 32) * 4 + 15u) & ~15u;
+    s.d_row = ((uint32_t)(ncols_max / 32) * 8 + 15u) & ~15u;
     uint32_t o = 0;
     s.aq = o; o += kMaxGroupTokens * s.q_row;
     s.ad = o; o += kMaxGroupTokens * s.d_row;
     s.red = o; o += (uint32_t)(dual ? 2 : 1) * wk * kMaxGroupTokens * 32 * wr * 4;
     s.total = o;
     return s;
+}
+
+// Activations of `mp` tokens into shared memory: the int8 plane (row pitch qrow bytes) and, per unit, the pair
+// { f32 scale, correction word } (row pitch drow bytes; see tiled.cuh for the correction).  row_of(i) names the
+// global row of token i.  A thread copies 16 quants; the two halves of a unit sit in neighbouring lanes, which
+// exchange their sums.  Every thread of the CTA must call this (warp-wide shuffles).
+template <int TYPE, typename RowOf>
+__device__ __forceinline__ void stage_tokens(const GemvParams& p, uint8_t* aq, uint8_t* ad, int qrow, int drow, int mp, int ncols, int tid,
+                                             int nthreads, RowOf row_of) {
+    const int vq = ncols >> 4, total = mp * vq;
+    for (int v0 = 0; v0 < total; v0 += nthreads) {
+        const int v = v0 + tid;
+        const bool ok = v < total;
+        int i = 0, c = 0;
+        uint4 x = make_uint4(0u, 0u, 0u, 0u);
+        float d = 0.0f;
+        if (ok) {
+            i = v / vq; c = v - i * vq;
+            const int irow = row_of(i);
+            x = __ldcg(reinterpret_cast<const uint4*>(p.in_soa_q + (size_t)irow * p.in_soa_q_stride) + c);
+            if (!(c & 1)) d = __ldcg(p.in_soa_d + (size_t)irow * p.in_soa_d_stride + (c >> 1));
+            *reinterpret_cast<uint4*>(aq + i * qrow + c * 16) = x;
+        }
+        const int s = sum16(x);
+        const int so = __shfl_xor_sync(0xffffffffu, s, 1);
+        if (ok && !(c & 1))
+            *reinterpret_cast<uint2*>(ad + i * drow + (c >> 1) * 8) = make_uint2(__float_as_uint(d), (uint32_t)Tiled<TYPE>::correction(s, so));
+    }
 }
 
 // One pass over groups g0, g0+gstep, ... < ngroups of the tile at `tile` (global memory) for M tokens whose int8
@@ -57,17 +85,14 @@ __device__ __forceinline__ void group_units(const typename Tiled<TYPE>::Regs& r,
         if (FULL || u < nu) {
             int w[8];
             TT::decode(r, u, w);
-            const uint32_t qb = aq + (g * kGroupUnits + u) * 32, db = ad + (g * kGroupUnits + u) * 4;
+            const uint32_t qb = aq + (g * kGroupUnits + u) * 32, db = ad + (g * kGroupUnits + u) * 8;
 #pragma unroll
             for (int i = 0; i < M; ++i) {
                 if (M == 1 || i < mrem) {
                     const uint4 q0 = lds128(qb + i * qrow), q1 = lds128(qb + i * qrow + 16);
-                    int s0 = __dp4a(w[0], (int)q0.x, 0), s1 = __dp4a(w[4], (int)q1.x, 0);   // two independent chains
-                    s0 = __dp4a(w[1], (int)q0.y, s0); s1 = __dp4a(w[5], (int)q1.y, s1);
-                    s0 = __dp4a(w[2], (int)q0.z, s0); s1 = __dp4a(w[6], (int)q1.z, s1);
-                    s0 = __dp4a(w[3], (int)q0.w, s0); s1 = __dp4a(w[7], (int)q1.w, s1);
-                    const float dx = __uint_as_float(lds32(db + i * drow));
-                    const float t = (float)TT::finish(s0 + s1, r, u, 0);
+                    const uint2 dc = lds64(db + i * drow);   // the token's scale and correction word for this unit
+                    const float dx = __uint_as_float(dc.x);
+                    const float t = (float)unit_dot<TYPE>(w, q0, q1, (int)dc.y, r, u);
                     if (TT::kGroupScale) part[i] = fmaf(t, dx, part[i]);
                     else acc[i] = fmaf(TT::dscale(r, u) * dx, t, acc[i]);
                 }
@@ -157,14 +182,9 @@ __global__ void __launch_bounds__(kThreadsT, 4) tile_kernel(const GemvParams p, 
         s_tok[tid] = shared ? prow - p.T * p.top_k : prow / p.top_k;
     }
     __syncthreads();
-    // activations of the entry's tokens: int8 plane and f32 scale plane, 16 bytes per thread and step
-    for (int i = 0; i < m; ++i) {
-        const int irow = (STAGE == kStageGateUp) ? s_tok[i] : s_row[i];
-        const uint4* sq = reinterpret_cast<const uint4*>(p.in_soa_q + (size_t)irow * p.in_soa_q_stride);
-        for (int v = tid; v < ncols / 16; v += nthreads) *reinterpret_cast<uint4*>(smem + ts.aq + i * qrow + v * 16) = __ldcg(sq + v);
-        const float* sd = p.in_soa_d + (size_t)irow * p.in_soa_d_stride;
-        for (int v = tid; v < nb; v += nthreads) *reinterpret_cast<float*>(smem + ts.ad + i * drow + v * 4) = __ldcg(sd + v);
-    }
+    // activations of the entry's tokens
+    stage_tokens<TYPE>(p, smem + ts.aq, smem + ts.ad, qrow, drow, m, ncols, tid, nthreads,
+                       [&](int i) { return (STAGE == kStageGateUp) ? s_tok[i] : s_row[i]; });
     __syncthreads();
 
 #pragma unroll
@@ -285,7 +305,7 @@ __host__ __device__ inline BulkSmem bulk_smem(uint32_t tile_bytes_max, int ncols
     BulkSmem s;
     s.w_slot = (tile_bytes_max + 127u) & ~127u;
     s.q_row = (uint32_t)ncols_max;
-    s.d_row = ((uint32_t)(ncols_max / 32) * 4 + 15u) & ~15u;
+    s.d_row = ((uint32_t)(ncols_max / 32) * 8 + 15u) & ~15u;
     uint32_t o = (uint32_t)nmat * wr * s.w_slot;
     s.aq = o; o += (uint32_t)mt * s.q_row;
     s.ad = o; o += (uint32_t)mt * s.d_row;
@@ -379,22 +399,9 @@ __global__ void __launch_bounds__(kThreadsT, 3) bulk_kernel(const GemvParams p, 
     for (int i0 = 0; i0 < m; i0 += mt) {
         const int mp = min(mt, m - i0);
         if (i0 > 0) __syncthreads();   // the planes and partial sums of the previous tokens are no longer read
-        // activations of tokens i0 .. i0+mp: int8 plane and f32 scale plane
-        {
-            const int vq = ncols >> 4, vd = (nb + 3) >> 2;
-            for (int v = tid; v < mp * vq; v += nthreads) {
-                const int i = v / vq, c = v - i * vq;
-                const int irow = (STAGE == kStageGateUp) ? s_tok[i0 + i] : s_row[i0 + i];
-                *reinterpret_cast<uint4*>(smem + bs.aq + i * qrow + c * 16) =
-                    __ldcg(reinterpret_cast<const uint4*>(p.in_soa_q + (size_t)irow * p.in_soa_q_stride) + c);
-            }
-            for (int v = tid; v < mp * vd; v += nthreads) {
-                const int i = v / vd, c = v - i * vd;
-                const int irow = (STAGE == kStageGateUp) ? s_tok[i0 + i] : s_row[i0 + i];
-                *reinterpret_cast<uint4*>(smem + bs.ad + i * drow + c * 16) =
-                    __ldcg(reinterpret_cast<const uint4*>(p.in_soa_d + (size_t)irow * p.in_soa_d_stride) + c);
-            }
-        }
+        // activations of tokens i0 .. i0+mp
+        stage_tokens<TYPE>(p, smem + bs.aq, smem + bs.ad, qrow, drow, mp, ncols, tid, nthreads,
+                           [&](int i) { return (STAGE == kStageGateUp) ? s_tok[i0 + i] : s_row[i0 + i]; });
         __syncthreads();
         if (!arrived) {
             if (bytes > 0 && !mbar_wait(&s_bar[warp], 0)) {
@@ -587,14 +594,13 @@ static BulkPlan plan_bulk(const GemvParams& p, int stage, bool dual, int wk, int
     int64_t tb = tile_bytes_of(p.type_routed, p.ncols_routed);
     if (p.nrows_shared > 0) tb = max(tb, tile_bytes_of(p.type_shared, p.ncols_shared));
     const uintptr_t ptrs = (uintptr_t)p.w_a | (uintptr_t)p.w_b | (uintptr_t)p.sh_a | (uintptr_t)p.sh_b | (uintptr_t)p.in_soa_q |
-                           (uintptr_t)p.in_soa_d | (uintptr_t)p.stride_a | (uintptr_t)p.stride_b | (uintptr_t)p.in_soa_q_stride |
-                           (uintptr_t)(p.in_soa_d_stride * 4);
+                           (uintptr_t)p.stride_a | (uintptr_t)p.stride_b | (uintptr_t)p.in_soa_q_stride;
     if (ptrs & 15) return b;
     const int nmat = dual ? 2 : 1;
     const bool need_red = gu || wk > 1;
     const int ncols_max = max(p.ncols_routed, p.ncols_shared);
     const int threads = 32 * wk * wr;
-    const int sm_bytes = 227 * 1024, per_cta = 1024 + 256;   // the system's reserve and the kernel's static variables
+    const int sm_bytes = 228 * 1024, per_cta = 1024 + 192;   // an SM's shared memory; per CTA the system's reserve and the kernel's static variables
     const int max_ctas = min(8, 1536 / threads);
     // decode-size batches: as many CTAs per SM as fit one token per pass, then as many tokens as still fit;
     // larger batches: at least four tokens per pass if that fits at all

@@ -25,8 +25,9 @@ __global__ void pack_kernel(const uint8_t* raw, uint8_t* out, int nrows, int nco
     if (TYPE == CHIMERE_TYPE_Q4_0) {
         const uint8_t* blk = src_row + b * 18;
         uint4 v;
-        v.x = ld_u32_a2(blk + 2) ^ 0x88888888u;  v.y = ld_u32_a2(blk + 6) ^ 0x88888888u;
-        v.z = ld_u32_a2(blk + 10) ^ 0x88888888u; v.w = ld_u32_a2(blk + 14) ^ 0x88888888u;
+        // low nibble: ggml's unsigned n; high nibble: n - 8 in two's complement
+        v.x = ld_u32_a2(blk + 2) ^ 0x80808080u;  v.y = ld_u32_a2(blk + 6) ^ 0x80808080u;
+        v.z = ld_u32_a2(blk + 10) ^ 0x80808080u; v.w = ld_u32_a2(blk + 14) ^ 0x80808080u;
         uint8_t* d = dst_tile + (size_t)b * 576;
         *reinterpret_cast<uint4*>(d + lane * 16) = v;
         *reinterpret_cast<uint16_t*>(d + 512 + lane * 2) = (uint16_t)ld_u16(blk);
@@ -52,9 +53,10 @@ __global__ void pack_kernel(const uint8_t* raw, uint8_t* out, int nrows, int nco
             for (int i = 0; i < 4; ++i) {
                 int v = (int)((gv >> (8 * i)) & 0xFFu);         // odd magnitude 1..15
                 if ((sgn >> (4 * g + i)) & 1u) v = -v;
-                const uint32_t code = (uint32_t)((v - 1) >> 1) & 15u;   // two's complement nibble s, value = 2s + 1
                 const int e = 4 * g + i;                      // element within the unit
                 const int byte = e & 15, hi = e >> 4;
+                const int c = (v - 1) >> 1;                   // code -8..7, value = 2c + 1
+                const uint32_t code = hi ? ((uint32_t)c & 15u) : (uint32_t)(c + 8);   // high: two's complement; low: offset by 8
                 word[byte >> 2] |= code << (8 * (byte & 3) + 4 * hi);
             }
         }
@@ -100,10 +102,10 @@ __global__ void block_sumi_tiled_kernel(const uint8_t* packed, const uint8_t* xq
             int w[8];
             TT::decode(r, u, w);
             const int b = grp * kGroupUnits + u;
-            int s = 0;
-#pragma unroll
-            for (int g = 0; g < 8; ++g) s = __dp4a(w[g], *reinterpret_cast<const int*>(xq8 + (size_t)b * kQ81Bytes + 4 + 4 * g), s);
-            out[(size_t)(tile * 32 + lane) * nb + b] = TT::finish(s, r, u, 0);
+            const int* qw = reinterpret_cast<const int*>(xq8 + (size_t)b * kQ81Bytes + 4);
+            const uint4 q0 = make_uint4((uint32_t)qw[0], (uint32_t)qw[1], (uint32_t)qw[2], (uint32_t)qw[3]);
+            const uint4 q1 = make_uint4((uint32_t)qw[4], (uint32_t)qw[5], (uint32_t)qw[6], (uint32_t)qw[7]);
+            out[(size_t)(tile * 32 + lane) * nb + b] = unit_dot<TYPE>(w, q0, q1, TT::correction(sum16(q0), sum16(q1)), r, u);
         }
     }
 }

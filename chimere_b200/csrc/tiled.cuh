@@ -10,17 +10,21 @@
 //   read and every lane receives whole units of its own row in registers.
 //
 //   Q4_0  -> per (tile, unit): 512 B nibbles + 64 B f16 scales               (576 B, as before)
-//            nibble stored as (n - 8) in two's complement: byte (s << 4) = 16 * (n - 8).
 //   Q8_0  -> per (tile, unit): 2 x 512 B int8 + 64 B f16 scales              (1088 B, as before)
-//   IQ3_S -> per (tile, super-block of 8 units): 8 x 512 B signed 4-bit codes + 64 B f16 d +
+//   IQ3_S -> per (tile, super-block of 8 units): 8 x 512 B 4-bit codes + 64 B f16 d +
 //            128 B sub-block scale nibbles                                   (4288 B, was 3520 B)
-//            Each IQ3_S weight is +-(1,3,..,15): sixteen values, i.e. exactly four bits.  Code s
-//            (two's complement nibble) stands for 2s + 1; byte (s << 4) | 8 = 8 * (2s + 1).
-//            The expansion is lossless: integer block dots are identical to the codebook form.
+//            Each IQ3_S weight is +-(1,3,..,15): sixteen values, i.e. exactly four bits: code s in
+//            -8..7 stands for 2s + 1.  The expansion is lossless: integer block dots are
+//            identical to the codebook form.
 //
 // Within a unit, byte j of a row's 16 bytes holds element j in its low nibble and element j+16
 // in its high nibble (the Q4_0 convention), so words 0..3 pair with Q8_1 words 0..3 (low) and
-// 4..7 (high).
+// 4..7 (high).  The two nibbles are stored differently so that neither needs a shift before dp4a:
+//   low nibble  = code + 8, unsigned 0..15 (for Q4_0 that is ggml's own nibble): x & 0x0F0F0F0F is an
+//                 unsigned byte vector;  sum(code * q) = sum(nibble * q) - 8 * sum(q)
+//   high nibble = code in two's complement: x & 0xF0F0F0F0 is the signed byte vector 16 * code
+// The terms in sum(q) depend on the activations only; whoever stages a token's Q8_1 block computes
+// them once per (token, unit) as the "correction" word that a dp4a accumulator starts from.
 #pragma once
 #include "common.cuh"
 
@@ -52,6 +56,24 @@ __device__ __forceinline__ uint32_t lds32(uint32_t a) {
     return v;
 }
 
+// dp4a with unsigned bytes in a and signed bytes in b
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+
+// Per type, besides the loads:
+//   decode(r, u, w)        w[0..3]: low-nibble words (elements 0..15), w[4..7]: high-nibble words (16..31)
+//   kLowUnsigned           w[0..3] are unsigned byte vectors (dp4a_us), else signed
+//   kCorrLow               the correction word starts the low accumulator (else the high one)
+//   correction(s_lo, s_hi) from the sums of a token's quants 0..15 and 16..31 of the unit
+//   finish(sl, sh, r, u)   the integer block dot from the two accumulators
 // A "group" is kGroupUnits = 4 consecutive units of the 32 rows of a tile: what one lane decodes
 // at a time.  kChunkBytes is the smallest contiguous piece a tile may be cut into when it is
 // streamed in slabs (an IQ3_S super-block keeps its scales behind its eight units).
@@ -85,12 +107,14 @@ template <> struct Tiled<CHIMERE_TYPE_Q4_0> {
     }
     static constexpr int kChunkUnits = 4;
     __host__ __device__ static uint32_t unit_offset(int u) { return (uint32_t)u * kUnitBytes; }   // u: a chunk boundary or the row's end
+    static constexpr bool kLowUnsigned = true, kCorrLow = true;
     __device__ static __forceinline__ void decode(const Regs& r, int u, int (&w)[8]) {
         const uint32_t x[4] = {r.v[u].x, r.v[u].y, r.v[u].z, r.v[u].w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { w[j] = (int)((x[j] << 4) & 0xF0F0F0F0u); w[4 + j] = (int)(x[j] & 0xF0F0F0F0u); }
+        for (int j = 0; j < 4; ++j) { w[j] = (int)(x[j] & 0x0F0F0F0Fu); w[4 + j] = (int)(x[j] & 0xF0F0F0F0u); }
     }
-    __device__ static __forceinline__ int finish(int s, const Regs&, int, int) { return s >> 4; }
+    __host__ __device__ static __forceinline__ int correction(int s_lo, int) { return -8 * s_lo; }
+    __device__ static __forceinline__ int finish(int sl, int sh, const Regs&, int) { return sl + (sh >> 4); }
     __device__ static __forceinline__ float dscale(const Regs& r, int u) { return h2f(r.d[u]); }
 };
 
@@ -126,17 +150,18 @@ template <> struct Tiled<CHIMERE_TYPE_IQ3_S> {
     }
     static constexpr int kChunkUnits = 8;
     __host__ __device__ static uint32_t unit_offset(int u) { return (uint32_t)(u >> 3) * kSuperBytes; }
+    static constexpr bool kLowUnsigned = true, kCorrLow = false;
     __device__ static __forceinline__ void decode(const Regs& r, int u, int (&w)[8]) {
         const uint32_t x[4] = {r.v[u].x, r.v[u].y, r.v[u].z, r.v[u].w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            w[j] = (int)(((x[j] << 4) & 0xF0F0F0F0u) | 0x08080808u);
-            w[4 + j] = (int)((x[j] & 0xF0F0F0F0u) | 0x08080808u);
-        }
+        for (int j = 0; j < 4; ++j) { w[j] = (int)(x[j] & 0x0F0F0F0Fu); w[4 + j] = (int)(x[j] & 0xF0F0F0F0u); }
     }
-    // dp4a result = 8 * sum(+-magnitude * q); times the sub-block factor 1 + 2*scale (chimere_kernels.cu:860)
-    __device__ static __forceinline__ int finish(int s, const Regs& r, int u, int) {
-        return (s >> 3) * (int)(1u + 2u * ((r.sc >> (4 * u)) & 15u));
+    // weight = 2*code + 1.  Low half: sum((2n - 15) q) = 2*sl - 15*s_lo; high half: sum((2c + 1) q) = sh/8 + s_hi with
+    // sh = sum(16c * q).  The correction 8*(s_hi - 15*s_lo) starts sh, so the block dot is 2*sl + (sh >> 3), exactly;
+    // times the sub-block factor 1 + 2*scale (chimere_kernels.cu:860).
+    __host__ __device__ static __forceinline__ int correction(int s_lo, int s_hi) { return 8 * (s_hi - 15 * s_lo); }
+    __device__ static __forceinline__ int finish(int sl, int sh, const Regs& r, int u) {
+        return (2 * sl + (sh >> 3)) * (int)(1u + 2u * ((r.sc >> (4 * u)) & 15u));
     }
     __device__ static __forceinline__ float dscale(const Regs& r, int) { return h2f(r.d); }
 };
@@ -178,9 +203,37 @@ template <> struct Tiled<CHIMERE_TYPE_Q8_0> {
         w[0] = (int)r.v[2 * u].x; w[1] = (int)r.v[2 * u].y; w[2] = (int)r.v[2 * u].z; w[3] = (int)r.v[2 * u].w;
         w[4] = (int)r.v[2 * u + 1].x; w[5] = (int)r.v[2 * u + 1].y; w[6] = (int)r.v[2 * u + 1].z; w[7] = (int)r.v[2 * u + 1].w;
     }
-    __device__ static __forceinline__ int finish(int s, const Regs&, int, int) { return s; }
+    static constexpr bool kLowUnsigned = false, kCorrLow = true;
+    __host__ __device__ static __forceinline__ int correction(int, int) { return 0; }
+    __device__ static __forceinline__ int finish(int sl, int sh, const Regs&, int) { return sl + sh; }
     __device__ static __forceinline__ float dscale(const Regs& r, int u) { return h2f(r.d[u]); }
 };
+
+// One unit against one token: q0 / q1 = the token's quants 0..15 / 16..31 of the unit, corr = its correction word.
+template <int TYPE>
+__device__ __forceinline__ int unit_dot(const int (&w)[8], const uint4& q0, const uint4& q1, int corr, const typename Tiled<TYPE>::Regs& r, int u) {
+    using TT = Tiled<TYPE>;
+    int sl = TT::kCorrLow ? corr : 0, sh = TT::kCorrLow ? 0 : corr;   // two independent chains
+    if (TT::kLowUnsigned) {
+        sl = dp4a_us((uint32_t)w[0], (int)q0.x, sl); sh = __dp4a(w[4], (int)q1.x, sh);
+        sl = dp4a_us((uint32_t)w[1], (int)q0.y, sl); sh = __dp4a(w[5], (int)q1.y, sh);
+        sl = dp4a_us((uint32_t)w[2], (int)q0.z, sl); sh = __dp4a(w[6], (int)q1.z, sh);
+        sl = dp4a_us((uint32_t)w[3], (int)q0.w, sl); sh = __dp4a(w[7], (int)q1.w, sh);
+    } else {
+        sl = __dp4a(w[0], (int)q0.x, sl); sh = __dp4a(w[4], (int)q1.x, sh);
+        sl = __dp4a(w[1], (int)q0.y, sl); sh = __dp4a(w[5], (int)q1.y, sh);
+        sl = __dp4a(w[2], (int)q0.z, sl); sh = __dp4a(w[6], (int)q1.z, sh);
+        sl = __dp4a(w[3], (int)q0.w, sl); sh = __dp4a(w[7], (int)q1.w, sh);
+    }
+    return TT::finish(sl, sh, r, u);
+}
+// sums of sixteen int8 held in a uint4
+__device__ __forceinline__ int sum16(const uint4& x) {
+    int s = __dp4a((int)x.x, 0x01010101, 0);
+    s = __dp4a((int)x.y, 0x01010101, s);
+    s = __dp4a((int)x.z, 0x01010101, s);
+    return __dp4a((int)x.w, 0x01010101, s);
+}
 
 // bytes of one matrix [nrows][ncols] in tiled32 form (nrows a multiple of 32)
 __host__ __device__ inline int64_t tiled_matrix_bytes(int type, int nrows, int ncols) {
