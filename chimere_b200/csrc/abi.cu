@@ -593,7 +593,9 @@ int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_m
     const int n_tiles_max = n_tiles_max_for(w, T);
     const bool dual = w->act == CHIMERE_ACT_SWIGLU;
 
-    cudaError_t e = launch_route(route_params(w, d_x, T, ws), stream);
+    RouteParams rp = route_params(w, d_x, T, ws);
+    rp.list_mode = 2;   // no work entries from the router: the tile builder below writes the list of the small experts
+    cudaError_t e = launch_route(rp, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     e = launch_build_tiles(ws->offsets, ws->perm, tiles, ws->group_list, w->E, T, w->top_k, w->F_s > 0, kGemmMin, stream);
     if (e != cudaSuccess) return cuda_rc(e);

@@ -13,11 +13,12 @@
 // followed by 128 f32 scales.  A plain bulk copy of a (tile, block range) lands MMA-ready in shared
 // memory: shared-memory descriptor with leading (K) byte offset 2048 and stride (row group) byte offset 128.
 //
-// CTA = 10 warps: warp 0 feeds a shared-memory ring with cp.async.bulk; warp 1 owns TMEM (512 columns =
+// CTA = 18 warps: warp 0 feeds a shared-memory ring with cp.async.bulk; warp 1 owns TMEM (512 columns =
 // four 128x128 int32 accumulators) and issues one tcgen05.mma kind::i8 (M 128, N 128, K 32) per block,
-// never accumulating across blocks; warps 2..9 read each block's accumulator back (tcgen05.ld; two warps per
-// TMEM lane quarter, 64 token columns each), convert, scale and add into fp32 registers (thread = output row),
-// then write the tile.
+// never accumulating across blocks; warps 2..17 read each block's accumulator back (tcgen05.ld; four warps per
+// TMEM lane quarter, 32 token columns each), convert, scale and add into fp32 registers (thread = output row)
+// with two-wide fp32 instructions, then write the tile.  The read-back is what bounds the kernel: 128 x 128
+// values per block against 64 tensor-pipe cycles of MMA.
 // All waits are bounded; a wait that runs out raises a status bit and the CTA still frees its TMEM.
 #include "common.cuh"
 #include "kernels.h"
@@ -28,7 +29,8 @@ constexpr int kG_TileBytes = 4096 + 512;     // one (128 x 32) int8 block + 128 
 constexpr int kG_BlocksPerStage = 4;
 constexpr int kG_Stages = 3;
 constexpr int kG_StageBytes = 2 * kG_BlocksPerStage * kG_TileBytes;   // A blocks then B blocks
-constexpr int kG_EpiWarps = 8;                 // two per TMEM lane quarter: each takes 64 of the 128 token columns
+constexpr int kG_EpiWarps = 16;                // four per TMEM lane quarter: each takes 32 of the 128 token columns
+constexpr int kG_EpiCols = 128 / (kG_EpiWarps / 4);
 constexpr int kG_Threads = 32 * (2 + kG_EpiWarps);
 constexpr int kG_TmemCols = 512;
 
@@ -76,6 +78,12 @@ __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sy
 // int32 -> f32 without the conversion unit: |v| <= 32 * 127 * 128 < 2^22, so v + 0x4B400000 read as a float is
 // 12582912 + v exactly, and one fp32 subtraction gives v.  (Integer add and float add run at full rate.)
 __device__ __forceinline__ float i2f_exact(int v) { return __int_as_float(v + 0x4B400000) - 12582912.0f; }
+// two fp32 lanes in one 64-bit register (sm_100 has two-wide fp32 add / mul / fma)
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi)); return r; }
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) { uint64_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) { uint64_t d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) { uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
 
 struct GemmShared {
     uint64_t full[kG_Stages];        // stage bytes have landed
@@ -159,14 +167,15 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
             }
         }
     } else {
-        // ------------------------------ epilogue: thread = output row, 64 token columns ------------------------------
+        // ------------------------------ epilogue: thread = output row, 32 token columns ------------------------------
         const int q = warp & 3;                      // TMEM lane quarter this warp may read
-        const int half = (warp - 2) >> 2;            // which 64 columns
+        const int part = (warp - 2) >> 2;            // which 32 columns
         const int row = q * 32 + lane;
-        const int ncols_here = min(64, max(0, item.n_valid - half * 64));
-        float acc[64];
+        const int ncols_here = min(kG_EpiCols, max(0, item.n_valid - part * kG_EpiCols));
+        uint64_t acc2[kG_EpiCols / 2];
 #pragma unroll
-        for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+        for (int i = 0; i < kG_EpiCols / 2; ++i) acc2[i] = 0ull;
+        const uint64_t neg_magic2 = pack2(__float_as_uint(-12582912.0f), __float_as_uint(-12582912.0f));
         bool ok = true;
         for (int blk = 0; blk < nblocks && ok; ++blk) {
             const int s = blk / kG_BlocksPerStage, j = blk - s * kG_BlocksPerStage;
@@ -176,30 +185,19 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
             tc_fence_after();
             if (ncols_here > 0) {
                 const uint8_t* stage = smem + (size_t)st * kG_StageBytes;
-                const float sa = *reinterpret_cast<const float*>(stage + j * kG_TileBytes + 4096 + row * 4);
-                const float4* sbv = reinterpret_cast<const float4*>(stage + (kG_BlocksPerStage + j) * kG_TileBytes + 4096) + half * 16;
-                int v0[32], v1[32];
-                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + buf * 128 + half * 64;
-                tc_ld32_nowait(taddr, v0);
-                if (ncols_here > 32) tc_ld32_nowait(taddr + 32, v1);
-                tc_wait_ld();
+                const uint32_t sab = *reinterpret_cast<const uint32_t*>(stage + j * kG_TileBytes + 4096 + row * 4);
+                const uint64_t sa2 = pack2(sab, sab);
+                const uint4* sbv = reinterpret_cast<const uint4*>(stage + (kG_BlocksPerStage + j) * kG_TileBytes + 4096) + part * (kG_EpiCols / 4);
+                int v[32];
+                tc_ld32(tmem + ((uint32_t)(q * 32) << 16) + buf * 128 + part * kG_EpiCols, v);
+                // value + 0x4B400000 read as a float is 12582912 + value (see i2f_exact); the rest runs two columns at a time
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const float4 sb4 = sbv[g];
-                    acc[4 * g + 0] = fmaf(i2f_exact(v0[4 * g + 0]) * sb4.x, sa, acc[4 * g + 0]);
-                    acc[4 * g + 1] = fmaf(i2f_exact(v0[4 * g + 1]) * sb4.y, sa, acc[4 * g + 1]);
-                    acc[4 * g + 2] = fmaf(i2f_exact(v0[4 * g + 2]) * sb4.z, sa, acc[4 * g + 2]);
-                    acc[4 * g + 3] = fmaf(i2f_exact(v0[4 * g + 3]) * sb4.w, sa, acc[4 * g + 3]);
-                }
-                if (ncols_here > 32) {
-#pragma unroll
-                    for (int g = 0; g < 8; ++g) {
-                        const float4 sb4 = sbv[8 + g];
-                        acc[32 + 4 * g + 0] = fmaf(i2f_exact(v1[4 * g + 0]) * sb4.x, sa, acc[32 + 4 * g + 0]);
-                        acc[32 + 4 * g + 1] = fmaf(i2f_exact(v1[4 * g + 1]) * sb4.y, sa, acc[32 + 4 * g + 1]);
-                        acc[32 + 4 * g + 2] = fmaf(i2f_exact(v1[4 * g + 2]) * sb4.z, sa, acc[32 + 4 * g + 2]);
-                        acc[32 + 4 * g + 3] = fmaf(i2f_exact(v1[4 * g + 3]) * sb4.w, sa, acc[32 + 4 * g + 3]);
-                    }
+                for (int g = 0; g < kG_EpiCols / 4; ++g) {
+                    const uint4 sb4 = sbv[g];
+                    const uint64_t f01 = add2(pack2((uint32_t)(v[4 * g + 0] + 0x4B400000), (uint32_t)(v[4 * g + 1] + 0x4B400000)), neg_magic2);
+                    const uint64_t f23 = add2(pack2((uint32_t)(v[4 * g + 2] + 0x4B400000), (uint32_t)(v[4 * g + 3] + 0x4B400000)), neg_magic2);
+                    acc2[2 * g + 0] = fma2(f01, mul2(pack2(sb4.x, sb4.y), sa2), acc2[2 * g + 0]);
+                    acc2[2 * g + 1] = fma2(f23, mul2(pack2(sb4.z, sb4.w), sa2), acc2[2 * g + 1]);
                 }
             }
             tc_fence_before();
@@ -209,7 +207,10 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
                 if (j == kG_BlocksPerStage - 1 || blk == nblocks - 1) mbar_arrive_cta(&sh.empty[st]);   // scales of the stage read
             }
         }
-        Policy::store(p, item, row, q, half, lane, acc, smem, ok);
+        float acc[kG_EpiCols];
+#pragma unroll
+        for (int i = 0; i < kG_EpiCols / 2; ++i) unpack2(acc2[i], acc[2 * i], acc[2 * i + 1]);
+        Policy::store(p, item, row, q, part, lane, acc, smem, ok);
     }
 
     tc_fence_before();
@@ -220,7 +221,7 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
     }
 }
 
-__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kG_EpiWarps) : "memory"); }
 
 // plain fp32 tile store: out[(row0 + r) * ldo + col0 + c] = D[r][c]  (the primitive)
 struct PlainPolicy {
@@ -231,12 +232,12 @@ struct PlainPolicy {
         w.aux0 = it.rows_valid; w.aux1 = it.out_row0; w.aux2 = it.out_col0; w.aux3 = 0;
         return true;
     }
-    __device__ static __forceinline__ void store(const GemmParams& p, const GemmWork& w, int row, int, int half, int,
-                                                 const float (&acc)[64], uint8_t*, bool ok) {
+    __device__ static __forceinline__ void store(const GemmParams& p, const GemmWork& w, int row, int, int part, int,
+                                                 const float (&acc)[kG_EpiCols], uint8_t*, bool ok) {
         if (!ok || row >= w.aux0) return;
 #pragma unroll
-        for (int c = 0; c < 64; ++c)
-            if (half * 64 + c < w.n_valid) p.out[(size_t)(w.aux1 + row) * p.ldo + w.aux2 + half * 64 + c] = acc[c];
+        for (int c = 0; c < kG_EpiCols; ++c)
+            if (part * kG_EpiCols + c < w.n_valid) p.out[(size_t)(w.aux1 + row) * p.ldo + w.aux2 + part * kG_EpiCols + c] = acc[c];
     }
 };
 
@@ -264,21 +265,21 @@ struct GateUpPolicy {
         w.aux0 = j; w.aux1 = rt; w.aux2 = shared ? 1 : 0; w.aux3 = t.y;
         return true;
     }
-    __device__ static __forceinline__ void store(const PrefillGemmParams& p, const GemmWork& w, int row, int q, int half, int lane,
-                                                 float (&acc)[64], uint8_t* smem, bool ok) {
+    __device__ static __forceinline__ void store(const PrefillGemmParams& p, const GemmWork& w, int row, int q, int part, int lane,
+                                                 float (&acc)[kG_EpiCols], uint8_t* smem, bool ok) {
         const bool dual = p.act == CHIMERE_ACT_SWIGLU;
         float* xch = reinterpret_cast<float*>(smem);   // [128][129] floats in the ring, which is idle once ...
         epilogue_sync();                                // ... every epilogue warp has read its last scales from it
 #pragma unroll
-        for (int c = 0; c < 64; ++c) xch[row * 129 + half * 64 + c] = acc[c];
+        for (int c = 0; c < kG_EpiCols; ++c) xch[row * 129 + part * kG_EpiCols + c] = acc[c];
         epilogue_sync();
         if (!ok || (dual && q >= 2)) return;
         // this warp's 32 rows form Q8_1 block `blk` of the intermediate; it quantises its half of the token columns
         const int blk = dual ? w.aux1 * 2 + q : w.aux1 * 4 + q;
         uint8_t* dst = p.out_tiles + (size_t)w.aux0 * p.out_tile_stride + (size_t)blk * kG_TileBytes;
         const int khalf = lane >> 4, kin = lane & 15;
-        const int c_end = min(w.n_valid, half * 64 + 64);
-        for (int c = half * 64; c < c_end; ++c) {
+        const int c_end = min(w.n_valid, part * kG_EpiCols + kG_EpiCols);
+        for (int c = part * kG_EpiCols; c < c_end; ++c) {
             const float a = xch[row * 129 + c];
             float v;
             if (dual) v = silu_mul_ref(a, xch[(row + 64) * 129 + c]);
@@ -292,7 +293,7 @@ struct GateUpPolicy {
             if (lane == 0) *reinterpret_cast<float*>(dst + 4096 + c * 4) = __half2float(__float2half(d));
         }
         // columns past n_valid: zero quants and scales, so that the down GEMM's unused columns stay finite
-        for (int c = max(w.n_valid, half * 64); c < half * 64 + 64; ++c) {
+        for (int c = max(w.n_valid, part * kG_EpiCols); c < part * kG_EpiCols + kG_EpiCols; ++c) {
             reinterpret_cast<int8_t*>(dst)[khalf * 2048 + (c >> 3) * 128 + (c & 7) * 16 + kin] = 0;
             if (lane == 0) *reinterpret_cast<float*>(dst + 4096 + c * 4) = 0.0f;
         }
@@ -314,14 +315,14 @@ struct DownPolicy {
         w.aux0 = j; w.aux1 = rt; w.aux2 = shared ? 1 : 0; w.aux3 = t.y;
         return true;
     }
-    __device__ static __forceinline__ void store(const PrefillGemmParams& p, const GemmWork& w, int row, int, int half, int,
-                                                 float (&acc)[64], uint8_t*, bool ok) {
+    __device__ static __forceinline__ void store(const PrefillGemmParams& p, const GemmWork& w, int row, int, int part, int,
+                                                 float (&acc)[kG_EpiCols], uint8_t*, bool ok) {
         if (!ok) return;
         const int h = w.aux1 * 128 + row;
         if (h >= p.H) return;
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-            const int col = half * 64 + c;
+        for (int c = 0; c < kG_EpiCols; ++c) {
+            const int col = part * kG_EpiCols + c;
             if (col < w.n_valid) {
                 const int prow = w.aux2 ? p.T * p.top_k + w.aux3 + col : __ldcg(p.perm + w.aux3 + col);
                 p.pair_out[(size_t)prow * p.H + h] = acc[c];

@@ -14,7 +14,8 @@ constexpr int kCtrRouteTile = 16;  // [ceil(max_T/8)] row tiles done per token t
 struct RouteParams {
     int T, H, E, top_k, route_mode, has_shared;
     int idx_stride;             // permute only: distance in int32 between consecutive ids (0 or 1 = dense)
-    int list_mode;              // 0: work list for routed + shared entries; 1: shared-expert entries only (expert-parallel home rank)
+    int list_mode;              // 0: work list for routed + shared entries; 1: shared-expert entries only (expert-parallel home
+                                // rank); 2: an empty list (the prefill path builds its own from offsets and perm)
     float route_scale;
     const float* x;             // [T][H]
     const float* router_w;      // [E][H]

@@ -121,28 +121,49 @@ __device__ void topk_warp(const RouteParams& p, const float* logit_row, int t, i
 
 // Stable counting sort of the T*k pairs by expert, plus the GEMV work list.  One CTA of 256.
 // s_ids: the T*k expert ids in shared memory if the caller has them there (else they are read from p.topk_idx).
-constexpr int kDispatchSmemInts = 512 + 2048 + 256 + 1024;
+// Each warp takes one contiguous eighth of the pairs: it counts its pairs per expert, the counts are turned into
+// every warp's first position within every expert, and the warp places its pairs in order; so the only CTA
+// barriers are between those steps, however many pairs there are.  The work entries are then filled by all
+// threads (entry -> expert by bisection of the entry offsets).
+constexpr int kDispatchSmemInts = 256 + 256 + 2048 + 32 + 288 + 1024;
 __device__ void build_dispatch(const RouteParams& p, int* smem_i, const int* s_ids) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int E = p.E, P = p.T * p.top_k;
-    int* hist = smem_i;              // [256]
-    int* cursor = smem_i + 256;      // [256]
-    int* warp_cnt = smem_i + 512;    // [8][256]
-    int* scan = smem_i + 512 + 2048; // [256]
-    int* s_perm = smem_i + 512 + 2048 + 256;   // [1024] copy of the permutation when it is that short
+    int* hist = smem_i;               // [256] pairs per expert
+    int* cursor = smem_i + 256;       // [256] first position of each expert
+    int* warp_cnt = smem_i + 512;     // [8][256] per warp: pairs of each expert, then the warp's next position within it
+    int* scan = smem_i + 2560;        // [32]
+    int* ent_base = smem_i + 2592;    // [257] first routed entry of each expert, [256] = their number
+    int* s_perm = smem_i + 2880;      // [1024] copy of the permutation when it is that short
     const bool perm_in_smem = P <= 1024;
-    hist[tid] = 0;
     for (int i = tid; i < 2048; i += 256) warp_cnt[i] = 0;
     __syncthreads();
     // ids outside [0, E) mark pairs that are not there (padding of a fixed-size exchange): they get no work
     const int istr = p.idx_stride > 1 ? p.idx_stride : 1;
-    for (int q = tid; q < P; q += 256) {
-        const int e = s_ids ? s_ids[q] : __ldcg(p.topk_idx + (size_t)q * istr);
-        if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
+    const int chunk = (((P + 7) >> 3) + 31) & ~31;
+    const int q0 = min(P, warp * chunk), q1 = min(P, q0 + chunk);
+    for (int base = q0; base < q1; base += 32) {
+        const int q = base + lane;
+        int e = q < q1 ? (s_ids ? s_ids[q] : __ldcg(p.topk_idx + (size_t)q * istr)) : -1;
+        const bool valid = e >= 0 && e < E;
+        if (!valid) e = 0x40000000 + lane;
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        if (valid && (same & ((1u << lane) - 1u)) == 0u) warp_cnt[warp * 256 + e] += __popc(same);
+        __syncwarp();
     }
     __syncthreads();
+    // thread = expert: its pair count, and where each warp's pairs start within it
+    int cnt = 0;
+    if (tid < E) {
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const int t = warp_cnt[w * 256 + tid];
+            warp_cnt[w * 256 + tid] = cnt;
+            cnt += t;
+        }
+    }
+    hist[tid] = cnt;
     // exclusive scans over the experts: pair offsets and work-entry offsets
-    const int cnt = (tid < E) ? hist[tid] : 0;
     const int nent = (cnt + kMaxGroupTokens - 1) / kMaxGroupTokens;
     int incl_c = cnt, incl_n = nent;
 #pragma unroll
@@ -157,67 +178,66 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i, const int* s_i
     const int off = base_c + incl_c - cnt;      // exclusive
     const int ent0 = base_n + incl_n - nent;
     cursor[tid] = off;
+    ent_base[tid] = ent0;
     if (tid < E) p.offsets[tid] = off;
     if (tid == 255) {
         p.offsets[E] = base_c + incl_c;  // tid 255 holds the inclusive total (cnt = 0 beyond E)
+        ent_base[256] = base_n + incl_n;
     }
     int total_routed = 0;
     for (int w = 0; w < 8; ++w) total_routed += scan[8 + w];
     // shared-expert entries first (all tokens, identity order), then the routed ones
     const int nsh = p.has_shared ? (p.T + kSharedGroupTokens - 1) / kSharedGroupTokens : 0;
-    if (p.list_mode == 1) total_routed = 0;
-    for (int i = tid; i < nsh; i += 256) {
+    if (p.list_mode != 0) total_routed = 0;
+    for (int i = tid; i < (p.list_mode == 2 ? 0 : nsh); i += 256) {
         int* ent = p.group_list + kListHeader + kListEntry * i;
         const int t0 = i * kSharedGroupTokens, mm = min(kSharedGroupTokens, p.T - t0);
         ent[0] = -1; ent[1] = t0; ent[2] = mm; ent[3] = 0;
         for (int j = 0; j < kMaxGroupTokens; ++j) ent[4 + j] = j < mm ? p.T * p.top_k + t0 + j : 0;
     }
-    for (int i = 0; i < (p.list_mode == 1 ? 0 : nent); ++i) {
-        int* ent = p.group_list + kListHeader + kListEntry * (nsh + ent0 + i);
-        ent[0] = tid;
-        ent[1] = off + i * kMaxGroupTokens;
-        ent[2] = min(kMaxGroupTokens, cnt - i * kMaxGroupTokens);
-        ent[3] = 0;
-    }
     if (tid == 0) {
         for (int i = 0; i < 4; ++i) p.counters[kCtrQueue + i] = 0;
-        p.group_list[0] = total_routed + nsh;
+        const int nsh_listed = p.list_mode == 2 ? 0 : nsh;
+        p.group_list[0] = total_routed + nsh_listed;
         p.group_list[1] = total_routed;
-        p.group_list[2] = nsh;
+        p.group_list[2] = nsh_listed;
         p.group_list[3] = 0;
     }
-    __syncthreads();
-    // stable placement, 256 pairs per step
-    for (int base = 0; base < P; base += 256) {
-        const int q = base + tid;
-        bool valid = q < P;
-        int e = valid ? (s_ids ? s_ids[q] : __ldcg(p.topk_idx + (size_t)q * istr)) : -1;
-        valid = valid && e >= 0 && e < E;
-        if (!valid) e = 0x40000000 + tid;
+    __syncthreads();   // cursor and the warps' first positions are in place
+    // stable placement: each warp walks its pairs in order
+    for (int base = q0; base < q1; base += 32) {
+        const int q = base + lane;
+        int e = q < q1 ? (s_ids ? s_ids[q] : __ldcg(p.topk_idx + (size_t)q * istr)) : -1;
+        const bool valid = e >= 0 && e < E;
+        if (!valid) e = 0x40000000 + lane;
         const unsigned same = __match_any_sync(0xffffffffu, e);
         const int rank = __popc(same & ((1u << lane) - 1u));
-        const bool leader = valid && rank == 0;
-        if (leader) warp_cnt[warp * 256 + e] = __popc(same);
-        __syncthreads();
         if (valid) {
-            int pos = cursor[e] + rank;
-            for (int w = 0; w < warp; ++w) pos += warp_cnt[w * 256 + e];
+            const int pos = cursor[e] + warp_cnt[warp * 256 + e] + rank;
             p.perm[pos] = q;
             if (perm_in_smem) s_perm[pos] = q;
         }
-        __syncthreads();
-        if (leader) {
-            atomicAdd(&cursor[e], __popc(same));
-            warp_cnt[warp * 256 + e] = 0;
-        }
-        __syncthreads();
+        __syncwarp();
+        if (valid && rank == 0) warp_cnt[warp * 256 + e] += __popc(same);
+        __syncwarp();
     }
-    // the pair rows of every routed entry (perm was written by this CTA: visible after the barrier above)
-    for (int i = 0; i < (p.list_mode == 1 ? 0 : nent); ++i) {
-        int* ent = p.group_list + kListHeader + kListEntry * (nsh + ent0 + i);
-        const int mm = min(kMaxGroupTokens, cnt - i * kMaxGroupTokens);
+    __syncthreads();
+    // the routed entries with their pair rows (perm was written by this CTA: visible after the barrier above)
+    for (int idx = tid; idx < total_routed; idx += 256) {
+        int lo = 0, hi = 256;   // ent_base[lo] <= idx < ent_base[hi]
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (ent_base[mid] <= idx) lo = mid; else hi = mid;
+        }
+        const int e = lo, i = idx - ent_base[e], c = hist[e], o = cursor[e];
+        const int mm = min(kMaxGroupTokens, c - i * kMaxGroupTokens);
+        int* ent = p.group_list + kListHeader + kListEntry * (nsh + idx);
+        ent[0] = e;
+        ent[1] = o + i * kMaxGroupTokens;
+        ent[2] = mm;
+        ent[3] = 0;
         for (int j = 0; j < kMaxGroupTokens; ++j)
-            ent[4 + j] = j < mm ? (perm_in_smem ? s_perm[off + i * kMaxGroupTokens + j] : p.perm[off + i * kMaxGroupTokens + j]) : 0;
+            ent[4 + j] = j < mm ? (perm_in_smem ? s_perm[o + i * kMaxGroupTokens + j] : p.perm[o + i * kMaxGroupTokens + j]) : 0;
     }
 }
 
