@@ -101,19 +101,19 @@ struct GemmWork {
     int aux0, aux1, aux2, aux3;   // policy specific
 };
 
-// One CTA per output tile (128 rows x up to 128 tokens).  Policy::work() names the tile (or says there is none:
-// the CTA leaves before touching TMEM); Policy::store() consumes the fp32 accumulators, thread = row.
+// Persistent: CTA c works on output tiles c, c + gridDim.x, ... (128 rows x up to 128 tokens each).
+// Policy::work() names tile idx: kWorkOk, kWorkSkip (no such tile, go on) or kWorkEnd (nothing at or after idx).
+// Policy::store() consumes the fp32 accumulators, thread = row.  The three roles walk the same sequence of tiles
+// on their own; the ring stages and the TMEM buffers are counted across tiles, so the copies and the MMAs of the
+// next tile run while the read-back warps finish and store the current one.
+constexpr int kWorkOk = 0, kWorkSkip = 1, kWorkEnd = 2;
+
 template <class Policy, class Params>
 __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ GemmShared sh;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    GemmWork item;
-    if (!Policy::work(p, blockIdx.x, item)) return;
-    const uint8_t* a_src = item.a_src;
-    const uint8_t* b_src = item.b_src;
-    const int nblocks = item.nblocks;
-    const int nstages_total = (nblocks + kG_BlocksPerStage - 1) / kG_BlocksPerStage;
+    const int stride = (int)gridDim.x;
 
     if (tid == 0) {
         for (int i = 0; i < kG_Stages; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1 + kG_EpiWarps); }
@@ -133,84 +133,110 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
     if (warp == 0) {
         // ------------------------------ producer ------------------------------
         if (lane == 0) {
-            for (int s = 0; s < nstages_total; ++s) {
-                const int st = s % kG_Stages, ph = (s / kG_Stages) & 1;
-                if (!mbar_wait(&sh.empty[st], ph ^ 1)) { atomicOr(p.status, kStatusWaitTimeout); sh.failed = 1; break; }
-                const int b0 = s * kG_BlocksPerStage, nb = min(kG_BlocksPerStage, nblocks - b0);
-                uint8_t* dst = smem + (size_t)st * kG_StageBytes;
-                const uint32_t bytes = (uint32_t)nb * kG_TileBytes;
-                mbar_expect_tx(&sh.full[st], 2 * bytes);
-                bulk_g2s(dst, a_src + (size_t)b0 * kG_TileBytes, bytes, &sh.full[st]);
-                bulk_g2s(dst + kG_BlocksPerStage * kG_TileBytes, b_src + (size_t)b0 * kG_TileBytes, bytes, &sh.full[st]);
+            uint32_t sg = 0;   // stages issued so far, over all tiles
+            bool ok = true;
+            for (int idx = blockIdx.x; ok; idx += stride) {
+                GemmWork item;
+                const int ws = Policy::work(p, idx, item);
+                if (ws == kWorkEnd) break;
+                if (ws == kWorkSkip) continue;
+                const int nstages = (item.nblocks + kG_BlocksPerStage - 1) / kG_BlocksPerStage;
+                for (int s = 0; s < nstages; ++s, ++sg) {
+                    const int st = sg % kG_Stages, ph = (sg / kG_Stages) & 1;
+                    if (!mbar_wait(&sh.empty[st], ph ^ 1)) { atomicOr(p.status, kStatusWaitTimeout); sh.failed = 1; ok = false; break; }
+                    const int b0 = s * kG_BlocksPerStage, nb = min(kG_BlocksPerStage, item.nblocks - b0);
+                    uint8_t* dst = smem + (size_t)st * kG_StageBytes;
+                    const uint32_t bytes = (uint32_t)nb * kG_TileBytes;
+                    mbar_expect_tx(&sh.full[st], 2 * bytes);
+                    bulk_g2s(dst, item.a_src + (size_t)b0 * kG_TileBytes, bytes, &sh.full[st]);
+                    bulk_g2s(dst + kG_BlocksPerStage * kG_TileBytes, item.b_src + (size_t)b0 * kG_TileBytes, bytes, &sh.full[st]);
+                }
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            int blk = 0;
+            uint32_t sg = 0, bg = 0;   // stages / blocks so far, over all tiles
             bool ok = true;
-            for (int s = 0; s < nstages_total && ok; ++s) {
-                const int st = s % kG_Stages, ph = (s / kG_Stages) & 1;
-                if (!mbar_wait(&sh.full[st], ph)) { atomicOr(p.status, kStatusWaitTimeout); sh.failed = 1; ok = false; break; }
-                tc_fence_after();
-                const int nb = min(kG_BlocksPerStage, nblocks - s * kG_BlocksPerStage);
-                const uint32_t sa = smem_u32(smem + (size_t)st * kG_StageBytes);
-                const uint32_t sb = sa + kG_BlocksPerStage * kG_TileBytes;
-                for (int j = 0; j < nb; ++j, ++blk) {
-                    const int buf = blk & 3, tph = (blk >> 2) & 1;
-                    if (!mbar_wait(&sh.tempty[buf], tph ^ 1)) { atomicOr(p.status, kStatusWaitTimeout); sh.failed = 1; ok = false; break; }
+            for (int idx = blockIdx.x; ok; idx += stride) {
+                GemmWork item;
+                const int ws = Policy::work(p, idx, item);
+                if (ws == kWorkEnd) break;
+                if (ws == kWorkSkip) continue;
+                const int nstages = (item.nblocks + kG_BlocksPerStage - 1) / kG_BlocksPerStage;
+                for (int s = 0; s < nstages && ok; ++s, ++sg) {
+                    const int st = sg % kG_Stages, ph = (sg / kG_Stages) & 1;
+                    if (!mbar_wait(&sh.full[st], ph)) { atomicOr(p.status, kStatusWaitTimeout); sh.failed = 1; ok = false; break; }
                     tc_fence_after();
-                    tc_mma_i8(tmem + buf * 128, smem_desc_kmajor(sa + j * kG_TileBytes), smem_desc_kmajor(sb + j * kG_TileBytes));
-                    tc_commit(&sh.tfull[buf]);       // accumulator ready when this MMA has finished
+                    const int nb = min(kG_BlocksPerStage, item.nblocks - s * kG_BlocksPerStage);
+                    const uint32_t sa = smem_u32(smem + (size_t)st * kG_StageBytes);
+                    const uint32_t sb = sa + kG_BlocksPerStage * kG_TileBytes;
+                    for (int j = 0; j < nb; ++j, ++bg) {
+                        const int buf = bg & 3, tph = (bg >> 2) & 1;
+                        if (!mbar_wait(&sh.tempty[buf], tph ^ 1)) { atomicOr(p.status, kStatusWaitTimeout); sh.failed = 1; ok = false; break; }
+                        tc_fence_after();
+                        tc_mma_i8(tmem + buf * 128, smem_desc_kmajor(sa + j * kG_TileBytes), smem_desc_kmajor(sb + j * kG_TileBytes));
+                        tc_commit(&sh.tfull[buf]);       // accumulator ready when this MMA has finished
+                    }
+                    tc_commit(&sh.empty[st]);            // ... and the stage's int8 data is no longer needed
                 }
-                tc_commit(&sh.empty[st]);            // ... and the stage's int8 data is no longer needed
             }
         }
     } else {
-        // ------------------------------ epilogue: thread = output row, 32 token columns ------------------------------
+        // ------------------------------ read-back: thread = output row, 32 token columns ------------------------------
         const int q = warp & 3;                      // TMEM lane quarter this warp may read
         const int part = (warp - 2) >> 2;            // which 32 columns
         const int row = q * 32 + lane;
-        const int ncols_here = min(kG_EpiCols, max(0, item.n_valid - part * kG_EpiCols));
-        uint64_t acc2[kG_EpiCols / 2];
-#pragma unroll
-        for (int i = 0; i < kG_EpiCols / 2; ++i) acc2[i] = 0ull;
         const uint64_t neg_magic2 = pack2(__float_as_uint(-12582912.0f), __float_as_uint(-12582912.0f));
+        uint32_t sg = 0, bg = 0;
         bool ok = true;
-        for (int blk = 0; blk < nblocks && ok; ++blk) {
-            const int s = blk / kG_BlocksPerStage, j = blk - s * kG_BlocksPerStage;
-            const int st = s % kG_Stages;
-            const int buf = blk & 3, tph = (blk >> 2) & 1;
-            if (!mbar_wait(&sh.tfull[buf], tph)) { atomicOr(p.status, kStatusWaitTimeout); sh.failed = 1; ok = false; break; }
-            tc_fence_after();
-            if (ncols_here > 0) {
-                const uint8_t* stage = smem + (size_t)st * kG_StageBytes;
-                const uint32_t sab = *reinterpret_cast<const uint32_t*>(stage + j * kG_TileBytes + 4096 + row * 4);
-                const uint64_t sa2 = pack2(sab, sab);
-                const uint4* sbv = reinterpret_cast<const uint4*>(stage + (kG_BlocksPerStage + j) * kG_TileBytes + 4096) + part * (kG_EpiCols / 4);
-                int v[32];
-                tc_ld32(tmem + ((uint32_t)(q * 32) << 16) + buf * 128 + part * kG_EpiCols, v);
-                // value + 0x4B400000 read as a float is 12582912 + value (see i2f_exact); the rest runs two columns at a time
+        for (int idx = blockIdx.x;; idx += stride) {
+            GemmWork item;
+            const int ws = Policy::work(p, idx, item);
+            if (ws == kWorkEnd) break;
+            if (ws == kWorkSkip) continue;
+            const int nblocks = item.nblocks;
+            const int ncols_here = min(kG_EpiCols, max(0, item.n_valid - part * kG_EpiCols));
+            uint64_t acc2[kG_EpiCols / 2];
 #pragma unroll
-                for (int g = 0; g < kG_EpiCols / 4; ++g) {
-                    const uint4 sb4 = sbv[g];
-                    const uint64_t f01 = add2(pack2((uint32_t)(v[4 * g + 0] + 0x4B400000), (uint32_t)(v[4 * g + 1] + 0x4B400000)), neg_magic2);
-                    const uint64_t f23 = add2(pack2((uint32_t)(v[4 * g + 2] + 0x4B400000), (uint32_t)(v[4 * g + 3] + 0x4B400000)), neg_magic2);
-                    acc2[2 * g + 0] = fma2(f01, mul2(pack2(sb4.x, sb4.y), sa2), acc2[2 * g + 0]);
-                    acc2[2 * g + 1] = fma2(f23, mul2(pack2(sb4.z, sb4.w), sa2), acc2[2 * g + 1]);
+            for (int i = 0; i < kG_EpiCols / 2; ++i) acc2[i] = 0ull;
+            for (int blk = 0; blk < nblocks && ok; ++blk, ++bg) {
+                const int s = blk / kG_BlocksPerStage, j = blk - s * kG_BlocksPerStage;
+                const int st = (sg + s) % kG_Stages;
+                const int buf = bg & 3, tph = (bg >> 2) & 1;
+                if (!mbar_wait(&sh.tfull[buf], tph)) { atomicOr(p.status, kStatusWaitTimeout); sh.failed = 1; ok = false; break; }
+                tc_fence_after();
+                if (ncols_here > 0) {
+                    const uint8_t* stage = smem + (size_t)st * kG_StageBytes;
+                    const uint32_t sab = *reinterpret_cast<const uint32_t*>(stage + j * kG_TileBytes + 4096 + row * 4);
+                    const uint64_t sa2 = pack2(sab, sab);
+                    const uint4* sbv = reinterpret_cast<const uint4*>(stage + (kG_BlocksPerStage + j) * kG_TileBytes + 4096) + part * (kG_EpiCols / 4);
+                    int v[32];
+                    tc_ld32(tmem + ((uint32_t)(q * 32) << 16) + buf * 128 + part * kG_EpiCols, v);
+                    // value + 0x4B400000 read as a float is 12582912 + value (see i2f_exact); the rest runs two columns at a time
+#pragma unroll
+                    for (int g = 0; g < kG_EpiCols / 4; ++g) {
+                        const uint4 sb4 = sbv[g];
+                        const uint64_t f01 = add2(pack2((uint32_t)(v[4 * g + 0] + 0x4B400000), (uint32_t)(v[4 * g + 1] + 0x4B400000)), neg_magic2);
+                        const uint64_t f23 = add2(pack2((uint32_t)(v[4 * g + 2] + 0x4B400000), (uint32_t)(v[4 * g + 3] + 0x4B400000)), neg_magic2);
+                        acc2[2 * g + 0] = fma2(f01, mul2(pack2(sb4.x, sb4.y), sa2), acc2[2 * g + 0]);
+                        acc2[2 * g + 1] = fma2(f23, mul2(pack2(sb4.z, sb4.w), sa2), acc2[2 * g + 1]);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_cta(&sh.tempty[buf]);
+                    if (j == kG_BlocksPerStage - 1 || blk == nblocks - 1) mbar_arrive_cta(&sh.empty[st]);   // scales of the stage read
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive_cta(&sh.tempty[buf]);
-                if (j == kG_BlocksPerStage - 1 || blk == nblocks - 1) mbar_arrive_cta(&sh.empty[st]);   // scales of the stage read
-            }
-        }
-        float acc[kG_EpiCols];
+            sg += (uint32_t)((nblocks + kG_BlocksPerStage - 1) / kG_BlocksPerStage);
+            float acc[kG_EpiCols];
 #pragma unroll
-        for (int i = 0; i < kG_EpiCols / 2; ++i) unpack2(acc2[i], acc[2 * i], acc[2 * i + 1]);
-        Policy::store(p, item, row, q, part, lane, acc, smem, ok);
+            for (int i = 0; i < kG_EpiCols / 2; ++i) unpack2(acc2[i], acc[2 * i], acc[2 * i + 1]);
+            Policy::store(p, item, row, q, part, lane, acc, smem + (size_t)kG_Stages * kG_StageBytes, ok);
+            if (!ok) break;
+        }
     }
 
     tc_fence_before();
@@ -225,12 +251,13 @@ __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, %0;"
 
 // plain fp32 tile store: out[(row0 + r) * ldo + col0 + c] = D[r][c]  (the primitive)
 struct PlainPolicy {
-    __device__ static __forceinline__ bool work(const GemmParams& p, int idx, GemmWork& w) {
+    __device__ static __forceinline__ int work(const GemmParams& p, int idx, GemmWork& w) {
+        if (idx >= p.n_items) return kWorkEnd;
         const GemmItem it = p.items[idx];
         w.a_src = p.a_base + it.a_offset; w.b_src = p.b_base + it.b_offset;
         w.nblocks = p.nblocks; w.n_valid = it.n_valid;
         w.aux0 = it.rows_valid; w.aux1 = it.out_row0; w.aux2 = it.out_col0; w.aux3 = 0;
-        return true;
+        return kWorkOk;
     }
     __device__ static __forceinline__ void store(const GemmParams& p, const GemmWork& w, int row, int, int part, int,
                                                  const float (&acc)[kG_EpiCols], uint8_t*, bool ok) {
@@ -250,26 +277,26 @@ constexpr int kTileHeader = 4;
 // gate).  The up half hands its sums to the gate half through shared memory; the activation is quantised to
 // Q8_1 (32 consecutive rows = one warp) straight into the down GEMM's token tile.
 struct GateUpPolicy {
-    __device__ static __forceinline__ bool work(const PrefillGemmParams& p, int idx, GemmWork& w) {
+    __device__ static __forceinline__ int work(const PrefillGemmParams& p, int idx, GemmWork& w) {
         const int n_tiles = __ldcg(p.tiles);
         const int j = idx / p.row_tiles_max, rt = idx - j * p.row_tiles_max;
-        if (j >= n_tiles) return false;
+        if (j >= n_tiles) return kWorkEnd;
         const int4 t = __ldcg(reinterpret_cast<const int4*>(p.tiles + kTileHeader) + j);
         const bool shared = t.x < 0;
         const int row_tiles = shared ? p.row_tiles_shared : p.row_tiles_routed;
-        if (rt >= row_tiles) return false;
+        if (rt >= row_tiles) return kWorkSkip;
         const int nb = p.ncols_in / 32;
         w.a_src = (shared ? p.sh_a : p.a_exps + (size_t)t.x * p.stride_a) + (size_t)rt * nb * kG_TileBytes;
         w.b_src = p.b_tiles + (size_t)j * p.b_tile_stride;
         w.nblocks = nb; w.n_valid = t.z;
         w.aux0 = j; w.aux1 = rt; w.aux2 = shared ? 1 : 0; w.aux3 = t.y;
-        return true;
+        return kWorkOk;
     }
     __device__ static __forceinline__ void store(const PrefillGemmParams& p, const GemmWork& w, int row, int q, int part, int lane,
                                                  float (&acc)[kG_EpiCols], uint8_t* smem, bool ok) {
         const bool dual = p.act == CHIMERE_ACT_SWIGLU;
-        float* xch = reinterpret_cast<float*>(smem);   // [128][129] floats in the ring, which is idle once ...
-        epilogue_sync();                                // ... every epilogue warp has read its last scales from it
+        float* xch = reinterpret_cast<float*>(smem);   // [128][129] floats behind the ring
+        epilogue_sync();                                // every read-back warp is done with the previous tile's exchange
 #pragma unroll
         for (int c = 0; c < kG_EpiCols; ++c) xch[row * 129 + part * kG_EpiCols + c] = acc[c];
         epilogue_sync();
@@ -302,10 +329,10 @@ struct GateUpPolicy {
 
 // down: rows of H; the tile's columns are pairs, written to pair_out[pair row][H]
 struct DownPolicy {
-    __device__ static __forceinline__ bool work(const PrefillGemmParams& p, int idx, GemmWork& w) {
+    __device__ static __forceinline__ int work(const PrefillGemmParams& p, int idx, GemmWork& w) {
         const int n_tiles = __ldcg(p.tiles);
         const int j = idx / p.row_tiles_max, rt = idx - j * p.row_tiles_max;
-        if (j >= n_tiles) return false;
+        if (j >= n_tiles) return kWorkEnd;
         const int4 t = __ldcg(reinterpret_cast<const int4*>(p.tiles + kTileHeader) + j);
         const bool shared = t.x < 0;
         const int nb = (shared ? p.ncols_in_shared : p.ncols_in) / 32;
@@ -313,7 +340,7 @@ struct DownPolicy {
         w.b_src = p.b_tiles + (size_t)j * p.b_tile_stride;
         w.nblocks = nb; w.n_valid = t.z;
         w.aux0 = j; w.aux1 = rt; w.aux2 = shared ? 1 : 0; w.aux3 = t.y;
-        return true;
+        return kWorkOk;
     }
     __device__ static __forceinline__ void store(const PrefillGemmParams& p, const GemmWork& w, int row, int, int part, int,
                                                  float (&acc)[kG_EpiCols], uint8_t*, bool ok) {
@@ -360,28 +387,43 @@ cudaError_t launch_pack_mma128(const int8_t* q, const float* scales, uint8_t* ou
     return cudaGetLastError();
 }
 
-cudaError_t launch_gemm_i8_f32(const GemmParams& p, int n_items, cudaStream_t stream) {
+// persistent CTAs: one per SM, or fewer when there are fewer tiles
+static int gemm_grid(int n_items) {
+    static int n_sm = 0;
+    if (!n_sm) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+    }
+    return n_items < n_sm ? n_items : n_sm;
+}
+constexpr size_t kG_RingBytes = (size_t)kG_Stages * kG_StageBytes;
+constexpr size_t kG_XchBytes = 128 * 129 * sizeof(float);   // gate/up: where the two halves of a tile meet
+
+cudaError_t launch_gemm_i8_f32(const GemmParams& p_in, int n_items, cudaStream_t stream) {
     if (n_items <= 0) return cudaSuccess;
-    const size_t smem = (size_t)kG_Stages * kG_StageBytes + 1024;
+    GemmParams p = p_in;
+    p.n_items = n_items;
+    const size_t smem = kG_RingBytes + 1024;
     cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<PlainPolicy, GemmParams>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    gemm_i8_kernel<PlainPolicy, GemmParams><<<n_items, kG_Threads, smem, stream>>>(p);
+    gemm_i8_kernel<PlainPolicy, GemmParams><<<gemm_grid(n_items), kG_Threads, smem, stream>>>(p);
     return cudaGetLastError();
 }
 
 cudaError_t launch_prefill_gemm(const PrefillGemmParams& p, bool down, int n_tiles_max, cudaStream_t stream) {
-    const size_t smem = (size_t)kG_Stages * kG_StageBytes + 1024;
-    const int grid = n_tiles_max * p.row_tiles_max;
-    if (grid <= 0) return cudaSuccess;
+    const int n_items = n_tiles_max * p.row_tiles_max;
+    if (n_items <= 0) return cudaSuccess;
     cudaError_t e;
     if (down) {
+        const size_t smem = kG_RingBytes + 1024;
         e = cudaFuncSetAttribute(gemm_i8_kernel<DownPolicy, PrefillGemmParams>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        gemm_i8_kernel<DownPolicy, PrefillGemmParams><<<grid, kG_Threads, smem, stream>>>(p);
+        gemm_i8_kernel<DownPolicy, PrefillGemmParams><<<gemm_grid(n_items), kG_Threads, smem, stream>>>(p);
     } else {
+        const size_t smem = kG_RingBytes + kG_XchBytes + 1024;
         e = cudaFuncSetAttribute(gemm_i8_kernel<GateUpPolicy, PrefillGemmParams>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        gemm_i8_kernel<GateUpPolicy, PrefillGemmParams><<<grid, kG_Threads, smem, stream>>>(p);
+        gemm_i8_kernel<GateUpPolicy, PrefillGemmParams><<<gemm_grid(n_items), kG_Threads, smem, stream>>>(p);
     }
     return cudaGetLastError();
 }
@@ -438,29 +480,39 @@ cudaError_t launch_pack_mma128_ggml(int type, const void* raw, void* out, int n_
 
 // After routing: token tiles for the experts with at least `gemm_min` pairs (and for the shared expert), and the
 // GEMV work list rewritten to hold only the smaller experts.  One CTA of 256 threads, thread e = expert e.
+// Full tiles (128 pairs) come first and the partly filled ones last, so that the persistent GEMM CTAs, which take
+// tiles round-robin, all get a similar mix of expensive and cheap tiles.
 __global__ void __launch_bounds__(256) build_tiles_kernel(const int32_t* offsets, const int32_t* perm, int32_t* tiles, int32_t* list,
                                                           int E, int T, int top_k, int has_shared, int gemm_min) {
-    __shared__ int scan_t[8], scan_e[8];
+    __shared__ int scan_f[8], scan_p[8], scan_e[8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cnt = tid < E ? offsets[tid + 1] - offsets[tid] : 0, off = tid < E ? offsets[tid] : 0;
     const bool big = cnt >= gemm_min;
-    const int nt = big ? (cnt + 127) / 128 : 0;
+    const int nf = big ? cnt / 128 : 0;                   // full tiles
+    const int np = big && (cnt % 128) ? 1 : 0;            // the partly filled one
     const int ne = big ? 0 : (cnt + kMaxGroupTokens - 1) / kMaxGroupTokens;
-    int it = nt, ie = ne;
+    int jf = nf, jp = np, ie = ne;
 #pragma unroll
     for (int s = 1; s < 32; s <<= 1) {
-        const int a = __shfl_up_sync(0xffffffffu, it, s), b = __shfl_up_sync(0xffffffffu, ie, s);
-        if (lane >= s) { it += a; ie += b; }
+        const int a = __shfl_up_sync(0xffffffffu, jf, s), b = __shfl_up_sync(0xffffffffu, jp, s), c = __shfl_up_sync(0xffffffffu, ie, s);
+        if (lane >= s) { jf += a; jp += b; ie += c; }
     }
-    if (lane == 31) { scan_t[warp] = it; scan_e[warp] = ie; }
+    if (lane == 31) { scan_f[warp] = jf; scan_p[warp] = jp; scan_e[warp] = ie; }
     __syncthreads();
-    int bt = 0, be = 0, tot_t = 0, tot_e = 0;
-    for (int w = 0; w < 8; ++w) { if (w < warp) { bt += scan_t[w]; be += scan_e[w]; } tot_t += scan_t[w]; tot_e += scan_e[w]; }
-    const int nsh = has_shared ? (T + 127) / 128 : 0;
+    int bf = 0, bp = 0, be = 0, tot_f = 0, tot_p = 0, tot_e = 0;
+    for (int w = 0; w < 8; ++w) {
+        if (w < warp) { bf += scan_f[w]; bp += scan_p[w]; be += scan_e[w]; }
+        tot_f += scan_f[w]; tot_p += scan_p[w]; tot_e += scan_e[w];
+    }
+    // shared-expert tiles: the full ones in front, its partly filled one with the other partly filled ones
+    const int nsh_full = has_shared ? T / 128 : 0, nsh_part = has_shared && (T % 128) ? 1 : 0;
     int4* tv = reinterpret_cast<int4*>(tiles + kTileHeader);
-    for (int i = tid; i < nsh; i += 256) tv[i] = make_int4(-1, i * 128, min(128, T - i * 128), 0);
-    const int t0 = nsh + bt + it - nt;
-    for (int i = 0; i < nt; ++i) tv[t0 + i] = make_int4(tid, off + i * 128, min(128, cnt - i * 128), 0);
+    for (int i = tid; i < nsh_full; i += 256) tv[i] = make_int4(-1, i * 128, 128, 0);
+    const int f0 = nsh_full + bf + jf - nf;
+    for (int i = 0; i < nf; ++i) tv[f0 + i] = make_int4(tid, off + i * 128, 128, 0);
+    const int part0 = nsh_full + tot_f;
+    if (tid == 0 && nsh_part) tv[part0] = make_int4(-1, nsh_full * 128, T - nsh_full * 128, 0);
+    if (np) tv[part0 + nsh_part + bp + jp - np] = make_int4(tid, off + nf * 128, cnt - nf * 128, 0);
     const int e0 = be + ie - ne;
     for (int i = 0; i < ne; ++i) {
         int* ent = list + kListHeader + kListEntry * (e0 + i);
@@ -469,7 +521,7 @@ __global__ void __launch_bounds__(256) build_tiles_kernel(const int32_t* offsets
         for (int j = 0; j < kMaxGroupTokens; ++j) ent[4 + j] = j < mm ? perm[off + i * kMaxGroupTokens + j] : 0;
     }
     if (tid == 0) {
-        tiles[0] = nsh + tot_t; tiles[1] = nsh; tiles[2] = tot_t; tiles[3] = 0;
+        tiles[0] = nsh_full + nsh_part + tot_f + tot_p; tiles[1] = nsh_full + nsh_part; tiles[2] = tot_f + tot_p; tiles[3] = 0;
         list[0] = tot_e; list[1] = tot_e; list[2] = 0; list[3] = 0;
     }
 }

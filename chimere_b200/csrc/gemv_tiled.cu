@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(kThreadsT, 4) tile_kernel(const GemvParams p, 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nthreads = (int)blockDim.x, nwarps = nthreads >> 5;
     griddep_wait();
-    griddep_launch();
+    if (threadIdx.x == 0) griddep_launch();
     // one look-up names everything the CTA needs: the entry (expert, token count, pair rows)
     const int4* entv = reinterpret_cast<const int4*>(p.group_list + kListHeader + kListEntry * blockIdx.y);
     const int n_entries = __ldcg(p.group_list);
@@ -344,7 +344,7 @@ __global__ void __launch_bounds__(kThreadsT, 3) bulk_kernel(const GemvParams p, 
     // behind this grid.  The down stage is launched after a gate/up grid whose CTAs all passed that wait, so the
     // list is complete when its CTAs start: they look up their entry and ask for their weights first, and wait
     // for the gate/up results only then.
-    if (STAGE == kStageGateUp) { griddep_wait(); griddep_launch(); }
+    if (STAGE == kStageGateUp) { griddep_wait(); if (threadIdx.x == 0) griddep_launch(); }
     const int4* entv = reinterpret_cast<const int4*>(p.group_list + kListHeader + kListEntry * blockIdx.y);
     const int n_entries = __ldcg(p.group_list);
     const int4 e0 = __ldcg(entv), e1 = __ldcg(entv + 1), e2 = __ldcg(entv + 2);
@@ -356,6 +356,9 @@ __global__ void __launch_bounds__(kThreadsT, 3) bulk_kernel(const GemvParams p, 
     const int ncols = shared ? p.ncols_shared : p.ncols_routed, nb = ncols >> 5;
     const int width = 32 * wr, tile0 = blockIdx.x << wr_shift, tiles_total = nrows >> 5;
     if (tile0 >= tiles_total) return;
+    // down stage: let the next kernel of the stream (the next layer's router, if it was launched programmatically)
+    // bring its CTAs in; it waits for this grid before it touches the workspace
+    if (STAGE == kStageDown && tid == 0) griddep_launch();
     const bool need_red = STAGE == kStageGateUp || wk > 1;
     const BulkSmem bs = bulk_smem(tile_bytes_max, max(p.ncols_routed, p.ncols_shared), wr, wk, kMat, mt, need_red);
     float* red = reinterpret_cast<float*>(smem + bs.red);
@@ -530,23 +533,6 @@ struct Geom { int wk, wr; };
 static int ngroups_of(int ncols) { return (ncols / 32 + kGroupUnits - 1) / kGroupUnits; }
 static int64_t tile_bytes_of(int type, int ncols) { return tiled_matrix_bytes(type, 32, ncols); }
 static int log2i(int v) { int s = 0; while ((1 << s) < v) ++s; return s; }
-
-// Launch with programmatic stream serialization: the grid may start while the previous kernel of the stream is
-// still running; the kernels call griddep_wait() before they touch what that kernel writes.
-template <typename... KArgs, typename... Args>
-static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, int threads, size_t smem, cudaStream_t stream, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(threads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
-}
 
 // Gate/up: one row tile per CTA, its K range cut over the eight warps.
 static Geom geom_for(int ngroups_min) {

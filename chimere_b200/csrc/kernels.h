@@ -101,6 +101,7 @@ struct GemmItem { int64_t a_offset, b_offset; int n_valid, rows_valid, out_row0,
 struct GemmParams {
     const uint8_t* a_base; const uint8_t* b_base;   // mma128 tiles; an item's operands start at base + offset
     const GemmItem* items;
+    int n_items;
     int nblocks;                                    // 32-wide K blocks
     float* out; int64_t ldo;                        // f32 output, row pitch in floats
     int32_t* status;
@@ -140,5 +141,22 @@ cudaError_t launch_gate_up_tiled(const GemvParams& p, int max_entries, cudaStrea
 cudaError_t launch_down_tiled(const GemvParams& p, int max_entries, cudaStream_t stream);
 cudaError_t launch_block_sumi_tiled(int type, const void* packed, const void* xq8, int32_t* sumi, int ncols, int nrows,
                                     cudaStream_t stream);
+
+// Launch with programmatic stream serialization: the grid may start while the previous kernel of the stream is
+// still running; the kernels call griddep_wait() before they touch what that kernel writes.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, int threads, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 }  // namespace chimere

@@ -126,9 +126,17 @@ __device__ void topk_warp(const RouteParams& p, const float* logit_row, int t, i
 // barriers are between those steps, however many pairs there are.  The work entries are then filled by all
 // threads (entry -> expert by bisection of the entry offsets).
 constexpr int kDispatchSmemInts = 256 + 256 + 2048 + 32 + 288 + 1024;
-__device__ void build_dispatch(const RouteParams& p, int* smem_i, const int* s_ids) {
+// ids_room: ints of shared memory behind the kDispatchSmemInts of scratch; if the ids fit there they are fetched
+// once, all loads in flight together, instead of one dependent load per step of the two passes.
+__device__ void build_dispatch(const RouteParams& p, int* smem_i, const int* s_ids, int ids_room) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int E = p.E, P = p.T * p.top_k;
+    if (!s_ids && P <= ids_room) {
+        int* stage = smem_i + kDispatchSmemInts;
+        const int istr0 = p.idx_stride > 1 ? p.idx_stride : 1;
+        for (int q = tid; q < P; q += 256) stage[q] = __ldcg(p.topk_idx + (size_t)q * istr0);
+        s_ids = stage;   // visible after the barrier below
+    }
     int* hist = smem_i;               // [256] pairs per expert
     int* cursor = smem_i + 256;       // [256] first position of each expert
     int* warp_cnt = smem_i + 512;     // [8][256] per warp: pairs of each expert, then the warp's next position within it
@@ -251,7 +259,6 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
     const int nrows = E + (p.shexp_gate_w ? 1 : 0);
     const int t0 = blockIdx.y * TT, r0 = blockIdx.x * TE;
     const int n_rtiles = gridDim.x;
-    griddep_launch();   // the grouped GEMV that follows may bring its CTAs in; it waits for this grid before it reads anything
 
     // ---- partial dot products; the router rows come from DRAM, so their loads go out first and the Q8_1 of
     //      this token tile's input rows (blocks dealt round-robin to the row tiles) runs while they are in flight ----
@@ -276,6 +283,11 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
             for (int b = 0; b < TE; ++b) wv[i][b] = (j < H && wrow[b]) ? __ldg(wrow[b] + j) : 0.0f;
         }
         if (j0 == 0) {
+            // The router rows are constants of the layer: their loads were issued above, possibly while the previous
+            // kernel of the stream was still running (programmatic launch).  Everything that kernel may have written
+            // (the input rows) or may still be reading (the workspace) is touched only after this wait.
+            griddep_wait();
+            if (tid == 0) griddep_launch();   // the grouped GEMV that follows may bring its CTAs in; it waits for this grid itself
             const int nbH = H >> 5;
             const int nt = min(TT, p.T - t0);
             for (int q = blockIdx.x * 8 + warp; q < nt * nbH; q += n_rtiles * 8) {
@@ -337,7 +349,7 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
     if (gridDim.y == 1) {
         // the only token tile: its ids are all in shared memory
         __syncthreads();
-        build_dispatch(p, reinterpret_cast<int*>(smem_f), s_ids);
+        build_dispatch(p, reinterpret_cast<int*>(smem_f), s_ids, 0);
         return;
     }
     __threadfence();
@@ -347,13 +359,122 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
     if (!s_flag) return;
     __threadfence();
     if (tid == 0) p.counters[kCtrRouteAll] = 0;
-    build_dispatch(p, reinterpret_cast<int*>(smem_f), nullptr);
+    build_dispatch(p, reinterpret_cast<int*>(smem_f), nullptr, (int)(TT * TE * 256) - kDispatchSmemInts);
+}
+
+// Larger batches: a CTA keeps its token tile's input columns in registers (thread p: elements p, p+256, ... of TT
+// rows) and walks over a group of router rows two at a time, the next pair's loads in flight while the current
+// pair is multiplied; every row element is read once per token tile and the input once per CTA.  The order of the
+// additions is the same as in route_kernel.  grid = (row groups, token tiles), NC = ceil(H / 256) columns per thread.
+constexpr int kBigRouteSmemInts = 24 * 1024;   // 96 KiB: two partial-sum buffers, later the dispatch scratch and the staged ids
+template <int TT, int NC>
+__global__ void __launch_bounds__(256, 1) route_big_kernel(const RouteParams p, int rows_per_group) {
+    extern __shared__ __align__(16) float smem_f[];   // [2][TT * 2][256] partial sums; the dispatch scratch afterwards
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int H = p.H, E = p.E;
+    const int nrows = E + (p.shexp_gate_w ? 1 : 0);
+    const int t0 = blockIdx.y * TT;
+    const int r_begin = blockIdx.x * rows_per_group, r_end = min(nrows, r_begin + rows_per_group);
+    if (tid == 0) griddep_launch();
+    auto wrow = [&](int r) -> const float* { return r < E ? p.router_w + (size_t)r * H : p.shexp_gate_w; };
+
+    float wn[2][NC];
+#pragma unroll
+    for (int b = 0; b < 2; ++b)
+#pragma unroll
+        for (int i = 0; i < NC; ++i) {
+            const int j = i * 256 + tid;
+            wn[b][i] = (r_begin + b < r_end && j < H) ? __ldg(wrow(r_begin + b) + j) : 0.0f;
+        }
+    float xv[TT][NC];
+#pragma unroll
+    for (int a = 0; a < TT; ++a)
+#pragma unroll
+        for (int i = 0; i < NC; ++i) {
+            const int j = i * 256 + tid;
+            xv[a][i] = (j < H && t0 + a < p.T) ? p.x[(size_t)(t0 + a) * H + j] : 0.0f;
+        }
+    {   // Q8_1 of this token tile's input rows, blocks dealt round-robin to the row groups
+        const int nbH = H >> 5;
+        const int nt = min(TT, p.T - t0);
+        for (int q = blockIdx.x * 8 + warp; q < nt * nbH; q += gridDim.x * 8) {
+            const int tt = q / nbH, b = q - tt * nbH;
+            const float xi = p.x[(size_t)(t0 + tt) * H + b * 32 + lane];
+            quantize_block_q8_1(xi, p.x_q8 + ((size_t)(t0 + tt) * nbH + b) * kQ81Bytes, lane,
+                                p.x_soa_q + (size_t)(t0 + tt) * H + b * 32, p.x_soa_d + (size_t)(t0 + tt) * p.x_soa_d_stride + b);
+        }
+    }
+    int buf = 0;
+    for (int r = r_begin; r < r_end; r += 2) {
+        float wc[2][NC];
+#pragma unroll
+        for (int b = 0; b < 2; ++b)
+#pragma unroll
+            for (int i = 0; i < NC; ++i) wc[b][i] = wn[b][i];
+#pragma unroll
+        for (int b = 0; b < 2; ++b)
+#pragma unroll
+            for (int i = 0; i < NC; ++i) {
+                const int j = i * 256 + tid;
+                wn[b][i] = (r + 2 + b < r_end && j < H) ? __ldg(wrow(r + 2 + b) + j) : 0.0f;
+            }
+        float acc[TT][2];
+#pragma unroll
+        for (int a = 0; a < TT; ++a) { acc[a][0] = 0.0f; acc[a][1] = 0.0f; }
+#pragma unroll
+        for (int i = 0; i < NC; ++i) {   // ascending j, one fused multiply-add each
+            if (i * 256 + tid < H) {
+#pragma unroll
+                for (int a = 0; a < TT; ++a) {
+                    acc[a][0] = fmaf(wc[0][i], xv[a][i], acc[a][0]);
+                    acc[a][1] = fmaf(wc[1][i], xv[a][i], acc[a][1]);
+                }
+            }
+        }
+        float* red = smem_f + buf * (TT * 2 * 256);
+#pragma unroll
+        for (int a = 0; a < TT; ++a) { red[(a * 2 + 0) * 256 + tid] = acc[a][0]; red[(a * 2 + 1) * 256 + tid] = acc[a][1]; }
+        __syncthreads();
+        for (int o = warp; o < TT * 2; o += 8) {
+            const float v = tree256(red + o * 256, lane);
+            const int t = t0 + (o >> 1), rr = r + (o & 1);
+            if (lane == 0 && t < p.T && rr < r_end) {
+                if (rr < E) p.router_logits[(size_t)t * E + rr] = p.router_bias ? v + p.router_bias[rr] : v;
+                else p.sh_gate_logit[t] = v;
+            }
+        }
+        buf ^= 1;   // the next pair writes the other half: its last readers are behind the barrier above
+    }
+
+    // ---- last CTA of the token tile: scores and top-k ----
+    __shared__ int s_flag;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_flag = (atomicAdd(&p.counters[kCtrRouteTile + blockIdx.y], 1) == (int)gridDim.x - 1);
+    __syncthreads();
+    if (!s_flag) return;
+    __threadfence();
+    if (tid == 0) p.counters[kCtrRouteTile + blockIdx.y] = 0;
+    for (int a = warp; a < TT; a += 8) {
+        const int t = t0 + a;
+        if (t < p.T) topk_warp(p, p.router_logits + (size_t)t * E, t, lane, smem_f + warp * 256, nullptr);
+    }
+    // ---- last token tile overall: dispatch permutation and work list ----
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_flag = (atomicAdd(&p.counters[kCtrRouteAll], 1) == (int)gridDim.y - 1);
+    __syncthreads();
+    if (!s_flag) return;
+    __threadfence();
+    if (tid == 0) p.counters[kCtrRouteAll] = 0;
+    build_dispatch(p, reinterpret_cast<int*>(smem_f), nullptr, kBigRouteSmemInts - kDispatchSmemInts);
 }
 
 // The dispatch step alone, for callers that bring their own expert ids in p.topk_idx.
+constexpr int kPermuteIdsRoom = 8192;
 __global__ void __launch_bounds__(256) permute_kernel(const RouteParams p) {
     extern __shared__ __align__(16) float smem_f[];
-    build_dispatch(p, reinterpret_cast<int*>(smem_f), nullptr);
+    build_dispatch(p, reinterpret_cast<int*>(smem_f), nullptr, kPermuteIdsRoom);
 }
 
 // Final step of an expert-parallel layer on the tokens' home rank: routing-weighted sum of the k expert
@@ -429,7 +550,7 @@ static size_t route_smem(int TT, int TE) {
 }
 
 cudaError_t launch_permute(const RouteParams& p, cudaStream_t stream) {
-    permute_kernel<<<1, 256, kDispatchSmemInts * sizeof(int), stream>>>(p);
+    permute_kernel<<<1, 256, (kDispatchSmemInts + kPermuteIdsRoom) * sizeof(int), stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -452,7 +573,25 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
     if (p.T <= 32) {
         constexpr int TT = 8, TE = 2;
         dim3 grid((nrows + TE - 1) / TE, (p.T + TT - 1) / TT);
-        route_kernel<TT, TE><<<grid, 256, route_smem(TT, TE), stream>>>(p);
+        return launch_pdl(route_kernel<TT, TE>, grid, 256, route_smem(TT, TE), stream, p);
+    } else if (p.H <= 4096) {
+        // token tiles of 16 (8 for H > 2048) with the input in registers; row groups so that a few CTAs per SM exist
+        const bool wide = p.H > 2048;
+        const int tt = wide ? 8 : 16;
+        const int token_tiles = (p.T + tt - 1) / tt;
+        int groups = (3 * 148 + token_tiles - 1) / token_tiles;
+        groups = groups < 1 ? 1 : (groups > (nrows + 1) / 2 ? (nrows + 1) / 2 : groups);
+        const int rows_per_group = 2 * (((nrows + groups - 1) / groups + 1) / 2);
+        const dim3 grid((nrows + rows_per_group - 1) / rows_per_group, token_tiles);
+        const size_t smem = (size_t)kBigRouteSmemInts * sizeof(int);
+        static bool attr_set = false;
+        if (!attr_set) {
+            cudaFuncSetAttribute(route_big_kernel<16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(route_big_kernel<8, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            attr_set = true;
+        }
+        if (wide) route_big_kernel<8, 16><<<grid, 256, smem, stream>>>(p, rows_per_group);
+        else route_big_kernel<16, 8><<<grid, 256, smem, stream>>>(p, rows_per_group);
     } else {
         constexpr int TT = 8, TE = 8;
         static bool attr_set = false;
