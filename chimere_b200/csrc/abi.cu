@@ -154,6 +154,7 @@ static RouteParams route_params(const chimere_moe_layer* w, const float* d_x, in
     p.topk_idx = ws->topk_idx; p.topk_w = ws->topk_w; p.x_q8 = ws->x_q8;
     p.perm = ws->perm; p.offsets = ws->offsets; p.group_list = ws->group_list; p.counters = ws->counters;
     p.x_soa_q = ws->x_q; p.x_soa_d = ws->x_d; p.x_soa_d_stride = (w->H / 32 + 3) & ~3;
+    p.status = ws->status;
     return p;
 }
 

@@ -527,21 +527,25 @@ __global__ void __launch_bounds__(256) build_tiles_kernel(const int32_t* offsets
 }
 
 // Token tiles of the gate/up GEMM: the Q8_1 planes of each tile's tokens in mma128 order.
-// grid = (max tiles, 128 token slots), 128 threads = the 16-byte chunks of a row.
-__global__ void __launch_bounds__(128) gather_tiles_kernel(const int32_t* tiles, const int32_t* perm, const int8_t* x_q, const float* x_d,
+// grid = (max tiles, 16 groups of 8 token slots), 256 threads = 8 slots x 32 chunk lanes: the eight slots of a group
+// are the 8 x 16 bytes of one core-matrix row group, so every 128-byte segment of the tile is written whole, and a
+// token's 16-byte chunks are read four in a row.
+__global__ void __launch_bounds__(256) gather_tiles_kernel(const int32_t* tiles, const int32_t* perm, const int8_t* x_q, const float* x_d,
                                                            int x_d_stride, uint8_t* b_tiles, int64_t b_tile_stride, int H, int top_k) {
-    const int j = blockIdx.x, c = blockIdx.y;
+    const int j = blockIdx.x, grp = blockIdx.y;
     if (j >= __ldcg(tiles)) return;
     const int4 t = __ldcg(reinterpret_cast<const int4*>(tiles + kTileHeader) + j);
+    const int sl = threadIdx.x & 7, lane_ch = threadIdx.x >> 3;
+    const int c = grp * 8 + sl;                   // token slot of the tile
     const bool valid = c < t.z;
     const int tok = !valid ? 0 : (t.x < 0 ? t.y + c : __ldcg(perm + t.y + c) / top_k);
     uint8_t* base = b_tiles + (size_t)j * b_tile_stride;
-    for (int ch = threadIdx.x; ch < H / 16; ch += 128) {
+    for (int ch = lane_ch; ch < H / 16; ch += 32) {
         const uint4 v = valid ? __ldcg(reinterpret_cast<const uint4*>(x_q + (size_t)tok * H) + ch) : make_uint4(0, 0, 0, 0);
         const int b = ch >> 1, khalf = ch & 1;
-        *reinterpret_cast<uint4*>(base + (size_t)b * kG_TileBytes + khalf * 2048 + (c >> 3) * 128 + (c & 7) * 16) = v;
+        *reinterpret_cast<uint4*>(base + (size_t)b * kG_TileBytes + khalf * 2048 + grp * 128 + sl * 16) = v;
     }
-    for (int b = threadIdx.x; b < H / 32; b += 128)
+    for (int b = lane_ch; b < H / 32; b += 32)
         *reinterpret_cast<float*>(base + (size_t)b * kG_TileBytes + 4096 + c * 4) = valid ? __ldcg(x_d + (size_t)tok * x_d_stride + b) : 0.0f;
 }
 
@@ -554,7 +558,7 @@ cudaError_t launch_build_tiles(const int32_t* offsets, const int32_t* perm, int3
 cudaError_t launch_gather_tiles(const int32_t* tiles, const int32_t* perm, const int8_t* x_q, const float* x_d, int x_d_stride,
                                 uint8_t* b_tiles, int64_t b_tile_stride, int H, int top_k, int n_tiles_max, cudaStream_t stream) {
     if (n_tiles_max <= 0) return cudaSuccess;
-    gather_tiles_kernel<<<dim3(n_tiles_max, 128), 128, 0, stream>>>(tiles, perm, x_q, x_d, x_d_stride, b_tiles, b_tile_stride, H, top_k);
+    gather_tiles_kernel<<<dim3(n_tiles_max, 16), 256, 0, stream>>>(tiles, perm, x_q, x_d, x_d_stride, b_tiles, b_tile_stride, H, top_k);
     return cudaGetLastError();
 }
 

@@ -33,6 +33,7 @@ struct RouteParams {
     int32_t* offsets;           // [E+1]
     int32_t* group_list;
     int32_t* counters;
+    int32_t* status;            // workspace status word (may be null): a bounded wait that ran out raises a bit here
 };
 
 // Grouped GEMV over work entries (see common.cuh for the list layout).

@@ -362,30 +362,50 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
     build_dispatch(p, reinterpret_cast<int*>(smem_f), nullptr, (int)(TT * TE * 256) - kDispatchSmemInts);
 }
 
+// Q8_1 of all input rows, one warp per 32-element block (large batches: the router kernel below does not do it).
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const RouteParams p) {
+    const int lane = threadIdx.x & 31, nbH = p.H >> 5;
+    const int64_t q = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (q >= (int64_t)p.T * nbH) return;
+    const int t = (int)(q / nbH), b = (int)(q - (int64_t)t * nbH);
+    quantize_block_q8_1(p.x[(size_t)t * p.H + b * 32 + lane], p.x_q8 + ((size_t)t * nbH + b) * kQ81Bytes, lane,
+                        p.x_soa_q + (size_t)t * p.H + b * 32, p.x_soa_d + (size_t)t * p.x_soa_d_stride + b);
+}
+
 // Larger batches: a CTA keeps its token tile's input columns in registers (thread p: elements p, p+256, ... of TT
-// rows) and walks over a group of router rows two at a time, the next pair's loads in flight while the current
-// pair is multiplied; every row element is read once per token tile and the input once per CTA.  The order of the
-// additions is the same as in route_kernel.  grid = (row groups, token tiles), NC = ceil(H / 256) columns per thread.
-constexpr int kBigRouteSmemInts = 24 * 1024;   // 96 KiB: two partial-sum buffers, later the dispatch scratch and the staged ids
+// rows) and walks over a group of router rows two at a time.  The rows come through a ring of bulk copies into
+// shared memory (one thread asks, four pairs ahead), so no load latency sits between the multiply-adds; every row
+// element is read once per token tile and the input once per CTA.  The order of the additions is the same as in
+// route_kernel.  grid = (row groups, token tiles), NC = ceil(H / 256) columns per thread; H a multiple of 4.
+constexpr int kBigRouteSmemInts = 24 * 1024;   // 96 KiB: partial sums + row ring; later the dispatch scratch and the staged ids
+constexpr int kBigRing = 4;
 template <int TT, int NC>
-__global__ void __launch_bounds__(256, 1) route_big_kernel(const RouteParams p, int rows_per_group) {
-    extern __shared__ __align__(16) float smem_f[];   // [2][TT * 2][256] partial sums; the dispatch scratch afterwards
+__global__ void __launch_bounds__(256, 2) route_big_kernel(const RouteParams p, int rows_per_group) {
+    extern __shared__ __align__(16) float smem_f[];   // [2][TT * 2][256] partial sums, then [kBigRing][2][H] router rows
+    __shared__ __align__(8) uint64_t s_full[kBigRing];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int H = p.H, E = p.E;
     const int nrows = E + (p.shexp_gate_w ? 1 : 0);
     const int t0 = blockIdx.y * TT;
     const int r_begin = blockIdx.x * rows_per_group, r_end = min(nrows, r_begin + rows_per_group);
+    const int npairs = (r_end - r_begin + 1) / 2;
     if (tid == 0) griddep_launch();
+    float* ring = smem_f + 2 * TT * 2 * 256;
     auto wrow = [&](int r) -> const float* { return r < E ? p.router_w + (size_t)r * H : p.shexp_gate_w; };
-
-    float wn[2][NC];
-#pragma unroll
-    for (int b = 0; b < 2; ++b)
-#pragma unroll
-        for (int i = 0; i < NC; ++i) {
-            const int j = i * 256 + tid;
-            wn[b][i] = (r_begin + b < r_end && j < H) ? __ldg(wrow(r_begin + b) + j) : 0.0f;
-        }
+    // thread 0: rows of pair k into ring slot k % kBigRing (a missing second row is not copied and not used)
+    auto ask = [&](int k) {
+        const int r = r_begin + 2 * k, slot = k % kBigRing;
+        const uint32_t bytes = (uint32_t)H * 4u;
+        const int n = (r + 1 < r_end) ? 2 : 1;
+        mbar_expect_tx(&s_full[slot], bytes * n);
+        bulk_g2s(ring + (size_t)slot * 2 * H, wrow(r), bytes, &s_full[slot]);
+        if (n == 2) bulk_g2s(ring + (size_t)slot * 2 * H + H, wrow(r + 1), bytes, &s_full[slot]);
+    };
+    if (tid == 0) {
+        for (int i = 0; i < kBigRing; ++i) mbar_init(&s_full[i], 1);
+        mbar_fence_init();
+        for (int k = 0; k < kBigRing && k < npairs; ++k) ask(k);
+    }
     float xv[TT][NC];
 #pragma unroll
     for (int a = 0; a < TT; ++a)
@@ -394,47 +414,39 @@ __global__ void __launch_bounds__(256, 1) route_big_kernel(const RouteParams p, 
             const int j = i * 256 + tid;
             xv[a][i] = (j < H && t0 + a < p.T) ? p.x[(size_t)(t0 + a) * H + j] : 0.0f;
         }
-    {   // Q8_1 of this token tile's input rows, blocks dealt round-robin to the row groups
-        const int nbH = H >> 5;
-        const int nt = min(TT, p.T - t0);
-        for (int q = blockIdx.x * 8 + warp; q < nt * nbH; q += gridDim.x * 8) {
-            const int tt = q / nbH, b = q - tt * nbH;
-            const float xi = p.x[(size_t)(t0 + tt) * H + b * 32 + lane];
-            quantize_block_q8_1(xi, p.x_q8 + ((size_t)(t0 + tt) * nbH + b) * kQ81Bytes, lane,
-                                p.x_soa_q + (size_t)(t0 + tt) * H + b * 32, p.x_soa_d + (size_t)(t0 + tt) * p.x_soa_d_stride + b);
-        }
-    }
+    __syncthreads();   // barriers initialised
     int buf = 0;
-    for (int r = r_begin; r < r_end; r += 2) {
-        float wc[2][NC];
-#pragma unroll
-        for (int b = 0; b < 2; ++b)
-#pragma unroll
-            for (int i = 0; i < NC; ++i) wc[b][i] = wn[b][i];
-#pragma unroll
-        for (int b = 0; b < 2; ++b)
-#pragma unroll
-            for (int i = 0; i < NC; ++i) {
-                const int j = i * 256 + tid;
-                wn[b][i] = (r + 2 + b < r_end && j < H) ? __ldg(wrow(r + 2 + b) + j) : 0.0f;
-            }
+    for (int k = 0; k < npairs; ++k) {
+        const int r = r_begin + 2 * k, slot = k % kBigRing;
+        const bool two = r + 1 < r_end;
+        if (!mbar_wait(&s_full[slot], (uint32_t)((k / kBigRing) & 1))) {
+            if (p.status && tid == 0) atomicOr(p.status, kStatusWaitTimeout);   // a wait ran out: leave a mark, go on
+            mbar_wait(&s_full[slot], (uint32_t)((k / kBigRing) & 1));
+        }
+        const float* w0 = ring + (size_t)slot * 2 * H;
         float acc[TT][2];
 #pragma unroll
         for (int a = 0; a < TT; ++a) { acc[a][0] = 0.0f; acc[a][1] = 0.0f; }
 #pragma unroll
         for (int i = 0; i < NC; ++i) {   // ascending j, one fused multiply-add each
-            if (i * 256 + tid < H) {
+            const int j = i * 256 + tid;
+            if (j < H) {
+                const float wa = w0[j], wb = two ? w0[H + j] : 0.0f;
 #pragma unroll
                 for (int a = 0; a < TT; ++a) {
-                    acc[a][0] = fmaf(wc[0][i], xv[a][i], acc[a][0]);
-                    acc[a][1] = fmaf(wc[1][i], xv[a][i], acc[a][1]);
+                    acc[a][0] = fmaf(wa, xv[a][i], acc[a][0]);
+                    acc[a][1] = fmaf(wb, xv[a][i], acc[a][1]);
                 }
             }
         }
         float* red = smem_f + buf * (TT * 2 * 256);
 #pragma unroll
         for (int a = 0; a < TT; ++a) { red[(a * 2 + 0) * 256 + tid] = acc[a][0]; red[(a * 2 + 1) * 256 + tid] = acc[a][1]; }
-        __syncthreads();
+        __syncthreads();   // partial sums complete; every thread is done with this ring slot
+        if (tid == 0 && k + kBigRing < npairs) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            ask(k + kBigRing);
+        }
         for (int o = warp; o < TT * 2; o += 8) {
             const float v = tree256(red + o * 256, lane);
             const int t = t0 + (o >> 1), rr = r + (o & 1);
@@ -574,24 +586,24 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
         constexpr int TT = 8, TE = 2;
         dim3 grid((nrows + TE - 1) / TE, (p.T + TT - 1) / TT);
         return launch_pdl(route_kernel<TT, TE>, grid, 256, route_smem(TT, TE), stream, p);
-    } else if (p.H <= 4096) {
+    } else if (p.H <= 2048 && p.H % 4 == 0) {
         // token tiles of 16 (8 for H > 2048) with the input in registers; row groups so that a few CTAs per SM exist
-        const bool wide = p.H > 2048;
-        const int tt = wide ? 8 : 16;
+        // Q8_1 of the input by its own small kernel, then the logits: token tiles of 8 rows held in registers, the
+        // router rows dealt to row groups so that a few CTAs per SM exist
+        quantize_rows_kernel<<<(unsigned)(((int64_t)p.T * (p.H / 32) + 7) / 8), 256, 0, stream>>>(p);
+        const int tt = 8;
         const int token_tiles = (p.T + tt - 1) / tt;
-        int groups = (3 * 148 + token_tiles - 1) / token_tiles;
+        int groups = (4 * 148 + token_tiles - 1) / token_tiles;
         groups = groups < 1 ? 1 : (groups > (nrows + 1) / 2 ? (nrows + 1) / 2 : groups);
         const int rows_per_group = 2 * (((nrows + groups - 1) / groups + 1) / 2);
         const dim3 grid((nrows + rows_per_group - 1) / rows_per_group, token_tiles);
-        const size_t smem = (size_t)kBigRouteSmemInts * sizeof(int);
+        const size_t smem = (size_t)kBigRouteSmemInts * sizeof(int);   // 2 x 16 KiB partial sums + 4 x 2 x H x 4 <= 64 KiB ring
         static bool attr_set = false;
         if (!attr_set) {
-            cudaFuncSetAttribute(route_big_kernel<16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            cudaFuncSetAttribute(route_big_kernel<8, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(route_big_kernel<8, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             attr_set = true;
         }
-        if (wide) route_big_kernel<8, 16><<<grid, 256, smem, stream>>>(p, rows_per_group);
-        else route_big_kernel<16, 8><<<grid, 256, smem, stream>>>(p, rows_per_group);
+        route_big_kernel<8, 8><<<grid, 256, smem, stream>>>(p, rows_per_group);
     } else {
         constexpr int TT = 8, TE = 8;
         static bool attr_set = false;
