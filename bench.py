@@ -294,6 +294,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--prefill-tokens", default="512,2048", help="comma list of T for the secondary prefill measurement ('' = skip)")
+    ap.add_argument("--prefill-only", action="store_true",
+                    help="run only the secondary prefill measurement and print its JSON (used for profiling the grouped GEMM)")
     ap.add_argument("--layout", default="tiled", choices=["tiled", "ggml"],
                     help="weight layout the layer entry runs on: the library's tiled32 repack (default) or raw ggml blocks")
     args = ap.parse_args()
@@ -318,6 +320,9 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     lib = abi.load()
+    if args.prefill_only:
+        print(json.dumps({"prefill": measure_prefill(lib, dev, [int(t) for t in args.prefill_tokens.split(",") if t])}))
+        return 0
     cfg = configs.QWEN_IQ3S
     T, L, K, W = args.tokens, args.layers, args.steps, args.warmup
     hbm_peak, peak_kind = peaks()
