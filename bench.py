@@ -293,7 +293,7 @@ def main():
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
-    ap.add_argument("--prefill-tokens", default="512,2048", help="comma list of T for the secondary prefill measurement ('' = skip)")
+    ap.add_argument("--prefill-tokens", default="512,2048,8192", help="comma list of T for the secondary prefill measurement ('' = skip)")
     ap.add_argument("--prefill-only", action="store_true",
                     help="run only the secondary prefill measurement and print its JSON (used for profiling the grouped GEMM)")
     ap.add_argument("--layout", default="tiled", choices=["tiled", "ggml"],
@@ -437,11 +437,11 @@ def main():
     gu_secs = time_steps(graph_of(gate_up_all).replay, max(5, K), 3) / (max(5, K) * L)
     dn_secs = time_steps(graph_of(down_all).replay, max(5, K), 3) / (max(5, K) * L)
     rt_secs = time_steps(graph_of(route_all).replay, max(5, K), 3) / (max(5, K) * L)
-    roof = {"bound": "hbm", "kernel": ("tile_kernel<IQ3_S, gate_up>" if args.layout == "tiled" else "gate_up_kernel<IQ3_S>"), "achieved": gu_bytes / gu_secs / 1e9, "peak": hbm_peak,
+    roof = {"bound": "hbm", "kernel": ("bulk_kernel<IQ3_S, gate_up>" if args.layout == "tiled" else "gate_up_kernel<IQ3_S>"), "achieved": gu_bytes / gu_secs / 1e9, "peak": hbm_peak,
             "unit": "GB/s", "frac": gu_bytes / gu_secs / 1e9 / hbm_peak, "peak_kind": peak_kind,
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at these sizes (ncu capture summarised
-            # in profiles/tile_kernel_decode_T8.md; IQ3_S is streamed as 4-bit codes: +22 % over the ggml bytes)
-            "traffic": (67055872 + 120000) if (args.layout == "tiled" and T == 8) else None,
+            # in profiles/bulk_kernel_decode_T8.md; IQ3_S is streamed as 4-bit codes: +22 % over the ggml bytes)
+            "traffic": (67008768 + 1450240) if (args.layout == "tiled" and T == 8) else None,
             "us_per_launch": gu_secs * 1e6, "algorithmic_bytes_per_launch": gu_bytes,
             "down_kernel": {"achieved": dn_bytes / dn_secs / 1e9, "frac": dn_bytes / dn_secs / 1e9 / hbm_peak,
                             "us_per_launch": dn_secs * 1e6, "algorithmic_bytes_per_launch": dn_bytes},

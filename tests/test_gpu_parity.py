@@ -132,12 +132,12 @@ def test_forward_full_size(cfg, T, layout):
     check_rows(y.cpu().numpy(), o["y"])
 
 
-def test_routing_bit_exact_against_reference_kernels():
+@pytest.mark.parametrize("T", [16, 75])   # 75 > 32: the large-batch router (token tiles in registers, ragged last tile)
+def test_routing_bit_exact_against_reference_kernels(T):
     if not refkernels.available():
         pytest.skip("oracle/_ref cubin not built")
     cfg = configs.QWEN_Q4_0
     wd, _ = layer_pair(cfg)
-    T = 16
     x = configs.make_input(cfg, T, device="cuda")
     sc = MoeScratch(wd, T)
     route_only(wd, sc, x)
@@ -153,6 +153,10 @@ def test_routing_bit_exact_against_reference_kernels():
         # shared-expert gate logit: same kernel shape as a one-row GEMV
         g = refkernels.f32_gemv(wd.shexp_gate_proj[None, :].contiguous(), x[t])
         assert torch.equal(g[0], sc.sh_gate_logit(T)[t])
+    # the dispatch permutation of those indices: stable counting sort by expert
+    perm, offs = oracle.permute(sc.topk_indices(T).cpu().numpy(), cfg.E)
+    assert np.array_equal(sc.perm(T).cpu().numpy(), perm)
+    assert np.array_equal(sc.offsets().cpu().numpy(), offs)
 
 
 def test_routing_ties_and_zipf_bias():
