@@ -149,9 +149,11 @@ class ExpertParallelMoE:
         abi.check(lib.chimere_b200_moe_route_home(C.byref(self.home), x.data_ptr(), T, C.byref(self.ws_home.ws), st), "route_home")
         abi.check(lib.chimere_b200_moe_ep_pack(C.byref(self.home), T, C.byref(self.ws_home.ws), send.data_ptr(), slot.data_ptr(),
                                                self.E_loc, G, C_, rb, st), "ep_pack")
-        dist.all_to_all_single(recv, send, group=self.group)
-        # the shared expert needs nothing from other ranks: it runs while the dispatch is in flight
+        # the shared expert needs nothing from other ranks: it runs while the dispatch is in flight (the exchange is
+        # enqueued on the communicator's stream; this stream joins it only after the shared expert's kernels)
+        work = dist.all_to_all_single(recv, send, group=self.group, async_op=True)
         abi.check(lib.chimere_b200_moe_shared_expert(C.byref(self.home), T, C.byref(self.ws_home.ws), st), "shared_expert")
+        work.wait()
         abi.check(lib.chimere_b200_moe_experts_packed(C.byref(self.owner), n, recv.data_ptr(), rb, C.byref(self.ws_owner.ws), st), "experts")
         dist.all_to_all_single(back, self.ws_owner.pair_out(n), group=self.group)
         abi.check(lib.chimere_b200_moe_ep_finish(C.byref(self.home), back.data_ptr(), slot.data_ptr(), T, C.byref(self.ws_home.ws),
