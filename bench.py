@@ -86,21 +86,33 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_port_tokens_per_s(cfg, T, n_layers, threads=None):
-    """The oracle's layer forward on the host cores: tokens x layer-calls per second."""
+_CPU_LAYERS = {}
+
+
+def cpu_port_tokens_per_s(cfg, T, n_layers, threads=None, min_seconds=0.0):
+    """The oracle's layer forward on the host cores: tokens x layer-calls per second.  The sample is `n_layers` seeded
+    layers (built once per process) walked round-robin until at least `min_seconds` have passed (at least one pass)."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle
     from chimere_b200 import configs
     if threads:
         oracle.lib().orc_set_num_threads(threads)
-    layers = [configs.make_layer(cfg, device="cpu", seed=9000 + i) for i in range(n_layers)]
-    xs = [configs.make_input(cfg, T, seed=77 + i).numpy() for i in range(n_layers)]
-    oracle.moe_forward(layers[0], xs[0], taps=False)  # warm
+    key = (cfg.name, T, n_layers)
+    if key not in _CPU_LAYERS:
+        _CPU_LAYERS[key] = ([configs.make_layer(cfg, device="cpu", seed=9000 + i) for i in range(n_layers)],
+                            [configs.make_input(cfg, T, seed=77 + i).numpy() for i in range(n_layers)])
+        oracle.moe_forward(_CPU_LAYERS[key][0][0], _CPU_LAYERS[key][1][0], taps=False)  # warm
+    layers, xs = _CPU_LAYERS[key]
+    calls = 0
     t0 = time.perf_counter()
-    for w, x in zip(layers, xs):
-        oracle.moe_forward(w, x, taps=False)
-    dt = time.perf_counter() - t0
-    return T * n_layers / dt, oracle.lib().orc_num_threads(), dt
+    while True:
+        for w, x in zip(layers, xs):
+            oracle.moe_forward(w, x, taps=False)
+        calls += n_layers
+        dt = time.perf_counter() - t0
+        if dt >= min_seconds:
+            break
+    return T * calls / dt, oracle.lib().orc_num_threads(), dt
 
 
 def run_reference(args):
@@ -112,11 +124,14 @@ def run_reference(args):
     T = args.tokens
     sample_layers = 2
     vals = []
+    # one step = a bounded sample: the layers walked for about `per_step` seconds, sized so that the whole run stays
+    # within a few minutes whatever --steps says
+    per_step = min(2.0, 120.0 / max(1, args.steps + args.warmup))
     for _ in range(args.warmup):
-        cpu_port_tokens_per_s(cfg, T, 1)
+        cpu_port_tokens_per_s(cfg, T, sample_layers, min_seconds=per_step)
     t_total = 0.0
     for _ in range(args.steps):
-        v, threads, dt = cpu_port_tokens_per_s(cfg, T, sample_layers)
+        v, threads, dt = cpu_port_tokens_per_s(cfg, T, sample_layers, min_seconds=per_step)
         vals.append(v); t_total += dt
     v = statistics.median(vals)
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
@@ -124,7 +139,7 @@ def run_reference(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "int8 block dots, f32 accumulate", "data": "synthetic",
             "config": workload_config(cfg, T, sample_layers),
             "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
-                             "sample": f"T={T} tokens through {sample_layers} layers per step (CPU restatement in oracle/, OpenMP)"},
+                             "sample": f"T={T} tokens through {sample_layers} layers, repeated for {per_step:.1f} s per step (CPU restatement in oracle/, OpenMP)"},
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line))
@@ -506,9 +521,9 @@ def main():
 
     cpu = None
     if not args.no_cpu_baseline:
-        v, threads, dt = cpu_port_tokens_per_s(cfg, T, 2)
+        v, threads, dt = cpu_port_tokens_per_s(cfg, T, 2, min_seconds=10.0)
         cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
-               "sample": f"T={T} tokens through 2 layers ({dt:.2f} s), CPU restatement in oracle/ with OpenMP"}
+               "sample": f"T={T} tokens through 2 layers, repeated for {dt:.1f} s; CPU restatement in oracle/ with OpenMP"}
 
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": 1e3 * secs / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
