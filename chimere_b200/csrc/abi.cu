@@ -276,7 +276,6 @@ static GemvParams gate_up_params(const chimere_moe_layer* w, int T, chimere_moe_
     g.act = w->act;
     g.group_list = ws->group_list; g.perm = ws->perm;
     g.status = ws->status;
-    g.queue = ws->counters + kCtrQueue;
     g.ncols_routed = w->H; g.ncols_shared = w->H;
     g.nrows_routed = w->F; g.nrows_shared = w->F_s;
     g.type_routed = w->type_up; g.type_shared = w->type_sh_up;
@@ -296,7 +295,6 @@ static GemvParams down_params(const chimere_moe_layer* w, float* d_y, int T, chi
     g.act = w->act;
     g.group_list = ws->group_list; g.perm = ws->perm;
     g.status = ws->status;
-    g.queue = ws->counters + kCtrQueue;
     g.ncols_routed = w->F; g.ncols_shared = w->F_s;
     g.nrows_routed = w->H; g.nrows_shared = w->F_s > 0 ? w->H : 0;
     g.type_routed = w->type_down; g.type_shared = w->type_sh_down;

@@ -7,7 +7,7 @@ namespace chimere {
 
 // layout of the workspace's integer scratch ("counters"); everything returns to zero after a call
 constexpr int kCtrRouteAll = 0;    // token tiles whose top-k is done
-constexpr int kCtrQueue = 4;       // [4] work queues of the streaming kernels
+constexpr int kCtrSpare = 4;       // [4] unused, kept zero
 constexpr int kCtrRouteTile = 16;  // [ceil(max_T/8)] row tiles done per token tile
 // the combine counters follow at ws-specific offset (one per token and output row tile)
 
@@ -70,7 +70,6 @@ struct GemvParams {
     const float* in_soa_d; int64_t in_soa_d_stride;     // floats per row
     int8_t* out_soa_q; int64_t out_soa_q_stride;
     float* out_soa_d; int64_t out_soa_d_stride;
-    int32_t* queue;              // streaming kernels: [0..1] gate/up work queue, [2..3] down work queue (zero between calls)
     int32_t* status;
     int no_combine;              // down stage: only write the per-pair rows (the caller combines)
 };

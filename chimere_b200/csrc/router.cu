@@ -204,7 +204,6 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i, const int* s_i
         for (int j = 0; j < kMaxGroupTokens; ++j) ent[4 + j] = j < mm ? p.T * p.top_k + t0 + j : 0;
     }
     if (tid == 0) {
-        for (int i = 0; i < 4; ++i) p.counters[kCtrQueue + i] = 0;
         const int nsh_listed = p.list_mode == 2 ? 0 : nsh;
         p.group_list[0] = total_routed + nsh_listed;
         p.group_list[1] = total_routed;
