@@ -82,28 +82,33 @@ __device__ void topk_warp(const RouteParams& p, const float* logit_row, int t, i
     for (int i = 0; i < 8; ++i)
         if (lane + 32 * i >= E) pr[i] = -2.0f;  // never selected
 
+    // Selection on integer keys: probabilities are >= 0, so their bit patterns order like the values; key 0 = not
+    // available (beyond E, or already taken).  One warp-wide max and one warp-wide min per slot (redux.sync) instead
+    // of a shuffle butterfly: the largest value wins, equal values go to the lowest index, like a strict-greater
+    // scan from index 0.
+    uint32_t key[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) key[i] = (lane + 32 * i < E) ? __float_as_uint(pr[i]) + 1u : 0u;
     float wsum = 0.0f;
     float wsel = 0.0f;  // lane j keeps the weight of slot j
     int isel = 0;
     for (int j = 0; j < k; ++j) {
-        float bv = -1.0f;
-        int bi = 0;
+        uint32_t lm = key[0];
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-            if (pr[i] > bv) { bv = pr[i]; bi = lane + 32 * i; }
-        // warp arg-max; equal values go to the lower index, like a strict-greater scan from 0
+        for (int i = 1; i < 8; ++i) lm = max(lm, key[i]);
+        const uint32_t m = __reduce_max_sync(0xffffffffu, lm);
+        uint32_t cand = 0xffffffffu;   // lowest index in this lane that holds the maximum
 #pragma unroll
-        for (int m = 16; m > 0; m >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-        }
+        for (int i = 7; i >= 0; --i)
+            if (key[i] == m) cand = (uint32_t)(lane + 32 * i);
+        const int bi = (int)__reduce_min_sync(0xffffffffu, cand);
+        const float bv = __uint_as_float(m - 1u);
         wsum += bv;
         if (lane == j) { wsel = bv; isel = bi; }
         if ((bi & 31) == lane) {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-                if (i == (bi >> 5)) pr[i] = -1.0f;
+                if (i == (bi >> 5)) key[i] = 0u;
         }
     }
     if (lane < k) {
