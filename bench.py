@@ -15,7 +15,7 @@ events; `sweep` with the layer-level numbers for T = 1, 2, 4, 8; `e2e` through t
 (pinned host x in, y out, per layer call); `cpu_baseline`: the CPU oracle port timed on this host.
 
 --impl reference times the CPU port of the reference's path (the reference's own CPU code needs ik_llama's
-ggml, which is neither vendored nor pinned) with all host threads on a bounded sample.
+ggml, which is neither vendored nor pinned, so it cannot be built here) with all host threads on a bounded sample.
 """
 from __future__ import annotations
 
@@ -454,8 +454,8 @@ def main():
     rt_secs = time_steps(graph_of(route_all).replay, max(5, K), 3) / (max(5, K) * L)
     roof = {"bound": "hbm", "kernel": ("bulk_kernel<IQ3_S, gate_up>" if args.layout == "tiled" else "gate_up_kernel<IQ3_S>"), "achieved": gu_bytes / gu_secs / 1e9, "peak": hbm_peak,
             "unit": "GB/s", "frac": gu_bytes / gu_secs / 1e9 / hbm_peak, "peak_kind": peak_kind,
-            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at these sizes (ncu capture summarised
-            # in profiles/bulk_kernel_decode_T8.md; IQ3_S is streamed as 4-bit codes: +22 % over the ggml bytes)
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at these sizes, from an ncu capture of
+            # the two-layer case (one launch = one layer); IQ3_S is streamed as 4-bit codes: +22 % over the ggml bytes
             "traffic": (67008768 + 1450240) if (args.layout == "tiled" and T == 8) else None,
             "us_per_launch": gu_secs * 1e6, "algorithmic_bytes_per_launch": gu_bytes,
             "down_kernel": {"achieved": dn_bytes / dn_secs / 1e9, "frac": dn_bytes / dn_secs / 1e9 / hbm_peak,
