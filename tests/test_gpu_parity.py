@@ -293,6 +293,13 @@ def test_host_entry_and_rmsnorm():
     forward_moe_host(wd, sc, x, y)
     o = oracle.moe_forward(wh, x.numpy(), taps=False)
     check_rows(y.numpy(), o["y"])
+    # the same call again with new contents in the same host buffers
+    first = y.clone()
+    for rep in range(3):
+        x.copy_(configs.make_input(cfg, T, seed=50 + rep))
+        forward_moe_host(wd, sc, x, y)
+        check_rows(y.numpy(), oracle.moe_forward(wh, x.numpy(), taps=False)["y"])
+        assert not torch.equal(y, first)
     lib = abi.load()
     yd = y.cuda()
     out = torch.empty_like(yd)
