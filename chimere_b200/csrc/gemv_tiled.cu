@@ -564,7 +564,8 @@ template <int TYPE, int STAGE, bool DUAL>
 static cudaError_t launch_tile_t(const GemvParams& p, int max_entries, int wk, int wr, cudaStream_t stream) {
     const TileSmem ts = tile_smem(max(p.ncols_routed, p.ncols_shared), wr, wk, DUAL);
     if (ts.total > 200 * 1024) return cudaErrorInvalidValue;
-    cudaError_t e = cudaFuncSetAttribute(tile_kernel<TYPE, STAGE, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    static bool attr_done[64] = {};
+    cudaError_t e = max_smem_once(tile_kernel<TYPE, STAGE, DUAL>, 200 * 1024, attr_done);
     if (e != cudaSuccess) return e;
     const int rows = max(p.nrows_routed, p.nrows_shared);
     const int items = (rows / 32 + wr - 1) / wr;
@@ -608,7 +609,8 @@ static BulkPlan plan_bulk(const GemvParams& p, int stage, bool dual, int wk, int
 
 template <int TYPE, int STAGE, bool DUAL, int MT>
 static cudaError_t launch_bulk_m(const GemvParams& p, int max_entries, int wk, int wr, const BulkPlan& b, cudaStream_t stream) {
-    cudaError_t e = cudaFuncSetAttribute(bulk_kernel<TYPE, STAGE, DUAL, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    static bool attr_done[64] = {};
+    cudaError_t e = max_smem_once(bulk_kernel<TYPE, STAGE, DUAL, MT>, 226 * 1024, attr_done);
     if (e != cudaSuccess) return e;
     const int rows = max(p.nrows_routed, p.nrows_shared);
     const int items = (rows / 32 + wr - 1) / wr;

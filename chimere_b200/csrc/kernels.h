@@ -142,6 +142,20 @@ cudaError_t launch_down_tiled(const GemvParams& p, int max_entries, cudaStream_t
 cudaError_t launch_block_sumi_tiled(int type, const void* packed, const void* xq8, int32_t* sumi, int ncols, int nrows,
                                     cudaStream_t stream);
 
+// cudaFuncSetAttribute(max dynamic shared memory) once per kernel and device instead of on every launch.
+// `done` is a static array owned by the calling launcher (one per kernel instantiation).
+template <typename K>
+inline cudaError_t max_smem_once(K kernel, int bytes, bool (&done)[64]) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) done[dev] = true;
+    return e;
+}
+
 // Launch with programmatic stream serialization: the grid may start while the previous kernel of the stream is
 // still running; the kernels call griddep_wait() before they touch what that kernel writes.
 template <typename... KArgs, typename... Args>
