@@ -494,7 +494,8 @@ int chimere_b200_gemm_i8(const void* d_a, const void* d_b, int rows, int tokens,
 
 // ---------------------------------------------------------------- prefill path ----
 namespace {
-constexpr int kGemmMin = 32;          // pairs an expert needs to go to the GEMM
+constexpr int kGemmMin = 8;           // pairs an expert needs to go to the GEMM (a partly filled tile costs the read-back
+                                      // warps only its own columns; eight tokens on the GEMV kernels cost eight passes of dp4a)
 constexpr size_t kMmaTile = 4096 + 512;
 int n_tiles_max_for(const chimere_moe_layer* w, int T) {
     const int P = T * w->top_k;
@@ -507,20 +508,21 @@ PrefillPlan prefill_plan(const chimere_moe_layer* w) {
     const bool dual = w->act == CHIMERE_ACT_SWIGLU;
     P.rows_per_tile = dual ? 64 : 128;
     const size_t nbH = w->H / 32;
-    P.sgu = (int64_t)(w->F / P.rows_per_tile) * nbH * kMmaTile;
+    P.sgu = (int64_t)((w->F + P.rows_per_tile - 1) / P.rows_per_tile) * nbH * kMmaTile;   // a last, partly filled row tile is zero-padded
     P.sdown = (int64_t)(w->H / 128) * (w->F / 32) * kMmaTile;
     size_t o = 0;
     P.gu = o; o += up256((size_t)P.sgu * w->E);
     P.down = o; o += up256((size_t)P.sdown * w->E);
     if (w->F_s > 0) {
-        P.sh_gu = o; o += up256((size_t)(w->F_s / P.rows_per_tile) * nbH * kMmaTile);
+        P.sh_gu = o; o += up256((size_t)((w->F_s + P.rows_per_tile - 1) / P.rows_per_tile) * nbH * kMmaTile);
         P.sh_down = o; o += up256((size_t)(w->H / 128) * (w->F_s / 32) * kMmaTile);
     }
     P.total = o;
     return P;
 }
 int prefill_dims_ok(const chimere_moe_layer* w) {
-    const int rpt = w->act == CHIMERE_ACT_SWIGLU ? 64 : 128;
+    // gated experts: 64 gate rows and their 64 up rows share a tile; ungated ones may end in a partly filled tile
+    const int rpt = w->act == CHIMERE_ACT_SWIGLU ? 64 : 32;
     if (w->H % 128 || w->F % rpt || w->F_s % rpt) return 0;
     return 1;
 }
@@ -557,7 +559,8 @@ int chimere_b200_moe_pack_prefill(const chimere_moe_layer* raw, void* d_arena, s
     const bool dual = raw->act == CHIMERE_ACT_SWIGLU;
     uint8_t* base = (uint8_t*)d_arena;
     cudaError_t e = cudaSuccess;
-    if (dual) e = launch_pack_mma128_ggml(raw->type_gate, raw->gate_exps, base + P.gu, raw->E, raw->F, raw->H, 1, raw->stride_gate, P.sgu, stream);
+    if (raw->F % P.rows_per_tile || raw->F_s % P.rows_per_tile) e = cudaMemsetAsync(base, 0, P.total, stream);   // zero rows and scales behind the last real row
+    if (dual && e == cudaSuccess) e = launch_pack_mma128_ggml(raw->type_gate, raw->gate_exps, base + P.gu, raw->E, raw->F, raw->H, 1, raw->stride_gate, P.sgu, stream);
     if (e == cudaSuccess) e = launch_pack_mma128_ggml(raw->type_up, raw->up_exps, base + P.gu, raw->E, raw->F, raw->H, dual ? 2 : 0, raw->stride_up, P.sgu, stream);
     if (e == cudaSuccess) e = launch_pack_mma128_ggml(raw->type_down, raw->down_exps, base + P.down, raw->E, raw->H, raw->F, 0, raw->stride_down, P.sdown, stream);
     if (raw->F_s > 0) {
@@ -601,11 +604,15 @@ int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_m
     e = launch_gather_tiles(tiles, ws->perm, ws->x_q, ws->x_d, L.x_d_stride, base + A.bx, A.bx_stride, w->H, w->top_k, n_tiles_max, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     // the small experts: GEMV kernels on the rewritten work list, per-pair rows only
+    // (the shared expert is not on this list: the kernels are sized for the routed matrices alone)
     const int max_entries = max_entries_for(w, T);
-    e = launch_gate_up_tiled(gate_up_params(w, T, ws, L), max_entries, stream);
+    GemvParams gu = gate_up_params(w, T, ws, L);
+    gu.nrows_shared = 0; gu.ncols_shared = 0; gu.sh_a = nullptr; gu.sh_b = nullptr;
+    e = launch_gate_up_tiled(gu, max_entries, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     GemvParams dn = down_params(w, d_y, T, ws, L);
     dn.no_combine = 1;
+    dn.nrows_shared = 0; dn.ncols_shared = 0; dn.sh_a = nullptr; dn.sh_b = nullptr;
     e = launch_down_tiled(dn, max_entries, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     // the large experts and the shared expert: grouped GEMMs
@@ -615,7 +622,9 @@ int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_m
     g.a_exps = (const uint8_t*)pw->gu_exps; g.stride_a = pw->stride_gu; g.sh_a = (const uint8_t*)pw->sh_gu;
     g.b_tiles = base + A.bx; g.b_tile_stride = A.bx_stride;
     g.out_tiles = base + A.b2; g.out_tile_stride = A.b2_stride;
-    g.row_tiles_routed = w->F / pw->rows_per_gu_tile; g.row_tiles_shared = w->F_s / pw->rows_per_gu_tile;
+    g.row_tiles_routed = (w->F + pw->rows_per_gu_tile - 1) / pw->rows_per_gu_tile;
+    g.row_tiles_shared = (w->F_s + pw->rows_per_gu_tile - 1) / pw->rows_per_gu_tile;
+    g.nblk_routed = w->F / 32; g.nblk_shared = w->F_s / 32;
     g.row_tiles_max = g.row_tiles_routed > g.row_tiles_shared ? g.row_tiles_routed : g.row_tiles_shared;
     g.ncols_in = w->H; g.ncols_in_shared = w->H;
     (void)dual;

@@ -303,6 +303,7 @@ struct GateUpPolicy {
         if (!ok || (dual && q >= 2)) return;
         // this warp's 32 rows form Q8_1 block `blk` of the intermediate; it quantises its half of the token columns
         const int blk = dual ? w.aux1 * 2 + q : w.aux1 * 4 + q;
+        if (blk >= (w.aux2 ? p.nblk_shared : p.nblk_routed)) return;   // rows of zero padding behind the last real row
         uint8_t* dst = p.out_tiles + (size_t)w.aux0 * p.out_tile_stride + (size_t)blk * kG_TileBytes;
         const int khalf = lane >> 4, kin = lane & 15;
         const int c_end = min(w.n_valid, part * kG_EpiCols + kG_EpiCols);

@@ -118,6 +118,7 @@ struct PrefillGemmParams {
     uint8_t* out_tiles; int64_t out_tile_stride;     // gate/up: token tiles of the down GEMM (output)
     float* pair_out;                                 // down: per-pair rows [pairs][H]
     int row_tiles_routed, row_tiles_shared, row_tiles_max;
+    int nblk_routed, nblk_shared;    // gate/up: 32-row blocks of the intermediate (F / 32, F_s / 32); blocks beyond are padding
     int ncols_in, ncols_in_shared;   // K of the routed / shared matrices
     int act, T, top_k, H;
     int32_t* status;

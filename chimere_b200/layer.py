@@ -137,7 +137,7 @@ class MoeWeightsPrefill:
         rs = raw.as_struct()
         nbytes = lib.chimere_b200_moe_pack_prefill_bytes(C.byref(rs))
         if nbytes == 0:
-            raise RuntimeError("chimere_b200_moe_pack_prefill_bytes rejected the layer (needs H % 128 == 0, F % 64 (128 without gate) == 0)")
+            raise RuntimeError("chimere_b200_moe_pack_prefill_bytes rejected the layer (needs H % 128 == 0 and, for gated experts, F % 64 == 0)")
         self.arena = torch.zeros(nbytes, dtype=torch.uint8, device=raw.router_weight.device)
         self.struct = abi.PrefillWeights()
         stream = torch.cuda.current_stream(self.arena.device).cuda_stream

@@ -241,7 +241,7 @@ int chimere_b200_gemm_i8(const void* d_a, const void* d_b, int rows, int tokens,
 
 /* ------------------------------------------------------------ prefill-size batches -------- */
 /* For many tokens per call the expert products run as grouped block-scaled int8 GEMMs on the tensor cores
- * (the primitive above): experts with at least 32 routed tokens and the shared expert go to the GEMM, the rest
+ * (the primitive above): experts with at least 8 routed tokens and the shared expert go to the GEMM, the rest
  * stay on the GEMV kernels.  The GEMM needs a second weight copy in its own layout (int8 values + f32 block
  * scales, gate and up rows interleaved per 64 rows): about 1.06x the Q8_0 bytes, 2x Q4_0, 2.3x IQ3_S. */
 typedef struct chimere_moe_prefill_weights {
@@ -253,7 +253,8 @@ typedef struct chimere_moe_prefill_weights {
 } chimere_moe_prefill_weights;
 
 size_t chimere_b200_moe_pack_prefill_bytes(const chimere_moe_layer* raw);
-/* raw: layout GGML.  F and F_s multiples of 128 (64 with a gate), H a multiple of 128. */
+/* raw: layout GGML.  H a multiple of 128; with a gate matrix F and F_s multiples of 64; without one any
+ * multiple of 32 (a last, partly filled 128-row tile is padded with zero rows). */
 int chimere_b200_moe_pack_prefill(const chimere_moe_layer* raw, void* d_arena, size_t bytes,
                                   chimere_moe_prefill_weights* out, cudaStream_t stream);
 /* Extra scratch the prefill path needs for up to max_T tokens; pass it with ws->prefill_arena / prefill_bytes. */

@@ -66,6 +66,7 @@ PREFILL_CASES = [
     (configs.scaled(configs.QWEN_Q4_0, E=8), 200),
     (configs.scaled(configs.QWEN_IQ3S, E=8), 130),
     (configs.scaled(configs.NEMOTRON_Q4_0, E=8, F=1792, F_s=3712 - 128), 96),   # no gate matrix: 128-row tiles
+    (configs.scaled(configs.NEMOTRON_Q4_0, E=8, name="nemotron-full-widths"), 160),  # F = 1856 = 14.5 row tiles: the last one is zero-padded
 ]
 
 
