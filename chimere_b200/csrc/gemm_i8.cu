@@ -88,8 +88,8 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) { uint64_t d; a
 struct GemmShared {
     uint64_t full[kG_Stages];        // stage bytes have landed
     uint64_t empty[kG_Stages];       // stage read by the MMAs and by the epilogue (scales)
-    uint64_t tfull[4];               // accumulator of a block is complete
-    uint64_t tempty[4];              // accumulator has been read back
+    uint64_t tfull[2];               // the two accumulators of a block pair are complete
+    uint64_t tempty[2];              // ... have been read back
     uint32_t tmem_base;
     int failed;
 };
@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
 
     if (tid == 0) {
         for (int i = 0; i < kG_Stages; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1 + kG_EpiWarps); }
-        for (int i = 0; i < 4; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], kG_EpiWarps); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], kG_EpiWarps); }
         sh.failed = 0;
         mbar_fence_init();
     }
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            uint32_t sg = 0, bg = 0;   // stages / blocks so far, over all tiles
+            uint32_t sg = 0, bg = 0;   // stages / block pairs so far, over all tiles
             bool ok = true;
             for (int idx = blockIdx.x; ok; idx += stride) {
                 GemmWork item;
@@ -171,12 +171,15 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
                     const int nb = min(kG_BlocksPerStage, item.nblocks - s * kG_BlocksPerStage);
                     const uint32_t sa = smem_u32(smem + (size_t)st * kG_StageBytes);
                     const uint32_t sb = sa + kG_BlocksPerStage * kG_TileBytes;
-                    for (int j = 0; j < nb; ++j, ++bg) {
-                        const int buf = bg & 3, tph = (bg >> 2) & 1;
-                        if (!mbar_wait(&sh.tempty[buf], tph ^ 1)) { atomicOr(p.status, kStatusWaitTimeout); sh.failed = 1; ok = false; break; }
+                    // two blocks per hand-over: accumulator pair bg & 1 = TMEM buffers 2 * (bg & 1) and + 1
+                    for (int j = 0; j < nb; j += 2, ++bg) {
+                        const int pr = bg & 1, tph = (bg >> 1) & 1;
+                        if (!mbar_wait(&sh.tempty[pr], tph ^ 1)) { atomicOr(p.status, kStatusWaitTimeout); sh.failed = 1; ok = false; break; }
                         tc_fence_after();
-                        tc_mma_i8(tmem + buf * 128, smem_desc_kmajor(sa + j * kG_TileBytes), smem_desc_kmajor(sb + j * kG_TileBytes));
-                        tc_commit(&sh.tfull[buf]);       // accumulator ready when this MMA has finished
+                        tc_mma_i8(tmem + (2 * pr) * 128, smem_desc_kmajor(sa + j * kG_TileBytes), smem_desc_kmajor(sb + j * kG_TileBytes));
+                        if (j + 1 < nb)
+                            tc_mma_i8(tmem + (2 * pr + 1) * 128, smem_desc_kmajor(sa + (j + 1) * kG_TileBytes), smem_desc_kmajor(sb + (j + 1) * kG_TileBytes));
+                        tc_commit(&sh.tfull[pr]);        // both accumulators ready when these MMAs have finished
                     }
                     tc_commit(&sh.empty[st]);            // ... and the stage's int8 data is no longer needed
                 }
@@ -188,7 +191,7 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
         const int part = (warp - 2) >> 2;            // which 32 columns
         const int row = q * 32 + lane;
         const uint64_t neg_magic2 = pack2(__float_as_uint(-12582912.0f), __float_as_uint(-12582912.0f));
-        uint32_t sg = 0, bg = 0;
+        uint32_t sg = 0, bg = 0;   // stages / block pairs so far
         bool ok = true;
         for (int idx = blockIdx.x;; idx += stride) {
             GemmWork item;
@@ -200,34 +203,44 @@ __global__ void __launch_bounds__(kG_Threads, 1) gemm_i8_kernel(const Params p) 
             uint64_t acc2[kG_EpiCols / 2];
 #pragma unroll
             for (int i = 0; i < kG_EpiCols / 2; ++i) acc2[i] = 0ull;
-            for (int blk = 0; blk < nblocks && ok; ++blk, ++bg) {
-                const int s = blk / kG_BlocksPerStage, j = blk - s * kG_BlocksPerStage;
+            // blocks come in pairs (never across a ring stage): one wait and one arrival per pair
+            for (int blk = 0; blk < nblocks && ok; ++bg) {
+                const int s = blk / kG_BlocksPerStage, j0 = blk - s * kG_BlocksPerStage;
                 const int st = (sg + s) % kG_Stages;
-                const int buf = bg & 3, tph = (bg >> 2) & 1;
-                if (!mbar_wait(&sh.tfull[buf], tph)) { atomicOr(p.status, kStatusWaitTimeout); sh.failed = 1; ok = false; break; }
+                const int nb_stage = min(kG_BlocksPerStage, nblocks - s * kG_BlocksPerStage);
+                const int npair = min(2, nb_stage - j0);
+                const int pr = bg & 1, tph = (bg >> 1) & 1;
+                if (!mbar_wait(&sh.tfull[pr], tph)) { atomicOr(p.status, kStatusWaitTimeout); sh.failed = 1; ok = false; break; }
                 tc_fence_after();
                 if (ncols_here > 0) {
                     const uint8_t* stage = smem + (size_t)st * kG_StageBytes;
-                    const uint32_t sab = *reinterpret_cast<const uint32_t*>(stage + j * kG_TileBytes + 4096 + row * 4);
-                    const uint64_t sa2 = pack2(sab, sab);
-                    const uint4* sbv = reinterpret_cast<const uint4*>(stage + (kG_BlocksPerStage + j) * kG_TileBytes + 4096) + part * (kG_EpiCols / 4);
-                    int v[32];
-                    tc_ld32(tmem + ((uint32_t)(q * 32) << 16) + buf * 128 + part * kG_EpiCols, v);
-                    // value + 0x4B400000 read as a float is 12582912 + value (see i2f_exact); the rest runs two columns at a time
 #pragma unroll
-                    for (int g = 0; g < kG_EpiCols / 4; ++g) {
-                        const uint4 sb4 = sbv[g];
-                        const uint64_t f01 = add2(pack2((uint32_t)(v[4 * g + 0] + 0x4B400000), (uint32_t)(v[4 * g + 1] + 0x4B400000)), neg_magic2);
-                        const uint64_t f23 = add2(pack2((uint32_t)(v[4 * g + 2] + 0x4B400000), (uint32_t)(v[4 * g + 3] + 0x4B400000)), neg_magic2);
-                        acc2[2 * g + 0] = fma2(f01, mul2(pack2(sb4.x, sb4.y), sa2), acc2[2 * g + 0]);
-                        acc2[2 * g + 1] = fma2(f23, mul2(pack2(sb4.z, sb4.w), sa2), acc2[2 * g + 1]);
+                    for (int h = 0; h < 2; ++h) {
+                        if (h < npair) {
+                            const int j = j0 + h;
+                            const uint32_t sab = *reinterpret_cast<const uint32_t*>(stage + j * kG_TileBytes + 4096 + row * 4);
+                            const uint64_t sa2 = pack2(sab, sab);
+                            const uint4* sbv = reinterpret_cast<const uint4*>(stage + (kG_BlocksPerStage + j) * kG_TileBytes + 4096) + part * (kG_EpiCols / 4);
+                            int v[32];
+                            tc_ld32(tmem + ((uint32_t)(q * 32) << 16) + (2 * pr + h) * 128 + part * kG_EpiCols, v);
+                            // value + 0x4B400000 read as a float is 12582912 + value (see i2f_exact); the rest runs two columns at a time
+#pragma unroll
+                            for (int g = 0; g < kG_EpiCols / 4; ++g) {
+                                const uint4 sb4 = sbv[g];
+                                const uint64_t f01 = add2(pack2((uint32_t)(v[4 * g + 0] + 0x4B400000), (uint32_t)(v[4 * g + 1] + 0x4B400000)), neg_magic2);
+                                const uint64_t f23 = add2(pack2((uint32_t)(v[4 * g + 2] + 0x4B400000), (uint32_t)(v[4 * g + 3] + 0x4B400000)), neg_magic2);
+                                acc2[2 * g + 0] = fma2(f01, mul2(pack2(sb4.x, sb4.y), sa2), acc2[2 * g + 0]);
+                                acc2[2 * g + 1] = fma2(f23, mul2(pack2(sb4.z, sb4.w), sa2), acc2[2 * g + 1]);
+                            }
+                        }
                     }
                 }
                 tc_fence_before();
                 __syncwarp();
+                blk += npair;
                 if (lane == 0) {
-                    mbar_arrive_cta(&sh.tempty[buf]);
-                    if (j == kG_BlocksPerStage - 1 || blk == nblocks - 1) mbar_arrive_cta(&sh.empty[st]);   // scales of the stage read
+                    mbar_arrive_cta(&sh.tempty[pr]);
+                    if (j0 + npair == nb_stage) mbar_arrive_cta(&sh.empty[st]);   // scales of the stage read
                 }
             }
             sg += (uint32_t)((nblocks + kG_BlocksPerStage - 1) / kG_BlocksPerStage);
