@@ -27,7 +27,7 @@ namespace chimere {
 
 constexpr int kG_TileBytes = 4096 + 512;     // one (128 x 32) int8 block + 128 f32 scales
 constexpr int kG_BlocksPerStage = 4;
-constexpr int kG_Stages = 3;
+constexpr int kG_Stages = 4;
 constexpr int kG_StageBytes = 2 * kG_BlocksPerStage * kG_TileBytes;   // A blocks then B blocks
 constexpr int kG_EpiWarps = 16;                // four per TMEM lane quarter: each takes 32 of the 128 token columns
 constexpr int kG_EpiCols = 128 / (kG_EpiWarps / 4);
