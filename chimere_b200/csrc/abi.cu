@@ -202,7 +202,7 @@ int chimere_b200_moe_shared_expert(const chimere_moe_layer* w, int T, chimere_mo
     if (w->layout != CHIMERE_LAYOUT_TILED32) return -2;
     if (w->F_s <= 0) return 0;
     const Layout L = make_layout(w, ws->max_T);
-    const int max_entries = max_entries_for(w, T);
+    const int max_entries = (T + kSharedGroupTokens - 1) / kSharedGroupTokens;   // the home rank's list holds nothing else
     cudaError_t e = launch_gate_up_tiled(gate_up_params(w, T, ws, L), max_entries, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     GemvParams g = down_params(w, nullptr, T, ws, L);
@@ -232,11 +232,13 @@ static int run_experts(const chimere_moe_layer* w_local, int n_rows, const void*
     if (d_packed) {
         gu.in_soa_q = (const int8_t*)d_packed; gu.in_soa_q_stride = row_bytes;
         gu.in_soa_d = (const float*)((const uint8_t*)d_packed + w_local->H); gu.in_soa_d_stride = row_bytes / 4;
+        gu.few_tokens = 1;   // a fixed-size exchange: most of the n_rows slots carry no pair
     }
     e = launch_gate_up_tiled(gu, max_entries, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     GemvParams g = down_params(w_local, nullptr, n_rows, ws, L);
     g.no_combine = 1;
+    g.few_tokens = d_packed ? 1 : 0;
     return cuda_rc(launch_down_tiled(g, max_entries, stream));
 }
 

@@ -591,7 +591,7 @@ static BulkPlan plan_bulk(const GemvParams& p, int stage, bool dual, int wk, int
     const int max_ctas = min(8, 1536 / threads);
     // decode-size batches: as many CTAs per SM as fit one token per pass, then as many tokens as still fit;
     // larger batches: at least four tokens per pass if that fits at all
-    const int mt_floor = (p.T > 16) ? 4 : 1;
+    const int mt_floor = (p.T > 16 && !p.few_tokens) ? 4 : 1;
     for (int floor_mt = mt_floor; floor_mt >= 1 && !b.ok; floor_mt = (floor_mt == 1 ? 0 : 1)) {
         int ctas = 0;
         for (int c = max_ctas; c >= 1; --c)

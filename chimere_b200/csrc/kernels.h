@@ -72,6 +72,8 @@ struct GemvParams {
     float* out_soa_d; int64_t out_soa_d_stride;
     int32_t* status;
     int no_combine;              // down stage: only write the per-pair rows (the caller combines)
+    int few_tokens;              // T counts row slots that are mostly empty (fixed-size expert-parallel exchange): size the
+                                 // kernels as for a decode batch whatever T says
 };
 
 cudaError_t launch_route(const RouteParams& p, cudaStream_t stream);
