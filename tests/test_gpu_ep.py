@@ -1,4 +1,5 @@
-"""Expert parallelism on real GPUs (needs at least two): launches tests/ep_check.py under torchrun."""
+"""Expert parallelism on real GPUs: launches tests/ep_check.py under torchrun (two or four ranks where there are that
+many GPUs, and always once with a single rank, which still goes through pack, exchange, owner-side kernels and combine)."""
 import os
 import subprocess
 import sys
@@ -17,5 +18,12 @@ def test_expert_parallel_matches_single_gpu():
     world = 2 if n < 4 else 4
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", "29731", os.path.join(ROOT, "tests", "ep_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_expert_parallel_single_rank_pipeline():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=1", "--master-addr", "127.0.0.1",
+           "--master-port", "29732", os.path.join(ROOT, "tests", "ep_check.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
