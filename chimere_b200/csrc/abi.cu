@@ -56,7 +56,7 @@ struct Layout {
 
 int max_entries_for(const chimere_moe_layer* w, int T) {
     const int P = T * w->top_k;
-    return (w->E < P ? w->E : P) + P / kMaxGroupTokens + (w->F_s > 0 ? (T + kSharedGroupTokens - 1) / kSharedGroupTokens : 0);
+    return (w->E < P ? w->E : P) + P / kMaxGroupTokens + (w->F_s > 0 ? (T + shared_group_tokens(T) - 1) / shared_group_tokens(T) : 0);
 }
 
 Layout make_layout(const chimere_moe_layer* w, int T) {
@@ -64,7 +64,8 @@ Layout make_layout(const chimere_moe_layer* w, int T) {
     const int k = w->top_k, H = w->H, E = w->E;
     const int Fmax = w->F > w->F_s ? w->F : w->F_s;
     const size_t pairs = (size_t)T * k + (w->F_s > 0 ? T : 0);
-    L.max_entries = max_entries_for(w, T);
+    L.max_entries = max_entries_for(w, T);   // T = the workspace's capacity; a smaller batch may need a few more entries
+    if (T > 8 && max_entries_for(w, 8) > L.max_entries) L.max_entries = max_entries_for(w, 8);   // (one-token shared entries up to T = 8)
     L.tile_rows = down_tile_rows(w->type_down, w->F, w->type_sh_down, w->F_s);
     L.n_row_tiles = (H + L.tile_rows - 1) / L.tile_rows;
     L.n_row_tiles_tiled = (H + 31) / 32;   // counters for the finest row tiling any batch size may choose
@@ -202,7 +203,7 @@ int chimere_b200_moe_shared_expert(const chimere_moe_layer* w, int T, chimere_mo
     if (w->layout != CHIMERE_LAYOUT_TILED32) return -2;
     if (w->F_s <= 0) return 0;
     const Layout L = make_layout(w, ws->max_T);
-    const int max_entries = (T + kSharedGroupTokens - 1) / kSharedGroupTokens;   // the home rank's list holds nothing else
+    const int max_entries = (T + shared_group_tokens(T) - 1) / shared_group_tokens(T);   // the home rank's list holds nothing else
     cudaError_t e = launch_gate_up_tiled(gate_up_params(w, T, ws, L), max_entries, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     GemvParams g = down_params(w, nullptr, T, ws, L);

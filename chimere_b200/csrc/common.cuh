@@ -15,6 +15,9 @@ namespace chimere {
 constexpr int kQ81Bytes = 36;
 constexpr int kMaxGroupTokens = 8;   // tokens one GEMV work entry carries
 constexpr int kSharedGroupTokens = 2;  // ... for the shared expert (every token uses it): smaller entries balance the grid
+// Decode-size batches give every token its own shared-expert entry: the kernels stage one token per pass there, and
+// a second pass in the same CTA is a longer chain than a second CTA reading the shared matrices from L2.
+__host__ __device__ inline int shared_group_tokens(int T) { return T <= 8 ? 1 : kSharedGroupTokens; }
 constexpr int kMaxTopK = 8;
 constexpr int kMaxExperts = 256;
 

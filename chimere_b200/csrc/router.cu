@@ -200,11 +200,12 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i, const int* s_i
     int total_routed = 0;
     for (int w = 0; w < 8; ++w) total_routed += scan[8 + w];
     // shared-expert entries first (all tokens, identity order), then the routed ones
-    const int nsh = p.has_shared ? (p.T + kSharedGroupTokens - 1) / kSharedGroupTokens : 0;
+    const int sgt = shared_group_tokens(p.T);
+    const int nsh = p.has_shared ? (p.T + sgt - 1) / sgt : 0;
     if (p.list_mode != 0) total_routed = 0;
     for (int i = tid; i < (p.list_mode == 2 ? 0 : nsh); i += 256) {
         int* ent = p.group_list + kListHeader + kListEntry * i;
-        const int t0 = i * kSharedGroupTokens, mm = min(kSharedGroupTokens, p.T - t0);
+        const int t0 = i * sgt, mm = min(sgt, p.T - t0);
         ent[0] = -1; ent[1] = t0; ent[2] = mm; ent[3] = 0;
         for (int j = 0; j < kMaxGroupTokens; ++j) ent[4 + j] = j < mm ? p.T * p.top_k + t0 + j : 0;
     }
