@@ -7,10 +7,13 @@
 // an f32 scale plane and read as warp-wide broadcasts.  The eight warps of a CTA are WR row tiles x WK
 // slices of K; slices meet in shared memory and are added in a fixed order.
 //
-// Measurements on B200 showed this path to be bound by the latency of the dependent look-ups every work
-// item starts with (work list -> pair ids -> activations -> weights), not by bandwidth or issue slots, and a
-// persistent producer/consumer variant with a shared-memory ring did not change that; so the kernels are
-// kept small (few registers, little shared memory) and many CTAs are resident per SM to overlap the chains.
+// Two kernels share this core.  bulk_kernel (the one that normally runs) brings every warp's contiguous piece of the
+// tiled layout into shared memory with one cp.async.bulk per matrix and reads the units back from there;
+// tile_kernel loads them straight into registers (ld.global.nc, 128 bits per lane) and is the fallback for shapes
+// whose row tile does not fit shared memory.  Measurements on B200 showed this path to be bound by the latency of
+// the chain every work item starts with (work entry -> weights and activations -> dot products -> reduction) and by
+// the tails of the CTA waves, not by bandwidth; a persistent variant with per-warp rings was slower than letting the
+// hardware start fresh CTAs, so the kernels stay one work item per CTA with several CTAs resident per SM.
 //
 //   STAGE_GATE_UP : act(gate . x, up . x) -> Q8_1 blocks of the intermediates
 //                   (replaces moe_ffn.rs:1206-1323 and :1597-1700 of the reference)
