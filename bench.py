@@ -456,7 +456,7 @@ def main():
             "unit": "GB/s", "frac": gu_bytes / gu_secs / 1e9 / hbm_peak, "peak_kind": peak_kind,
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at these sizes, from an ncu capture of
             # the two-layer case (one launch = one layer); IQ3_S is streamed as 4-bit codes: +22 % over the ggml bytes
-            "traffic": (67008768 + 1450240) if (args.layout == "tiled" and T == 8) else None,
+            "traffic": (67008256 + 735488) if (args.layout == "tiled" and T == 8) else None,
             "us_per_launch": gu_secs * 1e6, "algorithmic_bytes_per_launch": gu_bytes,
             "down_kernel": {"achieved": dn_bytes / dn_secs / 1e9, "frac": dn_bytes / dn_secs / 1e9 / hbm_peak,
                             "us_per_launch": dn_secs * 1e6, "algorithmic_bytes_per_launch": dn_bytes},
