@@ -91,6 +91,9 @@ PROTOTYPES = {
     "chimere_mmvq_iq3s": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
     "chimere_mmvq_q8_0": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
     "chimere_mmvq_q4_0": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "chimere_mmvq_iq3s_f32": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P]),
+    "chimere_mmvq_q8_0_f32": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P]),
+    "chimere_mmvq_q4_0_f32": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P]),
     "chimere_mmvq_iq3s_batched": (None, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int, _P]),
     "chimere_mmvq_q4_0_batched": (None, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int, _P]),
     "chimere_mmvq_q8_0_batched": (None, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int, _P]),
@@ -118,7 +121,8 @@ def load() -> C.CDLL:
 
 
 ERRORS = {-1: "null pointer", -2: "bad dimension", -3: "unsupported weight type", -4: "workspace too small",
-          -5: "misaligned arena", -6: "entry not available", -7: "larger than the built-in scratch"}
+          -5: "misaligned arena", -6: "entry not available", -7: "larger than the built-in scratch",
+          -8: "first call on this device was made during stream capture"}
 
 
 def check(rc: int, what: str) -> None:

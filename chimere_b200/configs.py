@@ -35,6 +35,8 @@ class LayerConfig:
     shared_gate: bool = True      # shared expert scaled by sigmoid(x . w_sg)
     zipf_bias: bool = False       # per-expert logit bias 2*log(rank^-1.1) over a seeded permutation
     seed: int = 0
+    type_sh_gate_up: Optional[int] = None   # shared expert's weight types when they differ from the routed experts'
+    type_sh_down: Optional[int] = None      # (the production files quantize the shared expert differently, moe_ffn.rs:1618-1705)
 
 
 QWEN_Q4_0 = LayerConfig("qwen35-moe-q4_0", 2048, 256, 512, 512, 8, Q4_0, Q4_0, seed=0)
@@ -83,11 +85,13 @@ def make_layer(cfg: LayerConfig, device="cpu", seed: Optional[int] = None) -> Mo
     down = _quant_matrix_stack(cfg.type_down, cfg.E, cfg.H, cfg.F, gen, dev)
     kw = {}
     if cfg.F_s > 0:
-        kw["shexp_gate_raw"] = _quant_matrix_stack(cfg.type_gate_up, 1, cfg.F_s, cfg.H, gen, dev)[0] if dual else None
-        kw["shexp_up_raw"] = _quant_matrix_stack(cfg.type_gate_up, 1, cfg.F_s, cfg.H, gen, dev)[0]
-        kw["shexp_down_raw"] = _quant_matrix_stack(cfg.type_down, 1, cfg.H, cfg.F_s, gen, dev)[0]
-        kw["type_sh_gate"] = cfg.type_gate_up if dual else 0
-        kw["type_sh_up"], kw["type_sh_down"] = cfg.type_gate_up, cfg.type_down
+        t_gu = cfg.type_gate_up if cfg.type_sh_gate_up is None else cfg.type_sh_gate_up
+        t_dn = cfg.type_down if cfg.type_sh_down is None else cfg.type_sh_down
+        kw["shexp_gate_raw"] = _quant_matrix_stack(t_gu, 1, cfg.F_s, cfg.H, gen, dev)[0] if dual else None
+        kw["shexp_up_raw"] = _quant_matrix_stack(t_gu, 1, cfg.F_s, cfg.H, gen, dev)[0]
+        kw["shexp_down_raw"] = _quant_matrix_stack(t_dn, 1, cfg.H, cfg.F_s, gen, dev)[0]
+        kw["type_sh_gate"] = t_gu if dual else 0
+        kw["type_sh_up"], kw["type_sh_down"] = t_gu, t_dn
         if cfg.shared_gate:
             kw["shexp_gate_proj"] = (torch.randn(cfg.H, generator=gen, device=dev) * 0.02).contiguous()
     if cfg.zipf_bias:
@@ -114,7 +118,9 @@ def algorithmic_bytes(cfg: LayerConfig, T: int, distinct_experts: int) -> int:
     b_exp = (n_mat - 1) * b_gu + b_dn
     b_sh = 0
     if cfg.F_s > 0:
-        b_sh = (n_mat - 1) * cfg.F_s * formats.row_bytes(cfg.type_gate_up, cfg.H) + cfg.H * formats.row_bytes(cfg.type_down, cfg.F_s)
+        t_gu = cfg.type_gate_up if cfg.type_sh_gate_up is None else cfg.type_sh_gate_up
+        t_dn = cfg.type_down if cfg.type_sh_down is None else cfg.type_sh_down
+        b_sh = (n_mat - 1) * cfg.F_s * formats.row_bytes(t_gu, cfg.H) + cfg.H * formats.row_bytes(t_dn, cfg.F_s)
     return distinct_experts * b_exp + b_sh + 4 * cfg.E * cfg.H + (4 * cfg.H if cfg.shared_gate else 0) + 8 * T * cfg.H
 
 

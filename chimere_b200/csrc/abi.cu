@@ -669,6 +669,25 @@ void chimere_mmvq_q8_0(const void* weights, const void* input_q8, float* output,
 void chimere_mmvq_q4_0(const void* weights, const void* input_q8, float* output, int ncols, int nrows, int, cudaStream_t stream) {
     launch_mmvq(CHIMERE_TYPE_Q4_0, weights, input_q8, output, nullptr, ncols, nrows, 0, 0, 1, stream);
 }
+// Fused quantize + GEMV from an f32 input row (ffi/ggml_cuda_gemv.cu:322-352): Q8_1 of the input into the caller's
+// scratch (pad(ncols, 512) / 32 * 36 bytes, blocks past ncols zero), then the GEMV above on that scratch.
+static void mmvq_f32(int wtype, const void* weights, const float* input_f32, float* output, int ncols, int nrows, int ncols_padded,
+                     void* q8_scratch, cudaStream_t stream) {
+    launch_quantize_q8_1(input_f32, q8_scratch, ncols, ncols_padded, 1, stream);
+    launch_mmvq(wtype, weights, q8_scratch, output, nullptr, ncols, nrows, 0, 0, 1, stream);
+}
+void chimere_mmvq_iq3s_f32(const void* weights, const float* input_f32, float* output, int ncols, int nrows, int ncols_padded,
+                           void* q8_scratch, cudaStream_t stream) {
+    mmvq_f32(CHIMERE_TYPE_IQ3_S, weights, input_f32, output, ncols, nrows, ncols_padded, q8_scratch, stream);
+}
+void chimere_mmvq_q8_0_f32(const void* weights, const float* input_f32, float* output, int ncols, int nrows, int ncols_padded,
+                           void* q8_scratch, cudaStream_t stream) {
+    mmvq_f32(CHIMERE_TYPE_Q8_0, weights, input_f32, output, ncols, nrows, ncols_padded, q8_scratch, stream);
+}
+void chimere_mmvq_q4_0_f32(const void* weights, const float* input_f32, float* output, int ncols, int nrows, int ncols_padded,
+                           void* q8_scratch, cudaStream_t stream) {
+    mmvq_f32(CHIMERE_TYPE_Q4_0, weights, input_f32, output, ncols, nrows, ncols_padded, q8_scratch, stream);
+}
 void chimere_mmvq_iq3s_batched(const void* all_weights, const void* input_q8, float* output, const int* expert_ids, int ncols,
                                int nrows, int, int64_t expert_stride, int64_t input_stride, int top_k, cudaStream_t stream) {
     launch_mmvq(CHIMERE_TYPE_IQ3_S, all_weights, input_q8, output, expert_ids, ncols, nrows, expert_stride, input_stride, top_k, stream);

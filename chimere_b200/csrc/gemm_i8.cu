@@ -401,12 +401,15 @@ cudaError_t launch_pack_mma128(const int8_t* q, const float* scales, uint8_t* ou
     return cudaGetLastError();
 }
 
-// persistent CTAs: one per SM, or fewer when there are fewer tiles
+// persistent CTAs: one per SM of the current device, or fewer when there are fewer tiles
 static int gemm_grid(int n_items) {
-    static int n_sm = 0;
+    static int n_sm_of[64] = {};
+    int dev = 0, n_sm = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+    if (dev >= 0) n_sm = n_sm_of[dev];
     if (!n_sm) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+        if (dev < 0 || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+        if (dev >= 0) n_sm_of[dev] = n_sm;
     }
     return n_items < n_sm ? n_items : n_sm;
 }
@@ -418,7 +421,8 @@ cudaError_t launch_gemm_i8_f32(const GemmParams& p_in, int n_items, cudaStream_t
     GemmParams p = p_in;
     p.n_items = n_items;
     const size_t smem = kG_RingBytes + 1024;
-    cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<PlainPolicy, GemmParams>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static bool attr_done[64] = {};
+    cudaError_t e = max_smem_once(gemm_i8_kernel<PlainPolicy, GemmParams>, (int)smem, attr_done);
     if (e != cudaSuccess) return e;
     gemm_i8_kernel<PlainPolicy, GemmParams><<<gemm_grid(n_items), kG_Threads, smem, stream>>>(p);
     return cudaGetLastError();
@@ -430,12 +434,14 @@ cudaError_t launch_prefill_gemm(const PrefillGemmParams& p, bool down, int n_til
     cudaError_t e;
     if (down) {
         const size_t smem = kG_RingBytes + 1024;
-        e = cudaFuncSetAttribute(gemm_i8_kernel<DownPolicy, PrefillGemmParams>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        static bool attr_done[64] = {};
+        e = max_smem_once(gemm_i8_kernel<DownPolicy, PrefillGemmParams>, (int)smem, attr_done);
         if (e != cudaSuccess) return e;
         gemm_i8_kernel<DownPolicy, PrefillGemmParams><<<gemm_grid(n_items), kG_Threads, smem, stream>>>(p);
     } else {
         const size_t smem = kG_RingBytes + kG_XchBytes + 1024;
-        e = cudaFuncSetAttribute(gemm_i8_kernel<GateUpPolicy, PrefillGemmParams>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        static bool attr_done[64] = {};
+        e = max_smem_once(gemm_i8_kernel<GateUpPolicy, PrefillGemmParams>, (int)smem, attr_done);
         if (e != cudaSuccess) return e;
         gemm_i8_kernel<GateUpPolicy, PrefillGemmParams><<<gemm_grid(n_items), kG_Threads, smem, stream>>>(p);
     }

@@ -351,14 +351,18 @@ __global__ void __launch_bounds__(kThreadsT, 3) bulk_kernel(const GemvParams p, 
     const int4* entv = reinterpret_cast<const int4*>(p.group_list + kListHeader + kListEntry * blockIdx.y);
     const int n_entries = __ldcg(p.group_list);
     const int4 e0 = __ldcg(entv), e1 = __ldcg(entv + 1), e2 = __ldcg(entv + 2);
-    if ((int)blockIdx.y >= n_entries) return;
     const int expert = e0.x, m = e0.z;
     const bool shared = expert < 0;
-    if ((shared ? p.type_shared : p.type_routed) != TYPE) return;
     const int nrows = shared ? p.nrows_shared : p.nrows_routed;
     const int ncols = shared ? p.ncols_shared : p.ncols_routed, nb = ncols >> 5;
     const int width = 32 * wr, tile0 = blockIdx.x << wr_shift, tiles_total = nrows >> 5;
-    if (tile0 >= tiles_total) return;
+    if ((int)blockIdx.y >= n_entries || (shared ? p.type_shared : p.type_routed) != TYPE || tile0 >= tiles_total) {
+        // Nothing to do for this CTA.  A down-stage CTA still waits for the grid before it: this grid must not count as
+        // complete while the gate/up grid is running, because whatever follows in the stream (a second down instance for
+        // the other weight type, the caller's next kernel) depends on this grid only.
+        if (STAGE == kStageDown) griddep_wait();
+        return;
+    }
     // down stage: let the next kernel of the stream (the next layer's router, if it was launched programmatically)
     // bring its CTAs in; it waits for this grid before it touches the workspace
     if (STAGE == kStageDown && tid == 0) griddep_launch();

@@ -603,19 +603,15 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
         const int rows_per_group = 2 * (((nrows + groups - 1) / groups + 1) / 2);
         const dim3 grid((nrows + rows_per_group - 1) / rows_per_group, token_tiles);
         const size_t smem = (size_t)kBigRouteSmemInts * sizeof(int);   // 2 x 16 KiB partial sums + 4 x 2 x H x 4 <= 64 KiB ring
-        static bool attr_set = false;
-        if (!attr_set) {
-            cudaFuncSetAttribute(route_big_kernel<8, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            attr_set = true;
-        }
+        static bool attr_done[64] = {};
+        cudaError_t e = max_smem_once(route_big_kernel<8, 8>, (int)smem, attr_done);
+        if (e != cudaSuccess) return e;
         route_big_kernel<8, 8><<<grid, 256, smem, stream>>>(p, rows_per_group);
     } else {
         constexpr int TT = 8, TE = 8;
-        static bool attr_set = false;
-        if (!attr_set) {
-            cudaFuncSetAttribute(route_kernel<TT, TE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)route_smem(TT, TE));
-            attr_set = true;
-        }
+        static bool attr_done[64] = {};
+        cudaError_t e = max_smem_once(route_kernel<TT, TE>, (int)route_smem(TT, TE), attr_done);
+        if (e != cudaSuccess) return e;
         dim3 grid((nrows + TE - 1) / TE, (p.T + TT - 1) / TT);
         route_kernel<TT, TE><<<grid, 256, route_smem(TT, TE), stream>>>(p);
     }
@@ -662,10 +658,10 @@ extern "C" int chimere_b200_moe_route_noalloc(const chimere_moe_layer* w, const 
                                               float* d_topk_w, cudaStream_t stream) {
     using namespace chimere;
     if (!w || !d_x || !d_topk_idx || !d_topk_w || !w->router_w) return -1;
-    if (w->H <= 0 || w->H % 32 || w->E <= 0 || w->E > kMaxExperts || w->top_k <= 0 || w->top_k > kMaxTopK || w->top_k > w->E) return -2;
+    if (w->H <= 0 || w->H % 32 || w->E <= 0 || w->top_k <= 0 || w->top_k > w->E || T <= 0) return -2;
     if (w->route_mode != CHIMERE_ROUTE_SOFTMAX_RENORM && w->route_mode != CHIMERE_ROUTE_SIGMOID_NORM_SCALE) return -2;
-    if (T <= 0) return -2;
-    if (T > kNoAllocMaxT || w->H > kNoAllocMaxH) return -7;   // larger than the built-in scratch: use chimere_b200_moe_route
+    // larger than the built-in scratch was sized for: use chimere_b200_moe_route with a workspace instead
+    if (T > kNoAllocMaxT || w->H > kNoAllocMaxH || w->E > kMaxExperts || w->top_k > kMaxTopK) return -7;
 
     // once per device, with that device current: the array's device address
     static unsigned char* s_base[64] = {nullptr};
@@ -674,6 +670,9 @@ extern "C" int chimere_b200_moe_route_noalloc(const chimere_moe_layer* w, const 
     if (e != cudaSuccess) return -100 - (int)e;
     if (dev < 0 || dev >= 64) return -2;
     if (!s_base[dev]) {
+        // the look-up is not a stream operation and must not happen while `stream` is being captured
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone) return -8;
         unsigned char* ptr = nullptr;
         e = cudaGetSymbolAddress((void**)&ptr, g_route_scratch);
         if (e != cudaSuccess || !ptr) return -100 - (int)e;

@@ -151,9 +151,11 @@ int chimere_b200_moe_route(const chimere_moe_layer* w, const float* d_x, int T,
  * allowed.  Same computation as chimere_b200_moe_route, but the scratch is a fixed array inside the
  * library (about 680 KiB per GPU, held from the moment the library is loaded on that GPU until the
  * process exits) and the results go to the caller's buffers: d_topk_idx [T][top_k] int32 and
- * d_topk_w [T][top_k] f32.  Limits: T <= 64 tokens, H <= 4096, E <= 256; anything larger returns -7.
- * The first call on each device looks the array's address up (cudaGetSymbolAddress): make that call
- * outside any stream capture.  All calls on a device share the array, so calls that overlap on the GPU
+ * d_topk_w [T][top_k] f32.  Limits: T <= 64 tokens, H <= 4096, E <= 256, top_k <= 8; anything larger
+ * returns -7 (malformed descriptions -- null pointers, non-positive sizes, H not a multiple of 32 --
+ * return -1 / -2 as everywhere else).  The first call on each device looks the array's address up
+ * (cudaGetSymbolAddress): make that call outside any stream capture; a first call made while `stream`
+ * is being captured returns -8 and does nothing.  All calls on a device share the array, so calls that overlap on the GPU
  * race; run them on one stream or order them yourself.  No cudaMalloc / cudaFree, here or below.
  * This entry has no counterpart in the reference. */
 int chimere_b200_moe_route_noalloc(const chimere_moe_layer* w, const float* d_x, int T,
@@ -289,6 +291,15 @@ void chimere_mmvq_q8_0(const void* weights, const void* input_q8, float* output,
 /* New, same shape as the two above, for Q4_0 experts. */
 void chimere_mmvq_q4_0(const void* weights, const void* input_q8, float* output, int ncols,
                        int nrows, int nrows_y_padded, cudaStream_t stream);
+/* ggml_cuda_gemv.cu:322-352 (Rust declarations src/kernels/ggml_gpu.rs:173-193, call sites :933, :972): quantize the
+ * f32 input row to Q8_1 into q8_scratch (ncols_padded / 32 * 36 bytes, ncols_padded = pad(ncols, 512); blocks past
+ * ncols are zero), then y[nrows] = W . x_q8.  The Q4_0 variant is new, same shape. */
+void chimere_mmvq_iq3s_f32(const void* weights, const float* input_f32, float* output, int ncols, int nrows,
+                           int ncols_padded, void* q8_scratch, cudaStream_t stream);
+void chimere_mmvq_q8_0_f32(const void* weights, const float* input_f32, float* output, int ncols, int nrows,
+                           int ncols_padded, void* q8_scratch, cudaStream_t stream);
+void chimere_mmvq_q4_0_f32(const void* weights, const float* input_f32, float* output, int ncols, int nrows,
+                           int ncols_padded, void* q8_scratch, cudaStream_t stream);
 /* ggml_cuda_gemv.cu:243-279: top_k expert GEMVs in one launch, expert ids read on the device.
  * input_stride = 0: one shared Q8_1 input; otherwise bytes between the per-slot inputs. */
 void chimere_mmvq_iq3s_batched(const void* all_weights, const void* input_q8, float* output,

@@ -404,9 +404,13 @@ void orc_permute(const int32_t* idx, int T, int k, int E, int32_t* perm, int32_t
  * Optional taps (any may be NULL):
  *   topk_idx[T][k], topk_w[T][k], logits[T][E], x_q8[T][H/32*36],
  *   inter_q8[T][k+1][Fmax/32*36] (slot k = shared expert), sh_logit[T]. */
-int orc_moe_forward(const chimere_moe_layer* w, const float* x, float* y, int T,
-                    int32_t* topk_idx, float* topk_w, float* logits_out, uint8_t* x_q8_out,
-                    uint8_t* inter_q8_out, float* sh_logit_out) {
+/* forced_idx (optional, [T][k]): take these expert ids instead of the oracle's own top-k and give them the weights
+ * the router would: the probabilities of those experts, renormalised (and scaled) exactly as after a selection.
+ * The GPU tests use it where the host's expf and the GPU's differ in the last place and flip a near-tie: the rest
+ * of the layer is then still checked on the GPU's routing. */
+int orc_moe_forward_ex(const chimere_moe_layer* w, const float* x, float* y, int T, const int32_t* forced_idx,
+                       int32_t* topk_idx, float* topk_w, float* logits_out, uint8_t* x_q8_out,
+                       uint8_t* inter_q8_out, float* sh_logit_out) {
     const int H = w->H, E = w->E, F = w->F, Fs = w->F_s, k = w->top_k;
     if (E > 256 || k > 16 || H % 32 || F % 32 || Fs % 32) return -1;
     const int dual = w->act == CHIMERE_ACT_SWIGLU;
@@ -430,10 +434,22 @@ int orc_moe_forward(const chimere_moe_layer* w, const float* x, float* y, int T,
             const float* xt = x + (size_t)t * H;
             float logits[256];
             orc_router_logits(w->router_w, w->router_bias, xt, E, H, logits);
+            float probs[256];
             if (w->route_mode == CHIMERE_ROUTE_SOFTMAX_RENORM) {
-                orc_topk_softmax(logits, E, k, idx + i * 16, wt + i * 16, NULL);
+                orc_topk_softmax(logits, E, k, idx + i * 16, wt + i * 16, probs);
                 if (w->route_scale != 1.0f) for (int j = 0; j < k; j++) wt[i * 16 + j] *= w->route_scale;
-            } else orc_topk_sigmoid(logits, E, k, w->route_scale, idx + i * 16, wt + i * 16, NULL);
+            } else orc_topk_sigmoid(logits, E, k, w->route_scale, idx + i * 16, wt + i * 16, probs);
+            if (forced_idx) {
+                float wsum = 0.0f;
+                for (int j = 0; j < k; j++) {
+                    idx[i * 16 + j] = forced_idx[(size_t)t * k + j];
+                    wt[i * 16 + j] = probs[idx[i * 16 + j]];
+                    wsum += wt[i * 16 + j];
+                }
+                if (wsum > 0.0f) { const float inv = 1.0f / wsum; for (int j = 0; j < k; j++) wt[i * 16 + j] *= inv; }
+                if (w->route_mode != CHIMERE_ROUTE_SOFTMAX_RENORM || w->route_scale != 1.0f)
+                    for (int j = 0; j < k; j++) wt[i * 16 + j] *= w->route_scale;
+            }
             orc_quantize_q8_1(xt, xq + (size_t)i * xq_row, H);
             if (Fs > 0 && w->shexp_gate_w) shl[i] = orc_dot_strided256(xt, w->shexp_gate_w, H);
             if (topk_idx) memcpy(topk_idx + (size_t)t * k, idx + i * 16, sizeof(int32_t) * (size_t)k);
@@ -494,6 +510,12 @@ int orc_moe_forward(const chimere_moe_layer* w, const float* x, float* y, int T,
     }
     free(idx); free(wt); free(shl); free(xq); free(inter); free(iq); free(eout);
     return 0;
+}
+
+int orc_moe_forward(const chimere_moe_layer* w, const float* x, float* y, int T,
+                    int32_t* topk_idx, float* topk_w, float* logits_out, uint8_t* x_q8_out,
+                    uint8_t* inter_q8_out, float* sh_logit_out) {
+    return orc_moe_forward_ex(w, x, y, T, NULL, topk_idx, topk_w, logits_out, x_q8_out, inter_q8_out, sh_logit_out);
 }
 
 int orc_num_threads(void) {

@@ -39,8 +39,8 @@ def lib() -> C.CDLL:
         L.orc_relu2.restype, L.orc_relu2.argtypes = C.c_float, [C.c_float]
         L.orc_row_bytes.restype, L.orc_row_bytes.argtypes = C.c_int64, [C.c_int, C.c_int]
         L.orc_dequant.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64]
-        L.orc_moe_forward.restype = C.c_int
-        L.orc_moe_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int] + [C.c_void_p] * 6
+        L.orc_moe_forward_ex.restype = C.c_int
+        L.orc_moe_forward_ex.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int] + [C.c_void_p] * 7
         L.orc_num_threads.restype = C.c_int
         L.orc_set_num_threads.argtypes = [C.c_int]
         _lib = L
@@ -139,8 +139,9 @@ def rmsnorm(x, eps=1e-6):
     return y
 
 
-def moe_forward(weights, x, taps=True):
-    """weights: chimere_b200.layer.MoeWeightsRaw on the CPU; x: [T, H] array.  Returns dict."""
+def moe_forward(weights, x, taps=True, forced_idx=None):
+    """weights: chimere_b200.layer.MoeWeightsRaw on the CPU; x: [T, H] array.  Returns dict.
+    forced_idx [T, k] (optional): route with these expert ids instead of the oracle's own top-k."""
     st = weights.as_struct()
     x = f32(x)
     T, H = x.shape
@@ -152,8 +153,9 @@ def moe_forward(weights, x, taps=True):
         out.update(topk_idx=np.empty((T, k), np.int32), topk_w=np.empty((T, k), np.float32),
                    logits=np.empty((T, E), np.float32), x_q8=np.empty((T, H // 32 * 36), np.uint8),
                    inter_q8=np.zeros((T, k + 1, Fmax // 32 * 36), np.uint8), sh_logit=np.zeros(T, np.float32))
-    rc = lib().orc_moe_forward(C.byref(st), _p(x), _p(y), C.c_int(T),
-                               _p(out.get("topk_idx")), _p(out.get("topk_w")), _p(out.get("logits")),
-                               _p(out.get("x_q8")), _p(out.get("inter_q8")), _p(out.get("sh_logit")))
+    forced = None if forced_idx is None else np.ascontiguousarray(forced_idx, np.int32).reshape(T, k)
+    rc = lib().orc_moe_forward_ex(C.byref(st), _p(x), _p(y), C.c_int(T), _p(forced),
+                                  _p(out.get("topk_idx")), _p(out.get("topk_w")), _p(out.get("logits")),
+                                  _p(out.get("x_q8")), _p(out.get("inter_q8")), _p(out.get("sh_logit")))
     assert rc == 0
     return out

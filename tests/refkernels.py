@@ -116,3 +116,18 @@ def dequant_iq3s(data: torch.Tensor, n_blocks: int) -> torch.Tensor:
     out = torch.empty(n_blocks * 256, dtype=torch.float32, device=data.device)
     _launch("dequant_iq3s", ((n_blocks + 255) // 256, 1, 1), (256, 1, 1), 0, [_dp(data), _dp(out), C.c_int(n_blocks)])
     return out
+
+
+def fused_moe_iq3s(hidden: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor,
+                   weights: torch.Tensor, hidden_size: int, expert_ffn: int, bytes_gate: int, bytes_up: int, bytes_down: int) -> torch.Tensor:
+    """fused_moe_iq3s (chimere_kernels.cu:1093-1143), the reference's whole-layer kernel for one token: one CTA per
+    selected expert dequantises its IQ3_S gate / up / down matrices on the fly (fp32 input, no activation
+    quantisation), applies SwiGLU and adds weight * down row sums into `output` with atomicAdd.  Launched as
+    src/kernels/fused_moe.rs:379-386 does: grid = top_k, block 256, shared (hidden + 3 * ffn) * 4 bytes; the output
+    must start at zero."""
+    k = ids.numel()
+    out = torch.zeros(hidden_size, dtype=torch.float32, device=hidden.device)
+    _launch("fused_moe_iq3s", (k, 1, 1), (256, 1, 1), (hidden_size + 3 * expert_ffn) * 4,
+            [_dp(hidden), _dp(gate), _dp(up), _dp(down), _dp(ids), _dp(weights), _dp(out), C.c_int(hidden_size), C.c_int(expert_ffn),
+             C.c_int(bytes_gate), C.c_int(bytes_up), C.c_int(bytes_down)])
+    return out

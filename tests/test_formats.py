@@ -10,7 +10,10 @@ import torch
 import oracle
 from chimere_b200 import formats as F
 
-REF_LOADER = "/root/reference/chimere-server/src/gguf_loader.rs"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+# the reference tree: CHIMERE_REFERENCE_DIR, or a directory named "reference" beside the repository
+REF_DIR = os.environ.get("CHIMERE_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
+REF_LOADER = os.path.join(REF_DIR, "chimere-server", "src", "gguf_loader.rs")
 
 
 def test_grid_matches_gguf_package():
