@@ -14,7 +14,7 @@ import oracle
 import refkernels
 from chimere_b200 import abi, configs, formats
 from chimere_b200.layer import MoeScratch, MoeWeightsTiled, forward_moe, forward_moe_host, route_only
-from parity_util import check_rows, near_tie_ok, oracle_on_gpu_routing  # noqa: F401
+from parity_util import COS_TOL, check_rows, near_tie_ok, oracle_on_gpu_routing  # noqa: F401
 
 pytestmark = pytest.mark.gpu
 
@@ -323,8 +323,12 @@ def test_legacy_mmvq_from_f32_input(qtype, fn):
 @pytest.mark.parametrize("layout", LAYOUTS)
 def test_whole_layer_against_reference_fused_kernel(layout):
     """The one whole-layer kernel of the reference that runs here: fused_moe_iq3s (chimere_kernels.cu:1093-1143), one
-    token, gate / up / down all IQ3_S, routed experts only.  It dequantises to fp32 and does not quantise the
-    activations, so its output differs from the Q8_1 path by the activation rounding: the 1e-2 / 0.9999 bar applies."""
+    token, gate / up / down all IQ3_S, routed experts only.  It multiplies dequantised weights with the fp32
+    activations; the path built here (like the reference's production path, moe_ffn.rs:1185-1373) rounds the input
+    and the intermediates to Q8_1 first.  That rounding alone moves an output by about 1 % of the largest one
+    (two 8-bit roundings per output, measured 1.2e-2), so against this kernel the bar is 2.5e-2 and cosine >= 0.9999;
+    the CPU oracle, which restates the Q8_1 path, must sit within the benchmark's own 1e-2 of the GPU result, and as
+    far from the fused kernel as the GPU result does."""
     if not refkernels.available():
         pytest.skip("oracle/_ref cubin not built")
     cfg = configs.scaled(configs.QWEN_IQ3S, type_down=configs.IQ3_S, F_s=0, name="qwen35-moe-iq3s-all")
@@ -339,4 +343,11 @@ def test_whole_layer_against_reference_fused_kernel(layout):
         ref = refkernels.fused_moe_iq3s(x[0].contiguous(), raw.gate_exps_raw, raw.up_exps_raw, raw.down_exps_raw, ids, wts,
                                         cfg.H, cfg.F, raw.expert_bytes_gate, raw.expert_bytes_up, raw.expert_bytes_down)
         torch.cuda.synchronize()
-        check_rows(y.cpu().numpy(), ref.cpu().numpy()[None, :])
+        yg, yr = y.cpu().numpy()[0].astype(np.float64), ref.cpu().numpy().astype(np.float64)
+        o = oracle_on_gpu_routing(wh, x.cpu().numpy(), sc.topk_indices(1).cpu().numpy())
+        yo = o["y"][0].astype(np.float64)
+        rel = lambda a, b: np.abs(a - b).max() / np.abs(b).max()
+        cos = lambda a, b: float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b)))
+        assert rel(yg, yr) <= 2.5e-2 and cos(yg, yr) >= COS_TOL, (rel(yg, yr), cos(yg, yr))
+        check_rows(yg[None, :], yo[None, :])                      # the Q8_1 path itself: the benchmark's bar
+        assert abs(rel(yo, yr) - rel(yg, yr)) <= 5e-3              # the distance to the fused kernel is the rounding, not the GPU code
