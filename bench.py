@@ -86,6 +86,28 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def pct(vals):
+    """median / p10 / p90 of a list of numbers."""
+    v = sorted(vals)
+    if not v:
+        return None
+    q = lambda f: v[min(len(v) - 1, max(0, int(round(f * (len(v) - 1)))))]
+    return {"p50": statistics.median(v), "p10": q(0.10), "p90": q(0.90), "n": len(v)}
+
+
+def captured_traffic(kernel, shape):
+    """DRAM bytes per launch of `kernel` at `shape` from the committed ncu capture table (profiles/dram_traffic.json),
+    or None when no capture of that kernel and shape has been recorded."""
+    try:
+        table = json.load(open(os.path.join(ROOT, "profiles", "dram_traffic.json")))
+    except (OSError, ValueError):
+        return None, None
+    ent = table.get(f"{kernel} | {shape}")
+    if not ent:
+        return None, None
+    return int(ent["dram_bytes_read"]) + int(ent["dram_bytes_write"]), ent.get("source")
+
+
 _CPU_LAYERS = {}
 
 
@@ -134,10 +156,13 @@ def run_reference(args):
         v, threads, dt = cpu_port_tokens_per_s(cfg, T, sample_layers, min_seconds=per_step)
         vals.append(v); t_total += dt
     v = statistics.median(vals)
+    conf = workload_config(cfg, T, sample_layers)
+    conf["sample"] = (f"each step walks {sample_layers} seeded layers (not the GPU arm's 16) for about {per_step:.1f} s: the same T and shapes, a rate "
+                      "metric; two layers' weights (0.8 GB) still exceed the host's caches")
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": 1e3 * t_total / max(1, args.steps), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int8 block dots, f32 accumulate", "data": "synthetic",
-            "config": workload_config(cfg, T, sample_layers),
+            "config": conf, "steps_stats": pct(vals),
             "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
                              "sample": f"T={T} tokens through {sample_layers} layers, repeated for {per_step:.1f} s per step (CPU restatement in oracle/, OpenMP)"},
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -152,40 +177,112 @@ def workload_config(cfg, T, L):
             "l2": f"weights rotate over {L} layers; one cycle touches more than the 126 MB L2, inputs differ per layer"}
 
 
-def measure_prefill(lib, dev, tokens_list):
-    """Secondary measurement: the prefill configuration (all experts Q8_0, Zipf-skewed routing) on one layer, with the
-    large experts on the tcgen05 grouped GEMM and, for comparison, everything on the GEMV kernels."""
+def measure_int8_peak(lib, dev):
+    """The int8 tensor-pipe rate of this GPU with nothing read back (tcgen05.mma kind::i8 issued back to back from
+    shared-memory operands by one CTA per SM): the denominator for the compute side of the prefill roofline."""
+    import torch
+    status = torch.zeros(64, dtype=torch.int32, device=dev)
+    st = torch.cuda.current_stream(dev).cuda_stream
+    out = {}
+    for n_cols in (128, 256):
+        n_mma = 16384
+        best = None
+        for rep in range(4):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            ctas = lib.chimere_b200_mma_i8_probe(n_mma, n_cols, status.data_ptr(), st)
+            e1.record()
+            torch.cuda.synchronize()
+            if ctas <= 0:
+                return {"error": ctas}
+            ms = e0.elapsed_time(e1)
+            if rep > 0:
+                best = ms if best is None else min(best, ms)
+        ops = ctas * n_mma * 2 * 128 * n_cols * 32
+        out[f"m128_n{n_cols}_k32"] = {"tops": ops / (best * 1e-3) / 1e12, "ms": best, "ctas": ctas, "mma_per_cta": n_mma}
+    out["device_status"] = int(status[0].item())
+    out["how"] = "one CTA per SM, tcgen05.mma kind::i8 accumulating in TMEM, no read-back; best of 3 after one warm-up"
+    return out
+
+
+class L2Flush:
+    """Writes a buffer twice the size of the L2 between timed calls, so that a call cannot find its weights there."""
+
+    def __init__(self, dev):
+        import torch
+        self.buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def __call__(self):
+        self.buf.fill_(1)
+
+
+def timed_calls(fn, reps, flush):
+    """Device time of `reps` single calls of fn(), each after an L2 flush (events on the current stream); microseconds."""
+    import torch
+    times = []
+    for _ in range(reps):
+        flush()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    return times
+
+
+def measure_secondary(lib, dev, hbm_peak, i8_peak_tops, prefill_tokens):
+    """The configurations beside the headline one, each on one seeded layer, one layer call per timed sample with the L2
+    flushed before it: the prefill configuration (all experts Q8_0, Zipf-skewed routing) at the given batch sizes on the
+    tensor-core path (and, for comparison, everything on the GEMV kernels), the Nemotron-H-style layer at T = 1 and 256,
+    and the CPU-runnable Q4_0 layer at T = 16.  Every entry carries its algorithmic bytes (with the measured number of
+    distinct experts), its int8 operations and frac = max(bytes / HBM peak, ops / int8 peak) / time."""
     import torch
     from chimere_b200 import configs
     from chimere_b200.layer import MoeScratch, MoeWeightsPrefill, MoeWeightsTiled, forward_moe, forward_moe_prefill
-    cfg = configs.QWEN_Q8_0
-    raw = configs.make_layer(cfg, device=dev)
-    tiled, pw = MoeWeightsTiled(raw), MoeWeightsPrefill(raw)
-    del raw
+    flush = L2Flush(dev)
+    plan = []
+    if prefill_tokens:
+        plan.append((configs.QWEN_Q8_0, [(T, ("gemm", "gemv")) for T in prefill_tokens]))
+    plan.append((configs.NEMOTRON_Q4_0, [(1, ("gemv",)), (256, ("gemm", "gemv"))]))
+    plan.append((configs.QWEN_Q4_0, [(16, ("gemv", "gemm"))]))
     out = []
-    for T in tokens_list:
-        x = configs.make_input(cfg, T, device=dev)
-        sc = MoeScratch(tiled, T, device=dev)
-        sc.enable_prefill()
-        y = torch.empty_like(x)
-        res = {"T": T}
-        for name, fn in (("gemm", lambda: forward_moe_prefill(tiled, pw, sc, x, y)), ("gemv", lambda: forward_moe(tiled, sc, x, y))):
-            for _ in range(3):
-                fn()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            reps = 5
-            e0.record()
-            for _ in range(reps):
-                fn()
-            e1.record()
-            torch.cuda.synchronize()
-            us = e0.elapsed_time(e1) * 1e3 / reps
-            res[name] = {"us_per_layer_call": us, "tokens_per_s": T / (us * 1e-6), "int8_tops": configs.int8_ops(cfg, T) / (us * 1e-6) / 1e12}
-        res["device_status"] = sc.status()
-        out.append(res)
-        del sc, x, y
-    return {"workload": f"{cfg.name}: one layer, all experts Q8_0, Zipf(1.1) logit bias, weights 0.86 GB (> L2)", "results": out}
+    for cfg, cases in plan:
+        raw = configs.make_layer(cfg, device=dev)
+        tiled, pw = MoeWeightsTiled(raw), MoeWeightsPrefill(raw)
+        del raw
+        for T, paths in cases:
+            x = configs.make_input(cfg, T, device=dev)
+            sc = MoeScratch(tiled, T, device=dev)
+            sc.enable_prefill()
+            y = torch.empty_like(x)
+            res = {"config": cfg.name, "T": T}
+            for name in paths:
+                fn = (lambda: forward_moe_prefill(tiled, pw, sc, x, y)) if name == "gemm" else (lambda: forward_moe(tiled, sc, x, y))
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                ts = timed_calls(fn, 7, flush)
+                us = statistics.median(ts)
+                U = int(torch.unique(sc.topk_indices(T)).numel())
+                alg = configs.algorithmic_bytes(cfg, T, U)
+                ops = configs.int8_ops(cfg, T)
+                t_hbm = alg / (hbm_peak * 1e9) * 1e6
+                t_i8 = ops / (i8_peak_tops * 1e12) * 1e6 if i8_peak_tops else 0.0
+                res[name] = {"us_per_layer_call": us, "us_stats": pct(ts), "tokens_per_s": T / (us * 1e-6),
+                             "int8_tops": ops / (us * 1e-6) / 1e12, "hbm_gbs": alg / (us * 1e-6) / 1e9,
+                             "frac": max(t_hbm, t_i8) / us, "bound": "hbm" if t_hbm >= t_i8 else "tensor"}
+                res.update(distinct_experts=U, algorithmic_bytes=alg, int8_ops=ops, roofline_us={"hbm": t_hbm, "int8": t_i8})
+            res["device_status"] = sc.status()
+            out.append(res)
+            del sc, x, y
+        del tiled, pw
+        torch.cuda.empty_cache()
+    return {"how": "one layer, one call per sample, L2 flushed (256 MB written) before every sample, CUDA events on the launching "
+                   "stream, median of 7; gemm = chimere_b200_moe_forward_prefill (tcgen05 grouped GEMM for experts with >= 8 tokens), "
+                   "gemv = chimere_b200_moe_forward; frac = max(algorithmic bytes / measured HBM peak, int8 operations / measured "
+                   "int8 tensor peak) / time",
+            "results": out}
 
 
 def run_expert_parallel(args, cfg, dev, rank, world, local, dist, hbm_peak, peak_kind):
@@ -308,9 +405,10 @@ def main():
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
-    ap.add_argument("--prefill-tokens", default="512,2048,8192", help="comma list of T for the secondary prefill measurement ('' = skip)")
+    ap.add_argument("--prefill-tokens", default="512,2048,8192",
+                    help="comma list of T for the prefill configuration in the secondary measurement ('' = none of them, 'none' = skip the secondary measurement)")
     ap.add_argument("--prefill-only", action="store_true",
-                    help="run only the secondary prefill measurement and print its JSON (used for profiling the grouped GEMM)")
+                    help="run only the int8 peak probe and the secondary measurement and print their JSON (used for profiling the grouped GEMM)")
     ap.add_argument("--layout", default="tiled", choices=["tiled", "ggml"],
                     help="weight layout the layer entry runs on: the library's tiled32 repack (default) or raw ggml blocks")
     args = ap.parse_args()
@@ -335,12 +433,14 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     lib = abi.load()
+    hbm_peak, peak_kind = peaks()
     if args.prefill_only:
-        print(json.dumps({"prefill": measure_prefill(lib, dev, [int(t) for t in args.prefill_tokens.split(",") if t])}))
+        i8 = measure_int8_peak(lib, dev)
+        i8_tops = i8.get("m128_n256_k32", {}).get("tops")
+        print(json.dumps({"int8_peak": i8, "secondary": measure_secondary(lib, dev, hbm_peak, i8_tops, [int(t) for t in args.prefill_tokens.split(",") if t])}))
         return 0
     cfg = configs.QWEN_IQ3S
     T, L, K, W = args.tokens, args.layers, args.steps, args.warmup
-    hbm_peak, peak_kind = peaks()
     if world > 1:
         return run_expert_parallel(args, cfg, dev, rank, world, local, dist, hbm_peak, peak_kind)
 
@@ -363,66 +463,48 @@ def main():
             if rc:
                 raise RuntimeError(f"chimere_b200_moe_forward rc={rc}")
 
-    def make_graph(Tn):
+    def graph_of(fn):
+        """The launches of fn() as one CUDA graph, so that the device time is not hidden behind the host's launch rate."""
         g = torch.cuda.CUDAGraph()
         with torch.cuda.stream(stream):
-            enqueue_layers(Tn)  # warm (also sets kernel attributes outside capture)
+            fn()  # warm (also sets kernel attributes outside capture)
             stream.synchronize()
             with torch.cuda.graph(g, stream=stream):
-                enqueue_layers(Tn)
+                fn()
         return g
 
     def time_steps(run, k, w):
-        """k timed repetitions of run() on `stream` after w warm-ups; returns seconds (device time)."""
+        """k timed repetitions of run() on `stream` after w warm-ups, bracketed by a synchronize on both sides.
+        Returns (seconds for the k repetitions, per-repetition seconds); all device time, CUDA events on `stream`."""
         with torch.cuda.stream(stream):
             for _ in range(w):
                 run()
             stream.synchronize()
-            if dist is not None:
-                dist.barrier()
             torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            for _ in range(k):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(k + 1)]
+            ev[0].record(stream)
+            for i in range(k):
                 run()
-            e1.record(stream)
+                ev[i + 1].record(stream)
             stream.synchronize()
             torch.cuda.synchronize()
-            if dist is not None:
-                dist.barrier()
-        return e0.elapsed_time(e1) * 1e-3
+        return ev[0].elapsed_time(ev[k]) * 1e-3, [ev[i].elapsed_time(ev[i + 1]) * 1e-3 for i in range(k)]
 
     def distinct_experts(Tn):
         return [int(torch.unique(sc.topk_indices(Tn)).numel()) for sc in scratch]
 
     # ---- headline: graph replay of one step = L layer calls ----
-    graph = make_graph(T)
+    graph = graph_of(lambda: enqueue_layers(T))
     sampler = ClockSampler(local)
-    secs = time_steps(graph.replay, K, W)
+    secs, per_step = time_steps(graph.replay, K, W)
     clocks = sampler.stop()
-    if dist is not None:
-        t = torch.tensor([secs], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        secs = float(t.item())
     value = world * T * L * K / secs
     U = distinct_experts(T)
     layer_bytes = sum(configs.algorithmic_bytes(cfg, T, u) for u in U) / L
     layer_us = secs / (K * L) * 1e6
     layer_gbs = layer_bytes / (layer_us * 1e-6) / 1e9
 
-    # ---- roofline of the dominant kernel (gate/up GEMV), timed alone over the rotating layers ----
-    def gate_up_all():
-        for w, sc in zip(layers, scratch):
-            rc = lib.chimere_b200_moe_gate_up(C.byref(w.as_struct()), T, C.byref(sc.ws), sptr)
-            if rc:
-                raise RuntimeError(f"gate_up rc={rc}")
-
-    def down_all():
-        for w, sc, y in zip(layers, scratch, ys):
-            rc = lib.chimere_b200_moe_down_combine(C.byref(w.as_struct()), y.data_ptr(), T, C.byref(sc.ws), sptr)
-            if rc:
-                raise RuntimeError(f"down rc={rc}")
-
+    # ---- the three kernels of a layer call, each replayed alone over the rotating layers ----
     from chimere_b200 import formats
     b_gu = cfg.F * formats.row_bytes(cfg.type_gate_up, cfg.H)
     b_gu_sh = cfg.F_s * formats.row_bytes(cfg.type_gate_up, cfg.H)
@@ -430,33 +512,37 @@ def main():
     b_dn_sh = cfg.H * formats.row_bytes(cfg.type_down, cfg.F_s)
     xq_row = cfg.H // 32 * 36
     iq_row = max(cfg.F, cfg.F_s) // 32 * 36
-    pairs = T * cfg.top_k + T
-    gu_bytes = sum(2 * (u * b_gu + b_gu_sh) + T * xq_row + pairs * (cfg.F // 32 * 36) for u in U) / L
-    dn_bytes = sum(u * b_dn + b_dn_sh + pairs * iq_row + T * cfg.H * 4 for u in U) / L
-    def graph_of(fn):
-        """L launches as one CUDA graph, so that the device time is not hidden behind the host's launch rate."""
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(stream):
-            fn()
-            stream.synchronize()
-            with torch.cuda.graph(g, stream=stream):
-                fn()
-        return g
 
-    def route_all():
-        for w, sc, x in zip(layers, scratch, xs):
-            rc = lib.chimere_b200_moe_route(C.byref(w.as_struct()), x.data_ptr(), T, C.byref(sc.ws), sptr)
-            if rc:
-                raise RuntimeError(f"route rc={rc}")
+    def stage_times(Tn, reps):
+        """us per launch of the router, gate/up and down kernels at batch size Tn (the workspaces must hold the routing of
+        a layer call at Tn), and the algorithmic bytes of the two GEMV launches."""
+        def calls(entry, with_x=False, with_y=False):
+            def run():
+                for w, sc, x, y in zip(layers, scratch, xs, ys):
+                    a = [C.byref(w.as_struct())] + ([x.data_ptr()] if with_x else []) + ([y.data_ptr()] if with_y else []) + [Tn, C.byref(sc.ws), sptr]
+                    rc = entry(*a)
+                    if rc:
+                        raise RuntimeError(f"stage rc={rc}")
+            return run
+        Un = distinct_experts(Tn)
+        pairs = Tn * cfg.top_k + Tn
+        gu_b = sum(2 * (u * b_gu + b_gu_sh) + Tn * xq_row + pairs * (cfg.F // 32 * 36) for u in Un) / L
+        dn_b = sum(u * b_dn + b_dn_sh + pairs * iq_row + Tn * cfg.H * 4 for u in Un) / L
+        gu = time_steps(graph_of(calls(lib.chimere_b200_moe_gate_up)).replay, reps, 3)[0] / (reps * L)
+        dn = time_steps(graph_of(calls(lib.chimere_b200_moe_down_combine, with_y=True)).replay, reps, 3)[0] / (reps * L)
+        rt = time_steps(graph_of(calls(lib.chimere_b200_moe_route, with_x=True)).replay, reps, 3)[0] / (reps * L)
+        return {"route_us": rt * 1e6, "gate_up_us": gu * 1e6, "down_us": dn * 1e6, "gate_up_bytes": gu_b, "down_bytes": dn_b,
+                "gate_up_frac": gu_b / gu / 1e9 / hbm_peak, "down_frac": dn_b / dn / 1e9 / hbm_peak}
 
-    gu_secs = time_steps(graph_of(gate_up_all).replay, max(5, K), 3) / (max(5, K) * L)
-    dn_secs = time_steps(graph_of(down_all).replay, max(5, K), 3) / (max(5, K) * L)
-    rt_secs = time_steps(graph_of(route_all).replay, max(5, K), 3) / (max(5, K) * L)
-    roof = {"bound": "hbm", "kernel": ("bulk_kernel<IQ3_S, gate_up>" if args.layout == "tiled" else "gate_up_kernel<IQ3_S>"), "achieved": gu_bytes / gu_secs / 1e9, "peak": hbm_peak,
+    stg = stage_times(T, max(5, K))
+    gu_secs, dn_secs, rt_secs, gu_bytes, dn_bytes = stg["gate_up_us"] * 1e-6, stg["down_us"] * 1e-6, stg["route_us"] * 1e-6, stg["gate_up_bytes"], stg["down_bytes"]
+    kname = "bulk_kernel<IQ3_S, gate_up>" if args.layout == "tiled" else "gate_up_kernel<IQ3_S>"
+    traffic, traffic_src = captured_traffic(kname, f"{cfg.name} T={T}")
+    roof = {"bound": "hbm", "kernel": kname, "achieved": gu_bytes / gu_secs / 1e9, "peak": hbm_peak,
             "unit": "GB/s", "frac": gu_bytes / gu_secs / 1e9 / hbm_peak, "peak_kind": peak_kind,
-            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at these sizes, from an ncu capture of
-            # the two-layer case (one launch = one layer); IQ3_S is streamed as 4-bit codes: +22 % over the ggml bytes
-            "traffic": (67008256 + 735488) if (args.layout == "tiled" and T == 8) else None,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this shape, from the committed ncu capture
+            # table (None when this kernel and shape have not been captured)
+            "traffic": traffic, "traffic_source": traffic_src,
             "us_per_launch": gu_secs * 1e6, "algorithmic_bytes_per_launch": gu_bytes,
             "down_kernel": {"achieved": dn_bytes / dn_secs / 1e9, "frac": dn_bytes / dn_secs / 1e9 / hbm_peak,
                             "us_per_launch": dn_secs * 1e6, "algorithmic_bytes_per_launch": dn_bytes},
@@ -464,20 +550,21 @@ def main():
             "layer": {"achieved": layer_gbs, "frac": layer_gbs / hbm_peak, "us_per_layer_call": layer_us,
                       "algorithmic_bytes_per_call": layer_bytes, "distinct_experts_mean": sum(U) / L}}
 
-    # ---- sweep over T (layer level, graph replay) ----
+    # ---- sweep over T: the layer call and its three kernels (graph replay over the rotating layers) ----
     sweep = []
-    if not args.no_sweep and rank == 0:
+    if not args.no_sweep:
         for Tn in (1, 2, 4, 8):
-            g = make_graph(Tn)
-            s = time_steps(g.replay, max(5, K), 3) / max(5, K)
+            g = graph_of(lambda: enqueue_layers(Tn))
+            s_ = time_steps(g.replay, max(5, K), 3)[0] / max(5, K)
             Un = distinct_experts(Tn)
             b = sum(configs.algorithmic_bytes(cfg, Tn, u) for u in Un) / L
-            us = s / L * 1e6
-            sweep.append({"T": Tn, "us_per_layer_call": us, "tokens_layers_per_s": Tn * L / s,
-                          "hbm_gbs": b / (us * 1e-6) / 1e9, "hbm_frac": b / (us * 1e-6) / 1e9 / hbm_peak,
-                          "distinct_experts_mean": sum(Un) / L})
-    elif dist is not None:
-        pass
+            us = s_ / L * 1e6
+            ent = {"T": Tn, "us_per_layer_call": us, "tokens_layers_per_s": Tn * L / s_,
+                   "hbm_gbs": b / (us * 1e-6) / 1e9, "hbm_frac": b / (us * 1e-6) / 1e9 / hbm_peak,
+                   "algorithmic_bytes_per_call": b, "distinct_experts_mean": sum(Un) / L}
+            ent["kernels"] = stage_times(Tn, 5)
+            sweep.append(ent)
+            del g
 
     # ---- end to end through the host-buffer C entry: pinned x in, y out, every layer call ----
     hx = [x[:T].cpu().pin_memory() for x in xs]
@@ -496,50 +583,48 @@ def main():
 
     for _ in range(W):
         e2e_step()
-    if dist is not None:
-        dist.barrier()
     torch.cuda.synchronize()
+    e2e_steps = []
     t0 = time.perf_counter()
     for _ in range(K):
-        e2e_step()
+        t1 = time.perf_counter()
+        e2e_step()                       # every call ends with a stream synchronisation: the step is complete on return
+        e2e_steps.append(time.perf_counter() - t1)
     torch.cuda.synchronize()
     e2e_secs = time.perf_counter() - t0
-    if dist is not None:
-        t = torch.tensor([e2e_secs], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_secs = float(t.item())
     e2e = {"value": world * T * L * K / e2e_secs, "unit": UNIT, "h2d_bytes_per_step": L * T * cfg.H * 4,
-           "d2h_bytes_per_step": L * T * cfg.H * 4, "ms_per_step": 1e3 * e2e_secs / K}
+           "d2h_bytes_per_step": L * T * cfg.H * 4, "ms_per_step": 1e3 * e2e_secs / K,
+           "ms_per_step_stats": pct([1e3 * t for t in e2e_steps]),
+           "how": "chimere_b200_moe_forward_host per layer call: pinned host x copied in, layer, y copied out, stream synchronised; host clock"}
 
     status = max(sc.status() for sc in scratch)
-    prefill = None
-    if rank == 0 and args.prefill_tokens and args.layout == "tiled":
+    secondary, i8 = None, None
+    if args.prefill_tokens != "none" and args.layout == "tiled":
         del graph
-        layers.clear(); scratch.clear(); xs.clear(); ys.clear()
+        layers.clear(); scratch.clear(); xs.clear(); ys.clear(); host_calls.clear()
         torch.cuda.empty_cache()
-        prefill = measure_prefill(lib, dev, [int(t) for t in args.prefill_tokens.split(",") if t])
-    if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
-        return
+        i8 = measure_int8_peak(lib, dev)
+        secondary = measure_secondary(lib, dev, hbm_peak, i8.get("m128_n256_k32", {}).get("tops"), [int(t) for t in args.prefill_tokens.split(",") if t])
 
     cpu = None
     if not args.no_cpu_baseline:
         v, threads, dt = cpu_port_tokens_per_s(cfg, T, 2, min_seconds=10.0)
         cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
                "sample": f"T={T} tokens through 2 layers, repeated for {dt:.1f} s; CPU restatement in oracle/ with OpenMP"}
+        # the reference's own default for its CPU expert path is four threads (moe_ffn.rs:1551, ggml_backend.rs:292-300)
+        v4, t4, dt4 = cpu_port_tokens_per_s(cfg, T, 2, threads=4, min_seconds=6.0)
+        cpu["threads4"] = {"value": v4, "cores": t4, "sample": f"the same sample with 4 threads for {dt4:.1f} s (the reference's default thread count for this path)"}
 
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": 1e3 * secs / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int8 block dots (dp4a), f32 accumulate", "data": "synthetic",
-            "config": dict(workload_config(cfg, T, L), parallelism=("single GPU" if world == 1 else f"{world} independent replicas"),
+            "config": dict(workload_config(cfg, T, L), parallelism="single GPU",
                            timing="CUDA graph replay of one step, CUDA events on the launching stream",
                            weight_layout=args.layout),
+            "ms_per_step_stats": pct([1e3 * t for t in per_step]),
             "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": 3 * L * K, "clocks": clocks,
-            "sweep": sweep, "prefill": prefill, "device_status": status}
+            "sweep": sweep, "int8_peak": i8, "secondary": secondary, "device_status": status}
     print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

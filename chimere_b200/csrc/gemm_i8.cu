@@ -448,6 +448,74 @@ cudaError_t launch_prefill_gemm(const PrefillGemmParams& p, bool down, int n_til
     return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------ tensor-pipe probe ----
+// What the int8 tensor pipe can do when nothing is read back: every CTA (one per SM) keeps issuing
+// tcgen05.mma kind::i8 (M 128, N 128 or 256, K 32) on operands resident in shared memory, accumulating in TMEM,
+// with a commit every 64 instructions and a bounded wait on the last one.  Timed from the host with events, this
+// is the denominator the prefill numbers are stated against (2 * 128 * N * 32 operations per instruction).
+__global__ void __launch_bounds__(128, 1) mma_i8_probe_kernel(int n_mma, int n_cols, int32_t* status) {
+    extern __shared__ __align__(1024) uint8_t smem[];   // A: 128 x 32 int8 (4096 B), B: n_cols x 32 int8
+    __shared__ __align__(8) uint64_t s_bar[2];   // commit groups alternate between the two
+    __shared__ uint32_t s_tmem;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    for (int i = tid; i < (4096 + n_cols * 32) / 4; i += blockDim.x)
+        reinterpret_cast<uint32_t*>(smem)[i] = 0x9E3779B9u * (uint32_t)(i + 1 + blockIdx.x * 977);   // any bytes will do
+    if (tid == 0) { mbar_init(&s_bar[0], 1); mbar_init(&s_bar[1], 1); mbar_fence_init(); }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the operands were written by ordinary stores
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    if (tid == 0) {
+        const uint32_t sa = smem_u32(smem), sb = sa + 4096;
+        const uint32_t lbo_b = (uint32_t)n_cols * 16u;   // K halves of B are n_cols / 8 row groups of 128 bytes apart
+        const uint64_t adesc = smem_desc_kmajor(sa);
+        const uint64_t bdesc = (uint64_t)((sb & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_b >> 4) << 16) | ((uint64_t)(128u >> 4) << 32) | (1ull << 46);
+        const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | (((uint32_t)n_cols >> 3) << 17) | ((128u >> 4) << 24);
+        const int nacc = 512 / n_cols;                   // accumulators taken in turn
+        uint32_t commits = 0;
+        for (int i = 0; i < n_mma; ++i) {
+            const uint32_t d = tmem + (uint32_t)((i % nacc) * n_cols);
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+                ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(i >= nacc ? 1u : 0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+            if ((i & 63) == 63 || i == n_mma - 1) {
+                tc_commit(&s_bar[commits & 1]);
+                // keep at most two commit groups in flight: wait for the one before the one just issued
+                if (commits >= 1) {
+                    const uint32_t c = commits - 1;
+                    if (!mbar_wait(&s_bar[c & 1], (c >> 1) & 1)) { if (status) atomicOr(status, kStatusWaitTimeout); break; }
+                }
+                ++commits;
+            }
+        }
+        if (commits >= 1) {
+            const uint32_t c = commits - 1;
+            if (!mbar_wait(&s_bar[c & 1], (c >> 1) & 1) && status) atomicOr(status, kStatusWaitTimeout);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+// Returns the number of CTAs launched (each issues n_mma instructions), or a negative CUDA error.
+int launch_mma_i8_probe(int n_mma, int n_cols, int32_t* status, cudaStream_t stream) {
+    const int ctas = gemm_grid(1 << 30);
+    const size_t smem = 4096 + (size_t)n_cols * 32 + 1024;
+    mma_i8_probe_kernel<<<ctas, 128, smem, stream>>>(n_mma, n_cols, status);
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? ctas : -100 - (int)e;
+}
+
 // ------------------------------------------------------------------ prefill plumbing kernels ----
 // ggml blocks -> mma128 tiles: int8 values and f32 block scales (IQ3_S: scale = d * (1 + 2*sub-scale), exact in f32).
 // dst row of source row r: plain (mode 0), gate half (mode 1: (r/64)*128 + r%64) or up half (mode 2: ... + 64).

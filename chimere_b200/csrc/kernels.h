@@ -109,6 +109,7 @@ struct GemmParams {
     int32_t* status;
 };
 cudaError_t launch_gemm_i8_f32(const GemmParams& p, int n_items, cudaStream_t stream);
+int launch_mma_i8_probe(int n_mma, int n_cols, int32_t* status, cudaStream_t stream);
 
 // MoE prefill on the GEMM: token tiles built on the device, weights in mma128 form
 struct PrefillGemmParams {
