@@ -190,7 +190,7 @@ def measure_int8_peak(lib, dev):
         for rep in range(4):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            ctas = lib.chimere_b200_mma_i8_probe(n_mma, n_cols, status.data_ptr(), st)
+            ctas = lib.chimere_b200_mma_i8_probe(n_mma, n_cols, 512 // n_cols, status.data_ptr(), st)
             e1.record()
             torch.cuda.synchronize()
             if ctas <= 0:

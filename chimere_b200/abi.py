@@ -79,7 +79,7 @@ PROTOTYPES = {
     "chimere_b200_mma128_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "chimere_b200_pack_mma128": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, _P]),
     "chimere_b200_gemm_i8": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P]),
-    "chimere_b200_mma_i8_probe": (C.c_int, [C.c_int, C.c_int, _P, _P]),
+    "chimere_b200_mma_i8_probe": (C.c_int, [C.c_int, C.c_int, C.c_int, _P, _P]),
     "chimere_b200_moe_pack_prefill_bytes": (C.c_size_t, [_LAYER_P]),
     "chimere_b200_moe_pack_prefill": (C.c_int, [_LAYER_P, _P, C.c_size_t, C.POINTER(PrefillWeights), _P]),
     "chimere_b200_moe_prefill_bytes": (C.c_size_t, [_LAYER_P, C.c_int]),

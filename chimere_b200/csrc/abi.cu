@@ -495,9 +495,9 @@ int chimere_b200_gemm_i8(const void* d_a, const void* d_b, int rows, int tokens,
     return cuda_rc(launch_gemm_i8_f32(p, (int)items.size(), stream));
 }
 
-int chimere_b200_mma_i8_probe(int n_mma, int n_cols, int32_t* d_status, cudaStream_t stream) {
-    if (n_mma <= 0 || (n_cols != 128 && n_cols != 256)) return -2;
-    return launch_mma_i8_probe(n_mma, n_cols, d_status, stream);
+int chimere_b200_mma_i8_probe(int n_mma, int n_cols, int n_acc, int32_t* d_status, cudaStream_t stream) {
+    if (n_mma <= 0 || n_mma % 64 || (n_cols != 128 && n_cols != 256) || n_acc < 1 || n_acc * n_cols > 512) return -2;
+    return launch_mma_i8_probe(n_mma, n_cols, n_acc, d_status, stream);
 }
 
 // ---------------------------------------------------------------- prefill path ----

@@ -403,14 +403,7 @@ cudaError_t launch_pack_mma128(const int8_t* q, const float* scales, uint8_t* ou
 
 // persistent CTAs: one per SM of the current device, or fewer when there are fewer tiles
 static int gemm_grid(int n_items) {
-    static int n_sm_of[64] = {};
-    int dev = 0, n_sm = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
-    if (dev >= 0) n_sm = n_sm_of[dev];
-    if (!n_sm) {
-        if (dev < 0 || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
-        if (dev >= 0) n_sm_of[dev] = n_sm;
-    }
+    const int n_sm = sm_count();
     return n_items < n_sm ? n_items : n_sm;
 }
 constexpr size_t kG_RingBytes = (size_t)kG_Stages * kG_StageBytes;
@@ -453,7 +446,7 @@ cudaError_t launch_prefill_gemm(const PrefillGemmParams& p, bool down, int n_til
 // tcgen05.mma kind::i8 (M 128, N 128 or 256, K 32) on operands resident in shared memory, accumulating in TMEM,
 // with a commit every 64 instructions and a bounded wait on the last one.  Timed from the host with events, this
 // is the denominator the prefill numbers are stated against (2 * 128 * N * 32 operations per instruction).
-__global__ void __launch_bounds__(128, 1) mma_i8_probe_kernel(int n_mma, int n_cols, int32_t* status) {
+__global__ void __launch_bounds__(128, 1) mma_i8_probe_kernel(int n_mma, int n_cols, int n_acc, int32_t* status) {
     extern __shared__ __align__(1024) uint8_t smem[];   // A: 128 x 32 int8 (4096 B), B: n_cols x 32 int8
     __shared__ __align__(8) uint64_t s_bar[2];   // commit groups alternate between the two
     __shared__ uint32_t s_tmem;
@@ -476,28 +469,30 @@ __global__ void __launch_bounds__(128, 1) mma_i8_probe_kernel(int n_mma, int n_c
         const uint64_t adesc = smem_desc_kmajor(sa);
         const uint64_t bdesc = (uint64_t)((sb & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_b >> 4) << 16) | ((uint64_t)(128u >> 4) << 32) | (1ull << 46);
         const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | (((uint32_t)n_cols >> 3) << 17) | ((128u >> 4) << 24);
-        const int nacc = 512 / n_cols;                   // accumulators taken in turn
-        uint32_t commits = 0;
-        for (int i = 0; i < n_mma; ++i) {
-            const uint32_t d = tmem + (uint32_t)((i % nacc) * n_cols);
+        auto mma = [&](uint32_t d, uint32_t acc) {
             asm volatile(
                 "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-                ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(i >= nacc ? 1u : 0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
-            if ((i & 63) == 63 || i == n_mma - 1) {
-                tc_commit(&s_bar[commits & 1]);
-                // keep at most two commit groups in flight: wait for the one before the one just issued
-                if (commits >= 1) {
-                    const uint32_t c = commits - 1;
-                    if (!mbar_wait(&s_bar[c & 1], (c >> 1) & 1)) { if (status) atomicOr(status, kStatusWaitTimeout); break; }
-                }
-                ++commits;
+                ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+        };
+        // accumulators taken in turn (n_acc of them, n_cols columns each); groups of 64 instructions per commit
+        uint32_t dcol[4];
+        for (int j = 0; j < 4; ++j) dcol[j] = tmem + (uint32_t)((j % n_acc) * n_cols);
+        const int groups = (n_mma + 63) / 64;
+        bool ok = true;
+        for (int g = 0; g < groups && ok; ++g) {
+#pragma unroll 4
+            for (int j = 0; j < 64; j += 4) {
+                mma(dcol[0], g > 0 || j >= 4 ? 1u : 0u);
+                mma(dcol[1], g > 0 || j >= 4 ? 1u : 0u);
+                mma(dcol[2], g > 0 || j >= 4 ? 1u : 0u);
+                mma(dcol[3], g > 0 || j >= 4 ? 1u : 0u);
             }
+            tc_commit(&s_bar[g & 1]);
+            // at most two commit groups in flight: wait for the one before the one just issued
+            if (g >= 1 && !mbar_wait(&s_bar[(g - 1) & 1], ((g - 1) >> 1) & 1)) { if (status) atomicOr(status, kStatusWaitTimeout); ok = false; }
         }
-        if (commits >= 1) {
-            const uint32_t c = commits - 1;
-            if (!mbar_wait(&s_bar[c & 1], (c >> 1) & 1) && status) atomicOr(status, kStatusWaitTimeout);
-        }
+        if (ok && groups >= 1 && !mbar_wait(&s_bar[(groups - 1) & 1], ((groups - 1) >> 1) & 1) && status) atomicOr(status, kStatusWaitTimeout);
     }
     tc_fence_before();
     __syncthreads();
@@ -507,11 +502,11 @@ __global__ void __launch_bounds__(128, 1) mma_i8_probe_kernel(int n_mma, int n_c
     }
 }
 
-// Returns the number of CTAs launched (each issues n_mma instructions), or a negative CUDA error.
-int launch_mma_i8_probe(int n_mma, int n_cols, int32_t* status, cudaStream_t stream) {
+// Returns the number of CTAs launched (each issues n_mma instructions, rounded up to a multiple of 64), or a negative CUDA error.
+int launch_mma_i8_probe(int n_mma, int n_cols, int n_acc, int32_t* status, cudaStream_t stream) {
     const int ctas = gemm_grid(1 << 30);
     const size_t smem = 4096 + (size_t)n_cols * 32 + 1024;
-    mma_i8_probe_kernel<<<ctas, 128, smem, stream>>>(n_mma, n_cols, status);
+    mma_i8_probe_kernel<<<ctas, 128, smem, stream>>>(n_mma, n_cols, n_acc, status);
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? ctas : -100 - (int)e;
 }

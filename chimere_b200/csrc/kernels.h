@@ -109,7 +109,7 @@ struct GemmParams {
     int32_t* status;
 };
 cudaError_t launch_gemm_i8_f32(const GemmParams& p, int n_items, cudaStream_t stream);
-int launch_mma_i8_probe(int n_mma, int n_cols, int32_t* status, cudaStream_t stream);
+int launch_mma_i8_probe(int n_mma, int n_cols, int n_acc, int32_t* status, cudaStream_t stream);
 
 // MoE prefill on the GEMM: token tiles built on the device, weights in mma128 form
 struct PrefillGemmParams {
@@ -158,6 +158,17 @@ inline cudaError_t max_smem_once(K kernel, int bytes, bool (&done)[64]) {
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e == cudaSuccess) done[dev] = true;
     return e;
+}
+
+// Number of SMs of the current device (cached per device).
+inline int sm_count() {
+    static int n_sm_of[64] = {};
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+    if (dev >= 0 && n_sm_of[dev]) return n_sm_of[dev];
+    if (dev < 0 || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    if (dev >= 0) n_sm_of[dev] = n;
+    return n;
 }
 
 // Launch with programmatic stream serialization: the grid may start while the previous kernel of the stream is

@@ -241,12 +241,13 @@ int chimere_b200_pack_mma128(const int8_t* d_q, const float* d_scales, void* d_o
 int chimere_b200_gemm_i8(const void* d_a, const void* d_b, int rows, int tokens, int cols, float* d_out,
                          void* d_items, int32_t* d_status, cudaStream_t stream);
 
-/* Measurement aid: what the int8 tensor pipe of this GPU sustains with no read-back.  One CTA per SM issues n_mma
- * tcgen05.mma kind::i8 instructions (M 128, N n_cols = 128 or 256, K 32) on operands resident in shared memory.
+/* Measurement aid: what the int8 tensor pipe of this GPU sustains with no read-back.  One CTA per SM issues n_mma (a
+ * multiple of 64) tcgen05.mma kind::i8 instructions (M 128, N n_cols = 128 or 256, K 32) on operands resident in
+ * shared memory, into n_acc accumulators taken in turn (n_acc * n_cols <= 512 TMEM columns).
  * Returns the number of CTAs launched (operations = CTAs * n_mma * 2 * 128 * n_cols * 32), or < 0 on error; the
  * caller times the stream.  d_status (may be NULL): raised if a bounded wait ran out.  No counterpart in the
  * reference (it has no tensor-core kernel). */
-int chimere_b200_mma_i8_probe(int n_mma, int n_cols, int32_t* d_status, cudaStream_t stream);
+int chimere_b200_mma_i8_probe(int n_mma, int n_cols, int n_acc, int32_t* d_status, cudaStream_t stream);
 
 /* ------------------------------------------------------------ prefill-size batches -------- */
 /* For many tokens per call the expert products run as grouped block-scaled int8 GEMMs on the tensor cores
