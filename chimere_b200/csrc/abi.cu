@@ -487,12 +487,15 @@ int chimere_b200_gemm_i8(const void* d_a, const void* d_b, int rows, int tokens,
         }
     cudaError_t e = cudaMemcpyAsync(d_items, items.data(), items.size() * sizeof(GemmItem), cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) return cuda_rc(e);
+    int32_t* counter = (int32_t*)((uint8_t*)d_items + items.size() * sizeof(GemmItem));   // the tile counter sits behind the list
+    e = cudaMemsetAsync(counter, 0, 256, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
     e = cudaStreamSynchronize(stream);   // the host vector goes away; this entry is a test primitive, not the hot path
     if (e != cudaSuccess) return cuda_rc(e);
     GemmParams p{};
     p.a_base = (const uint8_t*)d_a; p.b_base = (const uint8_t*)d_b; p.items = (const GemmItem*)d_items; p.nblocks = nb;
     p.out = d_out; p.ldo = tokens; p.status = d_status;
-    return cuda_rc(launch_gemm_i8_f32(p, (int)items.size(), stream));
+    return cuda_rc(launch_gemm_i8_f32(p, (int)items.size(), counter, stream));
 }
 
 int chimere_b200_mma_i8_probe(int n_mma, int n_cols, int n_acc, int32_t* d_status, cudaStream_t stream) {
@@ -542,7 +545,7 @@ PrefillArena prefill_arena(const chimere_moe_layer* w, int T) {
     A.bx_stride = (int64_t)(w->H / 32) * kMmaTile;
     A.b2_stride = (int64_t)(Fmax / 32) * kMmaTile;
     size_t o = 0;
-    A.tiles = o; o += up256((size_t)(4 + 4 * A.n_tiles_max) * 4);
+    A.tiles = o; o += up256((size_t)(8 + 4 * A.n_tiles_max) * 4);
     A.bx = o; o += up256((size_t)A.n_tiles_max * A.bx_stride);
     A.b2 = o; o += up256((size_t)A.n_tiles_max * A.b2_stride);
     A.total = o;
@@ -613,7 +616,10 @@ int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_m
     if (e != cudaSuccess) return cuda_rc(e);
     // the small experts: GEMV kernels on the rewritten work list, per-pair rows only
     // (the shared expert is not on this list: the kernels are sized for the routed matrices alone)
-    const int max_entries = max_entries_for(w, T);
+    // every expert on this list has fewer than kGemmMin <= kMaxGroupTokens pairs, i.e. one entry; the grid is sized for that,
+    // not for the worst case of the all-GEMV path
+    static_assert(kGemmMin <= kMaxGroupTokens, "a small expert must fit one work entry");
+    const int max_entries = w->E < T * w->top_k ? w->E : T * w->top_k;
     GemvParams gu = gate_up_params(w, T, ws, L);
     gu.nrows_shared = 0; gu.ncols_shared = 0; gu.sh_a = nullptr; gu.sh_b = nullptr;
     e = launch_gate_up_tiled(gu, max_entries, stream);

@@ -108,12 +108,12 @@ struct GemmParams {
     float* out; int64_t ldo;                        // f32 output, row pitch in floats
     int32_t* status;
 };
-cudaError_t launch_gemm_i8_f32(const GemmParams& p, int n_items, cudaStream_t stream);
+cudaError_t launch_gemm_i8_f32(const GemmParams& p, int n_items, int32_t* tile_counter, cudaStream_t stream);
 int launch_mma_i8_probe(int n_mma, int n_cols, int n_acc, int32_t* status, cudaStream_t stream);
 
 // MoE prefill on the GEMM: token tiles built on the device, weights in mma128 form
 struct PrefillGemmParams {
-    const int32_t* tiles;            // tile list (word 0 = count)
+    const int32_t* tiles;            // tile list (word 0 = count, words 4 / 5 = tile counters of the gate/up / down launch, tiles from word 8)
     const int32_t* perm;
     const uint8_t* a_exps; int64_t stride_a;   // routed experts' mma128 matrices
     const uint8_t* sh_a;                       // shared expert's

@@ -233,8 +233,10 @@ int chimere_b200_block_sumi_tiled(int wtype, const void* d_packed, const void* d
  * block arithmetic of the reference's Q8_0 x Q8_1 dot (src/kernels/gemv_q8_0.rs:230-255) for many tokens at
  * once.  The reference has no prefill kernel of its own (it loops tokens, compute_graph.rs:1787-1808).
  * Operands are int8 matrices [rows][cols] / [tokens][cols] with f32 block scales, rewritten by
- * chimere_b200_pack_mma128 into the MMA's shared-memory order.  d_items: scratch for ceil(rows/128) *
- * ceil(tokens/128) * 32 bytes.  This entry synchronises the stream once (it stages its tile list). */
+ * chimere_b200_pack_mma128 into the MMA's shared-memory order.  The scales of the rows (d_a) must have at most 22
+ * significant bits -- every ggml scale, an f16 times a small integer, has -- for the per-block scaling to round once.
+ * d_items: scratch for ceil(rows/128) * ceil(tokens/128) * 32 + 256 bytes.  This entry synchronises the stream once
+ * (it stages its tile list). */
 size_t chimere_b200_mma128_bytes(int rows, int cols);
 int chimere_b200_pack_mma128(const int8_t* d_q, const float* d_scales, void* d_out, int rows, int cols,
                              cudaStream_t stream);

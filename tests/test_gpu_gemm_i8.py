@@ -24,11 +24,12 @@ def _run(rows, tokens, cols, unit_scales):
     if unit_scales:
         sa, sb = torch.ones(rows, nb, device="cuda"), torch.ones(tokens, nb, device="cuda")
     else:
-        sa = torch.rand(rows, nb, generator=g, device="cuda") * 0.01 + 0.001
+        # weight-side scales as ggml has them: an f16 value (times a small odd factor, as IQ3_S sub-blocks do)
+        sa = (torch.rand(rows, nb, generator=g, device="cuda") * 0.01 + 0.001).half().float() * (1 + 2 * torch.randint(0, 16, (rows, nb), generator=g, device="cuda"))
         sb = torch.rand(tokens, nb, generator=g, device="cuda") * 0.05 + 0.001
     pa, pb = _pack(lib, A, sa), _pack(lib, B, sb)
     out = torch.full((rows, tokens), float("nan"), device="cuda")
-    items = torch.zeros(((rows + 127) // 128) * ((tokens + 127) // 128) * 32, dtype=torch.uint8, device="cuda")
+    items = torch.zeros(((rows + 127) // 128) * ((tokens + 127) // 128) * 32 + 256, dtype=torch.uint8, device="cuda")
     status = torch.zeros(64, dtype=torch.int32, device="cuda")
     abi.check(lib.chimere_b200_gemm_i8(pa.data_ptr(), pb.data_ptr(), rows, tokens, cols, out.data_ptr(), items.data_ptr(),
                                        status.data_ptr(), None), "gemm_i8")
@@ -41,13 +42,13 @@ def _run(rows, tokens, cols, unit_scales):
     return out, ref
 
 
-@pytest.mark.parametrize("rows,tokens,cols", [(128, 128, 128), (256, 200, 512), (192, 37, 2048)])
+@pytest.mark.parametrize("rows,tokens,cols", [(128, 128, 128), (256, 200, 512), (192, 37, 2048), (384, 20, 256), (128, 50, 96), (2048, 1100, 512)])
 def test_integer_dots_exact_with_unit_scales(rows, tokens, cols):
     out, ref = _run(rows, tokens, cols, unit_scales=True)
     assert torch.equal(out.double(), ref), "unit scales: every output is an integer below 2^24 and must be exact"
 
 
-@pytest.mark.parametrize("rows,tokens,cols", [(256, 200, 512), (512, 128, 2048)])
+@pytest.mark.parametrize("rows,tokens,cols", [(256, 200, 512), (512, 128, 2048), (256, 60, 1024), (256, 9, 160)])
 def test_block_scaled_result(rows, tokens, cols):
     out, ref = _run(rows, tokens, cols, unit_scales=False)
     rel = (out.double() - ref).abs().max() / ref.abs().max()
