@@ -84,6 +84,8 @@ PROTOTYPES = {
     "chimere_b200_moe_pack_prefill": (C.c_int, [_LAYER_P, _P, C.c_size_t, C.POINTER(PrefillWeights), _P]),
     "chimere_b200_moe_prefill_bytes": (C.c_size_t, [_LAYER_P, C.c_int]),
     "chimere_b200_moe_forward_prefill": (C.c_int, [_LAYER_P, C.POINTER(PrefillWeights), _P, _P, C.c_int, _WS_P, _P]),
+    "chimere_b200_moe_forward_residual_norm": (C.c_int, [_LAYER_P, C.POINTER(PrefillWeights), _P, _P, _P, C.c_float, _P, C.c_int, _WS_P, _P]),
+    "chimere_b200_moe_routing_trace": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P, _P, _P]),
     "chimere_b200_rmsnorm": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_float, _P]),
     "chimere_b200_abi_version": (C.c_int, []),
     "chimere_b200_built_for_sm": (C.c_int, []),

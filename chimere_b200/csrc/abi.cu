@@ -156,6 +156,12 @@ static RouteParams route_params(const chimere_moe_layer* w, const float* d_x, in
     p.perm = ws->perm; p.offsets = ws->offsets; p.group_list = ws->group_list; p.counters = ws->counters;
     p.x_soa_q = ws->x_q; p.x_soa_d = ws->x_d; p.x_soa_d_stride = (w->H / 32 + 3) & ~3;
     p.status = ws->status;
+    // the dispatch of a large batch counts in the memory of the down stage's combine counters (zero between the stages'
+    // uses, and large enough from a few dozen tokens on)
+    const Layout L = make_layout(w, ws->max_T);
+    const size_t combine_ints = (size_t)L.n_counters - kCtrRouteTile - (ws->max_T + 7) / 8;
+    const size_t need = (size_t)((T * w->top_k + 127) / 128) * 256 + 260;
+    p.dispatch_scratch = need <= combine_ints ? ws->counters + kCtrRouteTile + (ws->max_T + 7) / 8 : nullptr;
     return p;
 }
 
@@ -655,6 +661,27 @@ int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_m
     const float* shared_rows = w->F_s > 0 ? ws->pair_out + (size_t)T * w->top_k * w->H : nullptr;
     const float* logit = (w->F_s > 0 && w->shexp_gate_w) ? ws->sh_gate_logit : nullptr;
     return cuda_rc(launch_ep_finish(ws->pair_out, nullptr, ws->topk_w, shared_rows, logit, d_y, T, w->H, w->top_k, stream));
+}
+
+int chimere_b200_moe_forward_residual_norm(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, const float* d_hidden,
+                                           float* d_residual, const float* d_norm_weight, float eps, float* d_y, int T,
+                                           chimere_moe_workspace* ws, cudaStream_t stream) {
+    int rc = check_call(w, d_hidden, d_y, T, ws);
+    if (rc) return rc;
+    if (!d_residual || !d_norm_weight || !ws->pair_out) return -1;
+    // the normalised rows live in the first T rows of the per-pair output area until the router and the Q8_1 step have
+    // read them; the down stage writes that area only afterwards
+    float* normed = ws->pair_out;
+    cudaError_t e = launch_add_residual_rmsnorm(d_hidden, d_residual, d_norm_weight, normed, T, w->H, eps, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    return pw ? chimere_b200_moe_forward_prefill(w, pw, normed, d_y, T, ws, stream) : chimere_b200_moe_forward(w, normed, d_y, T, ws, stream);
+}
+
+int chimere_b200_moe_routing_trace(const chimere_moe_layer* w, int T, const chimere_moe_workspace* ws, uint8_t* d_trace,
+                                   int32_t* d_expert_load, cudaStream_t stream) {
+    if (!w || !ws || !ws->topk_idx || !d_trace) return -1;
+    if (T <= 0 || T > ws->max_T || w->top_k <= 0 || w->top_k > kMaxTopK || w->E <= 0 || w->E > kMaxExperts) return -2;
+    return cuda_rc(launch_routing_trace(ws->topk_idx, d_trace, d_expert_load, T, w->top_k, w->E, stream));
 }
 
 int chimere_b200_rmsnorm(const float* d_x, float* d_y, int T, int H, float eps, cudaStream_t stream) {

@@ -90,10 +90,6 @@ __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sy
 // 12582912 + v exactly.  The subtraction of 12582912 is folded into the first scaling step (see block_piece).
 constexpr uint32_t kMagicBits = 0x4B400000u;
 constexpr float kMagic = 12582912.0f;
-// two fp32 lanes in one 64-bit register (sm_100 has two-wide fp32 add / mul / fma)
-__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi)); return r; }
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) { uint64_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
 
 struct GemmShared {
     uint64_t full[kG_Stages];        // stage bytes have landed
@@ -129,7 +125,6 @@ __device__ __forceinline__ bool epilogue_meet(GemmShared& sh, uint32_t& phase, i
     return ok;
 }
 
-__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) { uint64_t d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
 // two 64-bit words (four floats) from a 32-bit shared address, the same for every lane
 __device__ __forceinline__ void lds_2x64(uint32_t a, uint64_t& x, uint64_t& y) { asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(x), "=l"(y) : "r"(a)); }
 __device__ __forceinline__ float lds_f32(uint32_t a) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a)); return v; }

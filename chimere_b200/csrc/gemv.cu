@@ -395,6 +395,41 @@ __global__ void rmsnorm_kernel(const float* x, float* y, int H, float eps) {
     for (int i = threadIdx.x; i < H; i += blockDim.x) y[(size_t)blockIdx.x * H + i] = xr[i] * inv;
 }
 
+// residual += hidden; normed = residual / sqrt(mean(residual^2) + eps) * weight, one CTA of 256 per token row.
+// fused_add_residual_rmsnorm (chimere-server/src/kernels/fused_ops.rs:91-140) for T rows at once, in its order:
+// thread i sums the squares of elements i, i+256, ... (one fused multiply-add each), the 256 sums meet in a tree
+// of strides 128 .. 1, and every element is scaled as (residual * inv_rms) * weight.
+__global__ void __launch_bounds__(256) add_residual_rmsnorm_kernel(const float* hidden, float* residual, const float* weight, float* normed,
+                                                                   int H, float eps) {
+    __shared__ float s_sum[256];
+    griddep_wait();                       // the rows may come from the previous kernel of the stream
+    if (threadIdx.x == 0) griddep_launch();
+    const int tid = threadIdx.x;
+    const float* h = hidden + (size_t)blockIdx.x * H;
+    float* r = residual + (size_t)blockIdx.x * H;
+    float sum_sq = 0.0f;
+    for (int i = tid; i < H; i += 256) {
+        const float val = h[i] + r[i];
+        r[i] = val;
+        sum_sq = fmaf(val, val, sum_sq);
+    }
+    s_sum[tid] = sum_sq;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (tid < s) s_sum[tid] += s_sum[tid + s];
+        __syncthreads();
+    }
+    const float rms = sqrtf(s_sum[0] / (float)H + eps);
+    const float inv_rms = 1.0f / rms;
+    for (int i = tid; i < H; i += 256) normed[(size_t)blockIdx.x * H + i] = r[i] * inv_rms * weight[i];
+}
+
+cudaError_t launch_add_residual_rmsnorm(const float* hidden, float* residual, const float* weight, float* normed, int T, int H, float eps,
+                                        cudaStream_t stream) {
+    if (T <= 0) return cudaSuccess;
+    return launch_pdl(add_residual_rmsnorm_kernel, dim3(T), 256, 0, stream, hidden, residual, weight, normed, H, eps);
+}
+
 // ------------------------------------------------------------------ launchers --------------
 constexpr int kSmemCap = 200 * 1024;
 

@@ -34,6 +34,8 @@ struct RouteParams {
     int32_t* group_list;
     int32_t* counters;
     int32_t* status;            // workspace status word (may be null): a bounded wait that ran out raises a bit here
+    int32_t* dispatch_scratch;  // zeroed scratch for the dispatch of large batches: ceil(T*top_k / 128) * 256 + 260 ints, left
+                                // zeroed again; null = always sort in one CTA
 };
 
 // Grouped GEMV over work entries (see common.cuh for the list layout).
@@ -96,6 +98,10 @@ cudaError_t launch_block_sumi(int wtype, const void* w, const void* xq8, int32_t
 cudaError_t launch_quantize_q8_1(const float* x, void* out, int64_t ncols, int64_t ncols_padded, int batch,
                                  cudaStream_t stream);
 cudaError_t launch_rmsnorm(const float* x, float* y, int T, int H, float eps, cudaStream_t stream);
+cudaError_t launch_add_residual_rmsnorm(const float* hidden, float* residual, const float* weight, float* normed, int T, int H, float eps,
+                                        cudaStream_t stream);
+// routing trace: ids as bytes [T][k] for the drafter tooling, and (optional) per-expert pair counts added into load[E]
+cudaError_t launch_routing_trace(const int32_t* topk_idx, uint8_t* trace, int32_t* load, int T, int k, int E, cudaStream_t stream);
 int down_tile_rows(int type_routed, int ncols_routed, int type_shared, int ncols_shared);
 
 // block-scaled int8 GEMM on tcgen05 (gemm_i8.cu); operands in the mma128 layout

@@ -131,6 +131,9 @@ __device__ void topk_warp(const RouteParams& p, const float* logit_row, int t, i
 // barriers are between those steps, however many pairs there are.  The work entries are then filled by all
 // threads (entry -> expert by bisection of the entry offsets).
 constexpr int kDispatchSmemInts = 256 + 256 + 2048 + 32 + 288 + 1024;
+// The dispatch step is written for 256 threads; in a larger CTA only the first 256 threads call it, so its meeting
+// point is a named barrier of those threads (in a CTA of 256 it is the same as a CTA-wide barrier).
+__device__ __forceinline__ void dispatch_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
 // ids_room: ints of shared memory behind the kDispatchSmemInts of scratch; if the ids fit there they are fetched
 // once, all loads in flight together, instead of one dependent load per step of the two passes.
 __device__ void build_dispatch(const RouteParams& p, int* smem_i, const int* s_ids, int ids_room) {
@@ -150,7 +153,7 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i, const int* s_i
     int* s_perm = smem_i + 2880;      // [1024] copy of the permutation when it is that short
     const bool perm_in_smem = P <= 1024;
     for (int i = tid; i < 2048; i += 256) warp_cnt[i] = 0;
-    __syncthreads();
+    dispatch_sync();
     // ids outside [0, E) mark pairs that are not there (padding of a fixed-size exchange): they get no work
     const int istr = p.idx_stride > 1 ? p.idx_stride : 1;
     const int chunk = (((P + 7) >> 3) + 31) & ~31;
@@ -164,7 +167,7 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i, const int* s_i
         if (valid && (same & ((1u << lane) - 1u)) == 0u) warp_cnt[warp * 256 + e] += __popc(same);
         __syncwarp();
     }
-    __syncthreads();
+    dispatch_sync();
     // thread = expert: its pair count, and where each warp's pairs start within it
     int cnt = 0;
     if (tid < E) {
@@ -185,7 +188,7 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i, const int* s_i
         if (lane >= s) { incl_c += a; incl_n += b; }
     }
     if (lane == 31) { scan[warp] = incl_c; scan[8 + warp] = incl_n; }
-    __syncthreads();
+    dispatch_sync();
     int base_c = 0, base_n = 0;
     for (int w = 0; w < warp; ++w) { base_c += scan[w]; base_n += scan[8 + w]; }
     const int off = base_c + incl_c - cnt;      // exclusive
@@ -216,7 +219,7 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i, const int* s_i
         p.group_list[2] = nsh_listed;
         p.group_list[3] = 0;
     }
-    __syncthreads();   // cursor and the warps' first positions are in place
+    dispatch_sync();   // cursor and the warps' first positions are in place
     // stable placement: each warp walks its pairs in order
     for (int base = q0; base < q1; base += 32) {
         const int q = base + lane;
@@ -234,7 +237,7 @@ __device__ void build_dispatch(const RouteParams& p, int* smem_i, const int* s_i
         if (valid && rank == 0) warp_cnt[warp * 256 + e] += __popc(same);
         __syncwarp();
     }
-    __syncthreads();
+    dispatch_sync();
     // the routed entries with their pair rows (perm was written by this CTA: visible after the barrier above)
     for (int idx = tid; idx < total_routed; idx += 256) {
         int lo = 0, hi = 256;   // ent_base[lo] <= idx < ent_base[hi]
@@ -367,103 +370,158 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
     build_dispatch(p, reinterpret_cast<int*>(smem_f), nullptr, (int)(TT * TE * 256) - kDispatchSmemInts);
 }
 
-// Q8_1 of all input rows, one warp per 32-element block (large batches: the router kernel below does not do it).
-__global__ void __launch_bounds__(256) quantize_rows_kernel(const RouteParams p) {
-    const int lane = threadIdx.x & 31, nbH = p.H >> 5;
-    const int64_t q = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (q >= (int64_t)p.T * nbH) return;
-    const int t = (int)(q / nbH), b = (int)(q - (int64_t)t * nbH);
-    quantize_block_q8_1(p.x[(size_t)t * p.H + b * 32 + lane], p.x_q8 + ((size_t)t * nbH + b) * kQ81Bytes, lane,
-                        p.x_soa_q + (size_t)t * p.H + b * 32, p.x_soa_d + (size_t)t * p.x_soa_d_stride + b);
+// Larger batches.  The order of the additions is fixed (256 partial sums per output, tree of strides 128 .. 1), so
+// a thread can only ever own one partial of an output, and the operands of an output tile have to pass through the
+// SM once per tile: the kernel is bound by how many outputs a CTA can hold per router row it fetches.
+// CTA = 512 threads = two token groups of 256 threads.  Thread (g, p) keeps elements p, p+256, ... of eight token
+// rows in registers (sixteen tokens per CTA) and owns partial p of every output of its group; the router rows come
+// four at a time through a ring of bulk copies shared by both groups, so every fetched row feeds sixteen tokens.
+// The 64 x 256 partial sums of a step are left in shared memory and summed by the sixteen warps, four outputs each,
+// in the reference's order.  A CTA whose row group starts at row 0
+// also writes the Q8_1 form of its tokens, from the values it holds anyway.
+// grid = (row groups, token tiles of 16); NC = ceil(H / 256) <= 8 columns per thread; H a multiple of 32.
+constexpr int kBigTT = 8, kBigTE = 4, kBigThreads = 512, kBigRing = 4;
+constexpr int kBigRedFloats = 2 * kBigTT * kBigTE * 256;                 // [group][token][row][256] partial sums of one step
+static size_t big_route_smem(int H) { return (size_t)(kBigRedFloats + kBigRing * kBigTE * H) * sizeof(float); }
+// The same tree for two outputs whose partials are interleaved (partial i of the pair at r[2 * i], r[2 * i + 1]): one
+// 64-bit load serves both, two-wide adds keep each lane's order.  Valid in lane 0.
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) { uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ void tree256_pair(const float* r, int lane, float& v0, float& v1) {
+    const uint64_t* q = reinterpret_cast<const uint64_t*>(r);
+    const uint64_t a0 = add2(q[lane], q[lane + 128]);
+    const uint64_t a1 = add2(q[lane + 32], q[lane + 160]);
+    const uint64_t a2 = add2(q[lane + 64], q[lane + 192]);
+    const uint64_t a3 = add2(q[lane + 96], q[lane + 224]);
+    const uint64_t b0 = add2(a0, a2);
+    const uint64_t b1 = add2(a1, a3);
+    unpack2(add2(b0, b1), v0, v1);
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        v0 += __shfl_down_sync(0xffffffffu, v0, s);
+        v1 += __shfl_down_sync(0xffffffffu, v1, s);
+    }
 }
 
-// Larger batches: a CTA keeps its token tile's input columns in registers (thread p: elements p, p+256, ... of TT
-// rows) and walks over a group of router rows two at a time.  The rows come through a ring of bulk copies into
-// shared memory (one thread asks, four pairs ahead), so no load latency sits between the multiply-adds; every row
-// element is read once per token tile and the input once per CTA.  The order of the additions is the same as in
-// route_kernel.  grid = (row groups, token tiles), NC = ceil(H / 256) columns per thread; H a multiple of 4.
-constexpr int kBigRouteSmemInts = 24 * 1024;   // 96 KiB: partial sums + row ring; later the dispatch scratch and the staged ids
-constexpr int kBigRing = 4;
-template <int TT, int NC>
-__global__ void __launch_bounds__(256, 2) route_big_kernel(const RouteParams p, int rows_per_group) {
-    extern __shared__ __align__(16) float smem_f[];   // [2][TT * 2][256] partial sums, then [kBigRing][2][H] router rows
+// EXACT: H == NC * 256 (the common case, H = 2048): no bounds tests and constant offsets in the inner loop.
+// The partial sums of two neighbouring tokens travel together (two-wide fused multiply-adds, each lane rounded like the
+// scalar instruction), so the sums of a step sit in shared memory as [group][token pair][row][partial][2].
+template <int NC, bool EXACT>
+__global__ void __launch_bounds__(kBigThreads, 1) route_big_kernel(const RouteParams p, int rows_per_group, int split_dispatch) {
+    extern __shared__ __align__(16) float smem_f[];   // [kBigRedFloats] partial sums, then [kBigRing][kBigTE][H] router rows
     __shared__ __align__(8) uint64_t s_full[kBigRing];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int H = p.H, E = p.E;
+    const int g = tid >> 8, pt = tid & 255;
+    const int H = EXACT ? NC * 256 : p.H, E = p.E;
     const int nrows = E + (p.shexp_gate_w ? 1 : 0);
-    const int t0 = blockIdx.y * TT;
+    const int t0 = blockIdx.y * (2 * kBigTT) + g * kBigTT;
     const int r_begin = blockIdx.x * rows_per_group, r_end = min(nrows, r_begin + rows_per_group);
-    const int npairs = (r_end - r_begin + 1) / 2;
+    const int nsteps = (r_end - r_begin + kBigTE - 1) / kBigTE;
     if (tid == 0) griddep_launch();
-    float* ring = smem_f + 2 * TT * 2 * 256;
+    float* ring = smem_f + kBigRedFloats;
     auto wrow = [&](int r) -> const float* { return r < E ? p.router_w + (size_t)r * H : p.shexp_gate_w; };
-    // thread 0: rows of pair k into ring slot k % kBigRing (a missing second row is not copied and not used)
+    // thread 0: the rows of step k into ring slot k % kBigRing (rows past r_end are not copied; what the slot holds in
+    // their place is multiplied and never stored)
     auto ask = [&](int k) {
-        const int r = r_begin + 2 * k, slot = k % kBigRing;
+        const int r = r_begin + kBigTE * k, slot = k % kBigRing;
         const uint32_t bytes = (uint32_t)H * 4u;
-        const int n = (r + 1 < r_end) ? 2 : 1;
+        const int n = min(kBigTE, r_end - r);
         mbar_expect_tx(&s_full[slot], bytes * n);
-        bulk_g2s(ring + (size_t)slot * 2 * H, wrow(r), bytes, &s_full[slot]);
-        if (n == 2) bulk_g2s(ring + (size_t)slot * 2 * H + H, wrow(r + 1), bytes, &s_full[slot]);
+        for (int b = 0; b < n; ++b) bulk_g2s(ring + ((size_t)slot * kBigTE + b) * H, wrow(r + b), bytes, &s_full[slot]);
     };
     if (tid == 0) {
         for (int i = 0; i < kBigRing; ++i) mbar_init(&s_full[i], 1);
         mbar_fence_init();
-        for (int k = 0; k < kBigRing && k < npairs; ++k) ask(k);
+        for (int k = 0; k < kBigRing && k < nsteps; ++k) ask(k);
     }
-    float xv[TT][NC];
+    // what is added to a row's sums before they are stored (a load from global memory at that point would put a trip
+    // to L2 behind every output of every step)
+    __shared__ float s_bias[kMaxExperts + 1];
+    for (int e = tid; e <= kMaxExperts; e += kBigThreads) s_bias[e] = (p.router_bias && e < E) ? p.router_bias[e] : 0.0f;
+    uint64_t xv2[kBigTT / 2][NC];   // elements pt + 256 i of tokens (2 a2, 2 a2 + 1)
+    {
+        const int nbH = H >> 5;
 #pragma unroll
-    for (int a = 0; a < TT; ++a)
+        for (int a2 = 0; a2 < kBigTT / 2; ++a2)
 #pragma unroll
-        for (int i = 0; i < NC; ++i) {
-            const int j = i * 256 + tid;
-            xv[a][i] = (j < H && t0 + a < p.T) ? p.x[(size_t)(t0 + a) * H + j] : 0.0f;
-        }
+            for (int i = 0; i < NC; ++i) {
+                const int j = i * 256 + pt, ta = t0 + 2 * a2;
+                const bool in = EXACT || j < H;
+                const float x0 = (in && ta < p.T) ? p.x[(size_t)ta * H + j] : 0.0f;
+                const float x1 = (in && ta + 1 < p.T) ? p.x[(size_t)(ta + 1) * H + j] : 0.0f;
+                xv2[a2][i] = pack2f(x0, x1);
+                if (blockIdx.x == 0) {
+                    // Q8_1 of this group's tokens: a warp's 32 threads hold one 32-element block per (token, i)
+                    const int b = i * 8 + (pt >> 5);
+                    if (b < nbH && ta < p.T)   // (uniform over the warp)
+                        quantize_block_q8_1(x0, p.x_q8 + ((size_t)ta * nbH + b) * kQ81Bytes, lane, p.x_soa_q + (size_t)ta * H + b * 32,
+                                            p.x_soa_d + (size_t)ta * p.x_soa_d_stride + b);
+                    if (b < nbH && ta + 1 < p.T)
+                        quantize_block_q8_1(x1, p.x_q8 + ((size_t)(ta + 1) * nbH + b) * kQ81Bytes, lane, p.x_soa_q + (size_t)(ta + 1) * H + b * 32,
+                                            p.x_soa_d + (size_t)(ta + 1) * p.x_soa_d_stride + b);
+                }
+            }
+    }
     __syncthreads();   // barriers initialised
-    int buf = 0;
-    for (int k = 0; k < npairs; ++k) {
-        const int r = r_begin + 2 * k, slot = k % kBigRing;
-        const bool two = r + 1 < r_end;
+    float* red = smem_f + g * (kBigTT * kBigTE * 256) + 2 * pt;   // this thread's pair slot of every (token pair, row)
+    for (int k = 0; k < nsteps; ++k) {
+        const int r = r_begin + kBigTE * k, slot = k % kBigRing;
         if (!mbar_wait(&s_full[slot], (uint32_t)((k / kBigRing) & 1))) {
             if (p.status && tid == 0) atomicOr(p.status, kStatusWaitTimeout);   // a wait ran out: leave a mark, go on
             mbar_wait(&s_full[slot], (uint32_t)((k / kBigRing) & 1));
         }
-        const float* w0 = ring + (size_t)slot * 2 * H;
-        float acc[TT][2];
+        const float* w0 = ring + (size_t)slot * kBigTE * H + pt;
+        uint64_t acc2[kBigTT / 2][kBigTE];
 #pragma unroll
-        for (int a = 0; a < TT; ++a) { acc[a][0] = 0.0f; acc[a][1] = 0.0f; }
+        for (int a2 = 0; a2 < kBigTT / 2; ++a2)
 #pragma unroll
-        for (int i = 0; i < NC; ++i) {   // ascending j, one fused multiply-add each
-            const int j = i * 256 + tid;
-            if (j < H) {
-                const float wa = w0[j], wb = two ? w0[H + j] : 0.0f;
+            for (int b = 0; b < kBigTE; ++b) acc2[a2][b] = 0ull;
 #pragma unroll
-                for (int a = 0; a < TT; ++a) {
-                    acc[a][0] = fmaf(wa, xv[a][i], acc[a][0]);
-                    acc[a][1] = fmaf(wb, xv[a][i], acc[a][1]);
+        for (int i = 0; i < NC; ++i) {   // ascending j, one fused multiply-add per output each
+            if (EXACT || i * 256 + pt < H) {
+#pragma unroll
+                for (int b = 0; b < kBigTE; ++b) {
+                    const float w = w0[b * H + i * 256];
+                    const uint64_t w2 = pack2f(w, w);
+#pragma unroll
+                    for (int a2 = 0; a2 < kBigTT / 2; ++a2) acc2[a2][b] = fma2(w2, xv2[a2][i], acc2[a2][b]);
                 }
             }
         }
-        float* red = smem_f + buf * (TT * 2 * 256);
+        if (k > 0) __syncthreads();   // the sums of the previous step have been read
 #pragma unroll
-        for (int a = 0; a < TT; ++a) { red[(a * 2 + 0) * 256 + tid] = acc[a][0]; red[(a * 2 + 1) * 256 + tid] = acc[a][1]; }
+        for (int a2 = 0; a2 < kBigTT / 2; ++a2)
+#pragma unroll
+            for (int b = 0; b < kBigTE; ++b) *reinterpret_cast<uint64_t*>(red + (a2 * kBigTE + b) * 512) = acc2[a2][b];
         __syncthreads();   // partial sums complete; every thread is done with this ring slot
-        if (tid == 0 && k + kBigRing < npairs) {
+        if (tid == 0 && k + kBigRing < nsteps) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             ask(k + kBigRing);
         }
-        for (int o = warp; o < TT * 2; o += 8) {
-            const float v = tree256(red + o * 256, lane);
-            const int t = t0 + (o >> 1), rr = r + (o & 1);
-            if (lane == 0 && t < p.T && rr < r_end) {
-                if (rr < E) p.router_logits[(size_t)t * E + rr] = p.router_bias ? v + p.router_bias[rr] : v;
-                else p.sh_gate_logit[t] = v;
+        // sixteen warps, two (token pair, row) sums each: warp = (group, token pair, row half)
+        {
+            const int og = warp >> 3, a2 = (warp >> 1) & 3, bh = warp & 1;
+            const float* rb = smem_f + og * (kBigTT * kBigTE * 256) + a2 * (kBigTE * 512);
+            const int t = blockIdx.y * (2 * kBigTT) + og * kBigTT + 2 * a2;
+#pragma unroll
+            for (int bb = 0; bb < kBigTE / 2; ++bb) {
+                const int b = bh * (kBigTE / 2) + bb, rr = r + b;
+                float v0, v1;
+                tree256_pair(rb + b * 512, lane, v0, v1);
+                if (lane == 0 && rr < r_end) {
+                    const float bias = s_bias[rr];
+                    if (rr < E) {
+                        if (t < p.T) p.router_logits[(size_t)t * E + rr] = p.router_bias ? v0 + bias : v0;
+                        if (t + 1 < p.T) p.router_logits[(size_t)(t + 1) * E + rr] = p.router_bias ? v1 + bias : v1;
+                    } else {
+                        if (t < p.T) p.sh_gate_logit[t] = v0;
+                        if (t + 1 < p.T) p.sh_gate_logit[t + 1] = v1;
+                    }
+                }
             }
         }
-        buf ^= 1;   // the next pair writes the other half: its last readers are behind the barrier above
     }
 
-    // ---- last CTA of the token tile: scores and top-k ----
+    // ---- last CTA of the token tile: scores and top-k, one warp per token ----
     __shared__ int s_flag;
     __threadfence();
     __syncthreads();
@@ -472,20 +530,148 @@ __global__ void __launch_bounds__(256, 2) route_big_kernel(const RouteParams p, 
     if (!s_flag) return;
     __threadfence();
     if (tid == 0) p.counters[kCtrRouteTile + blockIdx.y] = 0;
-    for (int a = warp; a < TT; a += 8) {
-        const int t = t0 + a;
+    {
+        const int t = blockIdx.y * (2 * kBigTT) + warp;
         if (t < p.T) topk_warp(p, p.router_logits + (size_t)t * E, t, lane, smem_f + warp * 256, nullptr);
     }
-    // ---- last token tile overall: dispatch permutation and work list ----
+    if (split_dispatch) return;   // three small launches follow and do the dispatch over the whole GPU
+    // ---- last token tile overall: dispatch permutation and work list (the first 256 threads) ----
     __threadfence();
     __syncthreads();
     if (tid == 0) s_flag = (atomicAdd(&p.counters[kCtrRouteAll], 1) == (int)gridDim.y - 1);
     __syncthreads();
-    if (!s_flag) return;
+    if (!s_flag || tid >= 256) return;
     __threadfence();
     if (tid == 0) p.counters[kCtrRouteAll] = 0;
-    build_dispatch(p, reinterpret_cast<int*>(smem_f), nullptr, kBigRouteSmemInts - kDispatchSmemInts);
+    build_dispatch(p, reinterpret_cast<int*>(smem_f), nullptr, kBigRedFloats - kDispatchSmemInts);
 }
+
+// ---- dispatch of a large batch in three small launches --------------------------------------
+// One CTA sorting tens of thousands of pairs is a serial tail of hundreds of microseconds, so large batches split
+// the same stable counting sort over the GPU: chunks of 128 consecutive pairs are counted per expert (hist),
+// one CTA turns the counts into every chunk's first position within every expert and into the experts' offsets
+// (scan), and the chunks place their own pairs (place); whoever finishes last writes the GEMV work list.
+// Scratch: hist[chunks][256] + 260 ints behind it, zero before and after (it shares memory with the combine
+// counters of the down stage, which need zeros).
+constexpr int kDispatchChunk = 128;
+__host__ __device__ inline int dispatch_chunks(int P) { return (P + kDispatchChunk - 1) / kDispatchChunk; }
+__host__ __device__ inline size_t dispatch_scratch_ints(int P) { return (size_t)dispatch_chunks(P) * 256 + 260; }
+
+__global__ void __launch_bounds__(kDispatchChunk) dispatch_hist_kernel(const RouteParams p, int32_t* hist) {
+    __shared__ int s_ids[kDispatchChunk];
+    const int tid = threadIdx.x, P = p.T * p.top_k, q = blockIdx.x * kDispatchChunk + tid;
+    const int istr = p.idx_stride > 1 ? p.idx_stride : 1;
+    int e = q < P ? __ldcg(p.topk_idx + (size_t)q * istr) : -1;
+    s_ids[tid] = (e >= 0 && e < p.E) ? e : -1;
+    __syncthreads();
+    for (int x = tid; x < 256; x += kDispatchChunk) {
+        int c = 0;
+#pragma unroll 8
+        for (int i = 0; i < kDispatchChunk; ++i) c += (s_ids[i] == x);
+        hist[(size_t)blockIdx.x * 256 + x] = c;
+    }
+}
+
+// One CTA of 256: thread = expert.  hist[chunk][e] becomes the number of pairs of expert e in earlier chunks.
+__global__ void __launch_bounds__(256) dispatch_scan_kernel(const RouteParams p, int32_t* hist, int nchunks) {
+    __shared__ int scan[16];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int run = 0;
+    int32_t* col = hist + tid;
+    int c = 0;
+    for (; c + 8 <= nchunks; c += 8) {   // eight independent loads in flight
+        int v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = col[(size_t)(c + i) * 256];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { col[(size_t)(c + i) * 256] = run; run += v[i]; }
+    }
+    for (; c < nchunks; ++c) { const int v = col[(size_t)c * 256]; col[(size_t)c * 256] = run; run += v; }
+    const int cnt = tid < p.E ? run : 0;
+    const int nent = (cnt + kMaxGroupTokens - 1) / kMaxGroupTokens;
+    int incl_c = cnt, incl_n = nent;
+#pragma unroll
+    for (int sft = 1; sft < 32; sft <<= 1) {
+        const int a = __shfl_up_sync(0xffffffffu, incl_c, sft), b = __shfl_up_sync(0xffffffffu, incl_n, sft);
+        if (lane >= sft) { incl_c += a; incl_n += b; }
+    }
+    if (lane == 31) { scan[warp] = incl_c; scan[8 + warp] = incl_n; }
+    __syncthreads();
+    int base_c = 0, base_n = 0;
+    for (int w = 0; w < warp; ++w) { base_c += scan[w]; base_n += scan[8 + w]; }
+    int32_t* ent_base = hist + (size_t)nchunks * 256;   // [257] first routed entry of each expert, then their number
+    if (tid < p.E) p.offsets[tid] = base_c + incl_c - cnt;
+    ent_base[tid] = base_n + incl_n - nent;
+    if (tid == 255) { p.offsets[p.E] = base_c + incl_c; ent_base[256] = base_n + incl_n; }
+}
+
+__global__ void __launch_bounds__(kDispatchChunk) dispatch_place_kernel(const RouteParams p, int32_t* hist, int nchunks) {
+    __shared__ int s_ids[kDispatchChunk];
+    __shared__ int s_last;
+    const int tid = threadIdx.x, P = p.T * p.top_k, q = blockIdx.x * kDispatchChunk + tid;
+    const int istr = p.idx_stride > 1 ? p.idx_stride : 1;
+    int e = q < P ? __ldcg(p.topk_idx + (size_t)q * istr) : -1;
+    if (e < 0 || e >= p.E) e = -1;
+    s_ids[tid] = e;
+    __syncthreads();
+    if (e >= 0) {
+        int rank = 0;
+        for (int i = 0; i < tid; ++i) rank += (s_ids[i] == e);
+        p.perm[__ldcg(p.offsets + e) + __ldcg(hist + (size_t)blockIdx.x * 256 + e) + rank] = q;
+    }
+    __syncthreads();
+    for (int x = tid; x < 256; x += kDispatchChunk) hist[(size_t)blockIdx.x * 256 + x] = 0;   // back to zero for whoever shares this memory
+    // ---- the chunk that finishes last writes the work list ----
+    int32_t* ent_base = hist + (size_t)nchunks * 256;
+    int32_t* done = ent_base + 258;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(done, 1) == nchunks - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    __shared__ int s_ent[257], s_off[257];
+    for (int x = tid; x < 257; x += kDispatchChunk) { s_ent[x] = __ldcg(ent_base + x); s_off[x] = x <= p.E ? __ldcg(p.offsets + x) : 0; }
+    __syncthreads();
+    const int sgt = shared_group_tokens(p.T);
+    const int nsh = (p.has_shared && p.list_mode != 2) ? (p.T + sgt - 1) / sgt : 0;
+    const int total_routed = p.list_mode == 0 ? s_ent[256] : 0;
+    for (int i = tid; i < nsh; i += kDispatchChunk) {
+        int* ent = p.group_list + kListHeader + kListEntry * i;
+        const int t0 = i * sgt, mm = min(sgt, p.T - t0);
+        ent[0] = -1; ent[1] = t0; ent[2] = mm; ent[3] = 0;
+        for (int j = 0; j < kMaxGroupTokens; ++j) ent[4 + j] = j < mm ? p.T * p.top_k + t0 + j : 0;
+    }
+    for (int idx = tid; idx < total_routed; idx += kDispatchChunk) {
+        int lo = 0, hi = 256;   // ent_base[lo] <= idx < ent_base[hi]
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_ent[mid] <= idx) lo = mid; else hi = mid;
+        }
+        const int ex = lo, i = idx - s_ent[ex], o = s_off[ex], cnt = s_off[ex + 1] - o;
+        const int mm = min(kMaxGroupTokens, cnt - i * kMaxGroupTokens);
+        int* ent = p.group_list + kListHeader + kListEntry * (nsh + idx);
+        ent[0] = ex; ent[1] = o + i * kMaxGroupTokens; ent[2] = mm; ent[3] = 0;
+        for (int j = 0; j < kMaxGroupTokens; ++j) ent[4 + j] = j < mm ? __ldcg(p.perm + o + i * kMaxGroupTokens + j) : 0;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        p.group_list[0] = total_routed + nsh; p.group_list[1] = total_routed; p.group_list[2] = nsh; p.group_list[3] = 0;
+        *done = 0;
+    }
+    for (int x = tid; x < 258; x += kDispatchChunk) ent_base[x] = 0;
+}
+
+static cudaError_t launch_dispatch_split(const RouteParams& p, cudaStream_t stream) {
+    const int nchunks = dispatch_chunks(p.T * p.top_k);
+    dispatch_hist_kernel<<<nchunks, kDispatchChunk, 0, stream>>>(p, p.dispatch_scratch);
+    dispatch_scan_kernel<<<1, 256, 0, stream>>>(p, p.dispatch_scratch, nchunks);
+    dispatch_place_kernel<<<nchunks, kDispatchChunk, 0, stream>>>(p, p.dispatch_scratch, nchunks);
+    return cudaGetLastError();
+}
+// Batches from this many pairs on take the three-launch dispatch (below, the single CTA at the router's end is faster).
+constexpr int kSplitDispatchPairs = 4096;
+static bool use_split_dispatch(const RouteParams& p) { return p.dispatch_scratch != nullptr && p.T * p.top_k >= kSplitDispatchPairs; }
 
 // The dispatch step alone, for callers that bring their own expert ids in p.topk_idx.
 constexpr int kPermuteIdsRoom = 8192;
@@ -567,7 +753,27 @@ static size_t route_smem(int TT, int TE) {
 }
 
 cudaError_t launch_permute(const RouteParams& p, cudaStream_t stream) {
+    if (use_split_dispatch(p)) return launch_dispatch_split(p, stream);
     permute_kernel<<<1, 256, (kDispatchSmemInts + kPermuteIdsRoom) * sizeof(int), stream>>>(p);
+    return cudaGetLastError();
+}
+
+// The routing decision of a layer call in the form the drafter tooling stores it: one byte per (token, slot), slots
+// in descending-score order (the "ffn_moe_topk-{L}" tensor, I32 [n_expert_used, n_tokens], narrowed to uint8
+// [n_tokens][8]; chimere-dflash/extract/target_daemon.cpp:18-23).  `load` (optional) collects how many pairs each expert
+// received: the per-expert load metric.
+__global__ void routing_trace_kernel(const int32_t* topk_idx, uint8_t* trace, int32_t* load, int n, int E) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int e = topk_idx[i];
+    trace[i] = (uint8_t)e;
+    if (load && e >= 0 && e < E) atomicAdd(load + e, 1);
+}
+
+cudaError_t launch_routing_trace(const int32_t* topk_idx, uint8_t* trace, int32_t* load, int T, int k, int E, cudaStream_t stream) {
+    const int n = T * k;
+    if (n <= 0) return cudaSuccess;
+    routing_trace_kernel<<<(n + 255) / 256, 256, 0, stream>>>(topk_idx, trace, load, n, E);
     return cudaGetLastError();
 }
 
@@ -591,22 +797,29 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
         constexpr int TT = 8, TE = 2;
         dim3 grid((nrows + TE - 1) / TE, (p.T + TT - 1) / TT);
         return launch_pdl(route_kernel<TT, TE>, grid, 256, route_smem(TT, TE), stream, p);
-    } else if (p.H <= 2048 && p.H % 4 == 0) {
-        // token tiles of 16 (8 for H > 2048) with the input in registers; row groups so that a few CTAs per SM exist
-        // Q8_1 of the input by its own small kernel, then the logits: token tiles of 8 rows held in registers, the
-        // router rows dealt to row groups so that a few CTAs per SM exist
-        quantize_rows_kernel<<<(unsigned)(((int64_t)p.T * (p.H / 32) + 7) / 8), 256, 0, stream>>>(p);
-        const int tt = 8;
-        const int token_tiles = (p.T + tt - 1) / tt;
-        int groups = (4 * 148 + token_tiles - 1) / token_tiles;
-        groups = groups < 1 ? 1 : (groups > (nrows + 1) / 2 ? (nrows + 1) / 2 : groups);
-        const int rows_per_group = 2 * (((nrows + groups - 1) / groups + 1) / 2);
+    } else if (p.H <= 2048 && p.H % 32 == 0) {
+        // token tiles of 16; the router rows are cut into row groups (multiples of four rows) only while there are too few
+        // token tiles to fill the GPU, because every row group fetches its tokens again
+        const int token_tiles = (p.T + 2 * kBigTT - 1) / (2 * kBigTT);
+        int groups = sm_count() / token_tiles;   // (rounded down: a second wave of a few CTAs would double the time)
+        const int max_groups = (nrows + kBigTE - 1) / kBigTE;
+        groups = groups < 1 ? 1 : (groups > max_groups ? max_groups : groups);
+        const int rows_per_group = kBigTE * (((nrows + groups - 1) / groups + kBigTE - 1) / kBigTE);
         const dim3 grid((nrows + rows_per_group - 1) / rows_per_group, token_tiles);
-        const size_t smem = (size_t)kBigRouteSmemInts * sizeof(int);   // 2 x 16 KiB partial sums + 4 x 2 x H x 4 <= 64 KiB ring
+        const size_t smem = big_route_smem(p.H);
         static bool attr_done[64] = {};
-        cudaError_t e = max_smem_once(route_big_kernel<8, 8>, (int)smem, attr_done);
-        if (e != cudaSuccess) return e;
-        route_big_kernel<8, 8><<<grid, 256, smem, stream>>>(p, rows_per_group);
+        static bool attr_done_x[64] = {};
+        const bool split = use_split_dispatch(p);
+        if (p.H == 2048) {
+            cudaError_t e = max_smem_once(route_big_kernel<8, true>, (int)big_route_smem(2048), attr_done_x);
+            if (e != cudaSuccess) return e;
+            route_big_kernel<8, true><<<grid, kBigThreads, smem, stream>>>(p, rows_per_group, split ? 1 : 0);
+        } else {
+            cudaError_t e = max_smem_once(route_big_kernel<8, false>, (int)big_route_smem(2048), attr_done);
+            if (e != cudaSuccess) return e;
+            route_big_kernel<8, false><<<grid, kBigThreads, smem, stream>>>(p, rows_per_group, split ? 1 : 0);
+        }
+        if (split) return launch_dispatch_split(p, stream);
     } else {
         constexpr int TT = 8, TE = 8;
         static bool attr_done[64] = {};

@@ -252,3 +252,32 @@ def route_only(w, scratch: MoeScratch, x: torch.Tensor) -> None:
     stream = torch.cuda.current_stream(x.device).cuda_stream
     abi.check(lib.chimere_b200_moe_route(C.byref(w.as_struct()), x.data_ptr(), x.shape[0], C.byref(scratch.ws), stream),
               "chimere_b200_moe_route")
+
+
+def forward_moe_residual_norm(w, scratch: MoeScratch, hidden: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+                              out: Optional[torch.Tensor] = None, pw: Optional[MoeWeightsPrefill] = None) -> torch.Tensor:
+    """residual += hidden; y = MoE(rmsnorm(residual) * norm_weight): the half-layer as the reference's forward runs it
+    (fused_add_residual_rmsnorm + forward_moe_cudarc_with_cache, compute_graph.rs:2063-2069).  `residual` is updated in place."""
+    lib = abi.load()
+    T = hidden.shape[0]
+    if out is None:
+        out = torch.empty_like(hidden)
+    if pw is not None and scratch.prefill is None:
+        scratch.enable_prefill()
+    stream = torch.cuda.current_stream(hidden.device).cuda_stream
+    abi.check(lib.chimere_b200_moe_forward_residual_norm(C.byref(w.as_struct()), C.byref(pw.struct) if pw is not None else None, hidden.data_ptr(),
+                                                         residual.data_ptr(), norm_weight.data_ptr(), eps, out.data_ptr(), T,
+                                                         C.byref(scratch.ws), stream), "chimere_b200_moe_forward_residual_norm")
+    return out
+
+
+def routing_trace(w, scratch: MoeScratch, T: int, trace: Optional[torch.Tensor] = None, expert_load: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The expert ids of the last routing in `scratch` as uint8 [T, top_k] (the drafter tooling's layout); `expert_load`
+    (int32 [E], optional) accumulates the pairs per expert."""
+    lib = abi.load()
+    if trace is None:
+        trace = torch.empty(T, w.top_k, dtype=torch.uint8, device=scratch.device)
+    stream = torch.cuda.current_stream(scratch.device).cuda_stream
+    abi.check(lib.chimere_b200_moe_routing_trace(C.byref(w.as_struct()), T, C.byref(scratch.ws), trace.data_ptr(),
+                                                 None if expert_load is None else expert_load.data_ptr(), stream), "chimere_b200_moe_routing_trace")
+    return trace

@@ -276,6 +276,23 @@ int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_m
                                      const float* d_x, float* d_y, int T, chimere_moe_workspace* ws,
                                      cudaStream_t stream);
 
+/* The step in front of the layer in both of the reference's callers, and the layer, in one call:
+ *   residual[t] += hidden[t];  normed[t] = residual[t] / sqrt(mean(residual[t]^2) + eps) * norm_weight;  y = MoE(normed)
+ * fused_add_residual_rmsnorm (src/kernels/fused_ops.rs:91-140) followed by forward_moe_cudarc_with_cache, as called at
+ * src/qwen35_model/compute_graph.rs:2063-2069, for T rows.  d_residual is updated in place; the normalised rows stay
+ * inside the workspace.  pw: NULL = the decode kernels, else the prefill path (w must then be TILED32).  Same capture
+ * rules as chimere_b200_moe_forward (src/qwen35_model/cuda_graph.rs:12-31: no allocation, no host synchronisation). */
+int chimere_b200_moe_forward_residual_norm(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw,
+                                           const float* d_hidden, float* d_residual, const float* d_norm_weight, float eps,
+                                           float* d_y, int T, chimere_moe_workspace* ws, cudaStream_t stream);
+
+/* Routing trace for the drafter tooling: the expert ids of the last routing in `ws` as d_trace[T][top_k] bytes, slots
+ * in descending-score order -- the layout in which chimere-dflash/extract/target_daemon.cpp:18-23 stores the
+ * "ffn_moe_topk-{L}" tensor of each captured layer.  d_expert_load (optional, int32 [E]): the number of pairs each
+ * expert received is added to it (the per-expert load metric the reference logs, moe_ffn.rs:120-131). */
+int chimere_b200_moe_routing_trace(const chimere_moe_layer* w, int T, const chimere_moe_workspace* ws, uint8_t* d_trace,
+                                   int32_t* d_expert_load, cudaStream_t stream);
+
 /* RMSNorm with unit weight over rows of length H: y = x / sqrt(mean(x^2) + eps). Used between
  * stacked layers. */
 int chimere_b200_rmsnorm(const float* d_x, float* d_y, int T, int H, float eps, cudaStream_t stream);

@@ -378,6 +378,27 @@ void orc_rmsnorm(const float* x, float* y, int T, int H, float eps) {
     }
 }
 
+/* residual += hidden; normed = residual / sqrt(mean(residual^2) + eps) * weight, for T rows of length n.
+ * fused_add_residual_rmsnorm, src/kernels/fused_ops.rs:91-140 (one block of 256 threads per row): thread i sums the
+ * squares of elements i, i+256, ... (nvcc contracts sum += v*v), the 256 sums meet in a tree with strides 128..1, and
+ * every element is (residual * inv_rms) * weight with inv_rms = 1 / sqrtf(sum / n + eps). */
+void orc_add_residual_rmsnorm(const float* hidden, float* residual, const float* weight, float* normed, int T, int n, float eps) {
+    for (int t = 0; t < T; t++) {
+        const float* h = hidden + (size_t)t * n; float* r = residual + (size_t)t * n; float* o = normed + (size_t)t * n;
+        float part[256];
+        for (int p = 0; p < 256; p++) {
+            float acc = 0.0f;
+            for (int i = p; i < n; i += 256) { float v = h[i] + r[i]; r[i] = v; acc = fmaf(v, v, acc); }
+            part[p] = acc;
+        }
+        for (int s = 128; s > 0; s >>= 1)
+            for (int p = 0; p < s; p++) part[p] += part[p + s];
+        float rms = sqrtf(part[0] / (float)n + eps);
+        float inv = 1.0f / rms;
+        for (int i = 0; i < n; i++) o[i] = r[i] * inv * weight[i];
+    }
+}
+
 /* ------------------------------------------------------------------- dispatch order ----- */
 
 /* Stable counting sort of the pairs p = t*k + j by expert id: offsets[E+1], perm[T*k].

@@ -12,6 +12,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 ORACLE_DIR = os.path.join(ROOT, "oracle")
 LIB_PATH = os.path.join(ORACLE_DIR, "libmoe_oracle.so")
 REF_CUBIN = os.path.join(ORACLE_DIR, "_ref", "chimere_kernels.cubin")
+REF_FUSED_OPS_CUBIN = os.path.join(ORACLE_DIR, "_ref", "fused_ops_kernels.cubin")
 
 _lib = None
 
@@ -137,6 +138,15 @@ def rmsnorm(x, eps=1e-6):
     y = np.empty_like(x)
     lib().orc_rmsnorm(_p(x), _p(y), C.c_int(x.shape[0]), C.c_int(x.shape[1]), C.c_float(eps))
     return y
+
+
+def add_residual_rmsnorm(hidden, residual, weight, eps=1e-6):
+    """Returns (updated residual, normed) for rows [T, n]."""
+    hidden, weight = f32(hidden), f32(weight)
+    res = f32(residual).copy()
+    normed = np.empty_like(res)
+    lib().orc_add_residual_rmsnorm(_p(hidden), _p(res), _p(weight), _p(normed), C.c_int(res.shape[0]), C.c_int(res.shape[1]), C.c_float(eps))
+    return res, normed
 
 
 def moe_forward(weights, x, taps=True, forced_idx=None):

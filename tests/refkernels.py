@@ -9,10 +9,10 @@ import os
 
 import torch
 
-from oracle import REF_CUBIN
+from oracle import REF_CUBIN, REF_FUSED_OPS_CUBIN
 
 _cuda = None
-_module = None
+_modules = {}
 _funcs = {}
 
 
@@ -20,34 +20,44 @@ def available() -> bool:
     return os.path.exists(REF_CUBIN) and torch.cuda.is_available()
 
 
+def fused_ops_available() -> bool:
+    return os.path.exists(REF_FUSED_OPS_CUBIN) and torch.cuda.is_available()
+
+
 def _drv():
-    global _cuda, _module
+    global _cuda
     if _cuda is None:
         torch.cuda.init()
         torch.zeros(1, device="cuda")  # primary context current on this thread
         _cuda = C.CDLL("libcuda.so.1")
-        mod = C.c_void_p()
-        data = open(REF_CUBIN, "rb").read()
-        rc = _cuda.cuModuleLoadData(C.byref(mod), data)
-        assert rc == 0, f"cuModuleLoadData failed: {rc}"
-        _module = mod
     return _cuda
 
 
-def _func(name: str):
-    if name not in _funcs:
+def _module(path: str):
+    if path not in _modules:
+        drv = _drv()
+        mod = C.c_void_p()
+        data = open(path, "rb").read()
+        rc = drv.cuModuleLoadData(C.byref(mod), data)
+        assert rc == 0, f"cuModuleLoadData({os.path.basename(path)}) failed: {rc}"
+        _modules[path] = mod
+    return _modules[path]
+
+
+def _func(name: str, cubin: str = REF_CUBIN):
+    if (cubin, name) not in _funcs:
         drv = _drv()
         f = C.c_void_p()
-        rc = drv.cuModuleGetFunction(C.byref(f), _module, name.encode())
+        rc = drv.cuModuleGetFunction(C.byref(f), _module(cubin), name.encode())
         assert rc == 0, f"cuModuleGetFunction({name}) failed: {rc}"
-        _funcs[name] = f
-    return _funcs[name]
+        _funcs[(cubin, name)] = f
+    return _funcs[(cubin, name)]
 
 
-def _launch(name, grid, block, smem, args):
+def _launch(name, grid, block, smem, args, cubin: str = REF_CUBIN):
     """args: list of ctypes values (c_void_p for pointers, c_int for ints)."""
     drv = _drv()
-    f = _func(name)
+    f = _func(name, cubin)
     arr = (C.c_void_p * len(args))(*[C.cast(C.pointer(a), C.c_void_p) for a in args])
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     rc = drv.cuLaunchKernel(f, grid[0], grid[1], grid[2], block[0], block[1], block[2], smem, stream, arr, None)
@@ -131,3 +141,14 @@ def fused_moe_iq3s(hidden: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, d
             [_dp(hidden), _dp(gate), _dp(up), _dp(down), _dp(ids), _dp(weights), _dp(out), C.c_int(hidden_size), C.c_int(expert_ffn),
              C.c_int(bytes_gate), C.c_int(bytes_up), C.c_int(bytes_down)])
     return out
+
+
+def fused_add_residual_rmsnorm(hidden: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float):
+    """fused_add_residual_rmsnorm (src/kernels/fused_ops.rs:91-140, the source the reference compiles with NVRTC), one row,
+    launched as its wrapper does (:667-669): grid 1, block 256, 1 KiB of shared memory.  Updates `residual` in place and
+    returns the normalised row."""
+    n = hidden.numel()
+    normed = torch.empty_like(hidden)
+    _launch("fused_add_residual_rmsnorm", (1, 1, 1), (256, 1, 1), 256 * 4,
+            [_dp(hidden), _dp(residual), _dp(weight), _dp(normed), C.c_int(n), C.c_float(eps)], cubin=REF_FUSED_OPS_CUBIN)
+    return normed

@@ -351,3 +351,60 @@ def test_whole_layer_against_reference_fused_kernel(layout):
         assert rel(yg, yr) <= 2.5e-2 and cos(yg, yr) >= COS_TOL, (rel(yg, yr), cos(yg, yr))
         check_rows(yg[None, :], yo[None, :])                      # the Q8_1 path itself: the benchmark's bar
         assert abs(rel(yo, yr) - rel(yg, yr)) <= 5e-3              # the distance to the fused kernel is the rounding, not the GPU code
+
+
+def test_fused_residual_rmsnorm_then_layer():
+    """residual += hidden, RMSNorm with a weight, then the layer, in one call.  The prologue must equal the reference's
+    fused_add_residual_rmsnorm kernel bit for bit (it is run here from the source the reference hands to NVRTC), and the
+    layer output must be what the plain entry gives on the normalised rows."""
+    from chimere_b200.layer import forward_moe_residual_norm
+    cfg = SMALL[1]
+    wd, wh = layer_pair(cfg, "tiled")
+    T, eps = 5, 1e-6
+    g = torch.Generator(device="cuda").manual_seed(21)
+    hidden = torch.randn(T, cfg.H, generator=g, device="cuda")
+    residual = torch.randn(T, cfg.H, generator=g, device="cuda")
+    weight = 1.0 + 0.1 * torch.randn(cfg.H, generator=g, device="cuda")
+    res_ref, normed_ref = oracle.add_residual_rmsnorm(hidden.cpu().numpy(), residual.cpu().numpy(), weight.cpu().numpy(), eps)
+    sc = MoeScratch(wd, 8)
+    res_gpu = residual.clone()
+    y = forward_moe_residual_norm(wd, sc, hidden, res_gpu, weight, eps)
+    torch.cuda.synchronize()
+    assert np.array_equal(res_gpu.cpu().numpy(), res_ref), "residual rows after the add"
+    if refkernels.fused_ops_available():
+        for t in range(T):
+            r = residual[t].clone()
+            n = refkernels.fused_add_residual_rmsnorm(hidden[t].contiguous(), r, weight, eps)
+            torch.cuda.synchronize()
+            assert torch.equal(r, res_gpu[t])
+            assert np.array_equal(n.cpu().numpy(), normed_ref[t]), "oracle restatement vs the reference kernel"
+    normed = torch.from_numpy(normed_ref).cuda()
+    y_plain = forward_moe(wd, MoeScratch(wd, 8), normed)
+    torch.cuda.synchronize()
+    # the same kernels on the same rows (the prologue's rows equal the oracle's up to the GPU's sqrt / division rounding)
+    np.testing.assert_allclose(y.cpu().numpy(), y_plain.cpu().numpy(), rtol=1e-4, atol=1e-6)
+    check_rows(y.cpu().numpy(), oracle.moe_forward(wh, normed_ref, taps=False)["y"])
+
+
+def test_routing_trace_layout_and_load():
+    from chimere_b200.layer import routing_trace
+    from chimere_b200.trace import RoutingTrace
+    cfg = configs.QWEN_Q8_0     # Zipf-biased: a skewed load histogram
+    wd, _ = layer_pair(cfg)
+    T = 40
+    sc = MoeScratch(wd, T)
+    load = torch.zeros(cfg.E, dtype=torch.int32, device="cuda")
+    tr = RoutingTrace(T, cfg.top_k)
+    idx_layers = []
+    for layer_seed in (5, 6):
+        x = configs.make_input(cfg, T, device="cuda", seed=layer_seed)
+        route_only(wd, sc, x)
+        tr.add_layer(routing_trace(wd, sc, T, expert_load=load))
+        idx_layers.append(sc.topk_indices(T).cpu().numpy().copy())
+    torch.cuda.synchronize()
+    data = RoutingTrace.parse(tr.payload())
+    assert data.shape == (2, T, 8)
+    for i, idx in enumerate(idx_layers):
+        assert np.array_equal(data[i], idx.astype(np.uint8))
+    ref_load = np.bincount(np.concatenate([i.reshape(-1) for i in idx_layers]), minlength=cfg.E)
+    assert np.array_equal(load.cpu().numpy(), ref_load)
