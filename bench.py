@@ -287,43 +287,13 @@ def measure_secondary(lib, dev, hbm_peak, i8_peak_tops, prefill_tokens):
 
 def run_expert_parallel(args, cfg, dev, rank, world, local, dist, hbm_peak, peak_kind):
     """N > 1: the same layer with its experts sharded over the ranks (E/N each, contiguous), router and shared
-    expert replicated, T tokens per rank (weak scaling), dispatch and combine by NCCL all-to-all."""
+    expert replicated, T tokens per rank (weak scaling).  Dispatch and combine either by the kernels themselves (peer
+    stores over NVLink, the default) or by NCCL all-to-all (--ep-exchange nccl)."""
     import torch
-    from chimere_b200 import configs, formats
+    from chimere_b200 import abi, configs, formats
     from chimere_b200.ep import ExpertParallelMoE
     T, L, K, W = args.tokens, args.layers, args.steps, args.warmup
-    layers = []
-    for i in range(L):
-        full = configs.make_layer(cfg, device=dev, seed=1000 + i)          # same weights on every rank, then sharded
-        layers.append(ExpertParallelMoE(full, max_tokens=T, rank=rank, world=world, device=dev))
-        del full
-    xs = [configs.make_input(cfg, T, device=dev, seed=31 * (rank + 1) + i) for i in range(L)]
-    ys = [torch.empty_like(x) for x in xs]
-
-    padded = T * cfg.top_k <= 1024          # decode-size: fixed-size exchange, no host sync per layer
-
-    def step():
-        for ep, x, y in zip(layers, xs, ys):
-            (ep.forward_padded if padded else ep.forward)(x, y)
-
-    # one step = one CUDA graph when the exchange is fixed-size (NCCL all-to-alls are captured with the kernels)
-    timing_note = "eager launches"
-    graph = None
-    if padded:
-        try:
-            step(); step()
-            torch.cuda.synchronize(); dist.barrier()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                step()
-            torch.cuda.synchronize()
-            timing_note = "CUDA graph replay of one step (kernels and NCCL all-to-alls captured together)"
-        except Exception as exc:  # keep the eager path if this torch/NCCL pair cannot capture collectives
-            graph = None
-            timing_note = f"eager launches (graph capture failed: {type(exc).__name__})"
-            print(f"[bench] graph capture failed: {exc}", file=sys.stderr)
-            torch.cuda.synchronize()
-    run_step = graph.replay if graph is not None else step
+    lib = abi.load()
 
     def timed(fn, k, w):
         for _ in range(w):
@@ -342,6 +312,66 @@ def run_expert_parallel(args, cfg, dev, rank, world, local, dist, hbm_peak, peak
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def build(cfg_, n_layers, tokens, seed0):
+        eps = []
+        for i in range(n_layers):
+            full = configs.make_layer(cfg_, device=dev, seed=seed0 + i)        # same weights on every rank, then sharded
+            eps.append(ExpertParallelMoE(full, max_tokens=tokens, rank=rank, world=world, device=dev, prefill=tokens * cfg_.top_k > 1024))
+            del full
+        return eps
+
+    def exchange_mode(eps, tokens):
+        """peer stores when asked for and the batch is decode-size; else the fixed-size NCCL exchange; else exact splits."""
+        if tokens * cfg.top_k <= 1024 and args.ep_exchange == "peer":
+            try:
+                for e in eps:
+                    e.enable_peer_exchange()
+                return "peer"
+            except Exception as exc:   # no IPC between these processes: the collective path still works
+                print(f"[bench] peer exchange not available ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
+        return "padded" if tokens * cfg.top_k <= 1024 else "exact"
+
+    def graph_or_eager(step):
+        note, graph = "eager launches", None
+        try:
+            step(); step()
+            torch.cuda.synchronize(); dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            torch.cuda.synchronize()
+            note = "CUDA graph replay of one step"
+        except Exception as exc:
+            graph = None
+            note = f"eager launches (graph capture failed: {type(exc).__name__})"
+            print(f"[bench] graph capture failed: {exc}", file=sys.stderr)
+            torch.cuda.synchronize()
+        return (graph.replay if graph is not None else step), note
+
+    def received_pairs(eps, tokens):
+        """Routed pairs every owner rank received in the last call of each layer: (mean, max) over ranks, averaged over layers."""
+        k_, e_loc = cfg.top_k, cfg.E // world
+        tot = torch.zeros(world, device=dev)
+        for e in eps:
+            idx = e.ws_home.topk_idx(tokens, k_).reshape(-1).to(torch.int64)
+            tot += torch.bincount(torch.div(idx, e_loc, rounding_mode="floor"), minlength=world).to(tot.dtype)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+        tot /= len(eps)
+        return float(tot.mean().item()), float(tot.max().item())
+
+    # ---- headline: the decode layer, T tokens per rank, L layers per step ----
+    layers = build(cfg, L, T, 1000)
+    xs = [configs.make_input(cfg, T, device=dev, seed=31 * (rank + 1) + i) for i in range(L)]
+    ys = [torch.empty_like(x) for x in xs]
+    mode = exchange_mode(layers, T)
+    fwd = {"peer": lambda ep, x, y: ep.forward_peer(x, y), "padded": lambda ep, x, y: ep.forward_padded(x, y),
+           "exact": lambda ep, x, y: ep.forward(x, y)}
+
+    def step():
+        for ep, x, y in zip(layers, xs, ys):
+            fwd[mode](ep, x, y)
+
+    run_step, timing_note = graph_or_eager(step) if mode != "exact" else (step, "eager launches")
     sampler = ClockSampler(local)
     secs = timed(run_step, K, W)
     clocks = sampler.stop()
@@ -353,39 +383,79 @@ def run_expert_parallel(args, cfg, dev, rank, world, local, dist, hbm_peak, peak
     def e2e_step():
         for ep, a, b, x, y in zip(layers, hx, hy, xs, ys):
             x.copy_(a, non_blocking=True)
-            (ep.forward_padded if padded else ep.forward)(x, y)
+            fwd[mode](ep, x, y)
             b.copy_(y, non_blocking=True)
         torch.cuda.synchronize()
 
     e2e_secs = timed(e2e_step, K, W)
-    recv = torch.tensor([float(sum(ep.last_recv_rows for ep in layers)) / L], device=dev)
-    rmax = recv.clone(); dist.all_reduce(rmax, op=dist.ReduceOp.MAX)
-    rsum = recv.clone(); dist.all_reduce(rsum, op=dist.ReduceOp.SUM)
+    rows_mean, rows_max = received_pairs(layers, T)
+    status = max(int(e.ws_home.arena[e.ws_home.ws.status - e.ws_home.arena.data_ptr():][:4].view(torch.int32).item()) for e in layers)
+    del layers, xs, ys, run_step
+    torch.cuda.empty_cache()
+
+    # ---- secondary: the expert-parallel stack (Q4_0 experts, Zipf-biased routing, RMSNorm between the layers) ----
+    stack = None
+    if args.ep_stack_layers > 0:
+        scfg = configs.QWEN_Q4_0_ZIPF
+        stack = {"workload": f"{scfg.name}: {args.ep_stack_layers} layers with independent seeded weights, experts sharded {scfg.E // world} per GPU, "
+                             "RMSNorm (unit weight, eps 1e-6) between the layers; tokens split evenly over the ranks", "results": []}
+        for total_tokens in (64, 8192):
+            tr = total_tokens // world
+            if tr * world != total_tokens or tr < 1:
+                continue
+            eps = build(scfg, args.ep_stack_layers, tr, 4000)
+            smode = exchange_mode(eps, tr)
+            xa, xb = configs.make_input(scfg, tr, device=dev, seed=7 + rank), torch.empty(tr, scfg.H, device=dev)
+            st = torch.cuda.current_stream(dev).cuda_stream
+
+            def stack_step():
+                h = xa
+                for ep in eps:
+                    fwd[smode](ep, h, xb)
+                    abi.check(lib.chimere_b200_rmsnorm(xb.data_ptr(), xb.data_ptr(), tr, scfg.H, 1e-6, st), "rmsnorm")
+                    h = xb
+
+            run, note = graph_or_eager(stack_step) if smode != "exact" else (stack_step, "eager launches, one host synchronisation per layer for the split sizes")
+            reps = 5 if smode != "exact" else 2
+            s_secs = timed(run, reps, 2)
+            r_mean, r_max = received_pairs(eps, tr)
+            st_status = max(int(e.ws_home.arena[e.ws_home.ws.status - e.ws_home.arena.data_ptr():][:4].view(torch.int32).item()) for e in eps)
+            stack["results"].append({"T_total": total_tokens, "T_per_rank": tr, "exchange": smode, "timing": note,
+                                     "ms_per_stack": 1e3 * s_secs / reps, "tokens_per_s": total_tokens * reps / s_secs,
+                                     "us_per_layer": 1e6 * s_secs / reps / args.ep_stack_layers,
+                                     "pairs_received_per_rank_mean": r_mean, "pairs_received_per_rank_max": r_max,
+                                     "imbalance": r_max / max(r_mean, 1e-9), "device_status": st_status})
+            del eps, run
+            torch.cuda.empty_cache()
+
     if rank == 0:
         b_gu = cfg.F * formats.row_bytes(cfg.type_gate_up, cfg.H)
         b_dn = cfg.H * formats.row_bytes(cfg.type_down, cfg.F)
-        rows_mean = float(rsum.item()) / world
         layer_us = secs / (K * L) * 1e6
         # per rank and layer call: every received pair's expert (upper bound on distinct experts: one per pair) + shared + router
         alg = min(rows_mean, cfg.E / world) * (2 * b_gu + b_dn) + (2 * b_gu + b_dn) + 4 * cfg.E * cfg.H + 8 * T * cfg.H
+        ds = (cfg.H // 32 + 3) & ~3
+        nvlink = (rows_mean * (cfg.H + 4 * ds + 12) + world * T * cfg.H * 4 if mode == "peer"
+                  else world * T * cfg.top_k * (cfg.H + 4 * ds + 4 + 4 * cfg.H))
+        exch = {"peer": "rows and partial sums written into the peers' buffers by the kernels (NVLink peer stores + flags), fixed-size slots, "
+                        "owners return one partial sum per (home rank, token); no collective call, no host sync",
+                "padded": "NCCL all-to-all, fixed size (padded to T*k rows per destination), no host sync",
+                "exact": "NCCL all-to-all with exact split sizes, one host sync per layer call"}[mode]
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
                 "ms_per_step": 1e3 * secs / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "int8 block dots (dp4a), f32 accumulate", "data": "synthetic",
                 "config": dict(workload_config(cfg, T, L), parallelism=f"ep{world}: {cfg.E // world} experts per GPU, router + shared expert replicated, "
-                               f"{T} tokens per GPU; dispatch Q8_1 planes / combine fp32 rows by NCCL all-to-all",
-                               timing="CUDA events around K steps, max over ranks; " + timing_note,
-                               exchange=("fixed-size (padded to T*k rows per destination), no host sync" if padded
-                                         else "exact split sizes, one host sync per layer call"),
-                               weight_layout="tiled"),
+                               f"{T} tokens per GPU", timing="CUDA events around K steps, max over ranks; " + timing_note,
+                               exchange=exch, weight_layout="tiled"),
                 "roofline": {"bound": "hbm", "kernel": "expert-parallel layer call (per rank)", "achieved": alg / (layer_us * 1e-6) / 1e9,
                              "peak": hbm_peak, "unit": "GB/s", "frac": alg / (layer_us * 1e-6) / 1e9 / hbm_peak, "peak_kind": peak_kind,
                              "traffic": None, "us_per_layer_call": layer_us,
-                             "pairs_received_per_rank_mean": rows_mean, "pairs_received_per_rank_max": float(rmax.item()),
-                             "nvlink_bytes_per_rank_per_call": rows_mean * (cfg.H + 4 * ((cfg.H // 32 + 3) & ~3) + 4 + 4 * cfg.H)},
+                             "pairs_received_per_rank_mean": rows_mean, "pairs_received_per_rank_max": rows_max,
+                             "nvlink_bytes_per_rank_per_call": nvlink},
                 "cpu_baseline": None,
                 "e2e": {"value": world * T * L * K / e2e_secs, "unit": UNIT, "h2d_bytes_per_step": L * T * cfg.H * 4,
                         "d2h_bytes_per_step": L * T * cfg.H * 4, "ms_per_step": 1e3 * e2e_secs / K},
-                "gpu_launches": 7 * L * K, "clocks": clocks}
+                "gpu_launches": (10 if mode == "peer" else 9) * L * K, "clocks": clocks, "device_status": status, "ep_stack": stack}
         print(json.dumps(line), flush=True)
     # leave without tearing the communicator down: with a captured graph still holding NCCL work the
     # teardown has been seen to wait for the watchdog; every rank is past its last collective here
@@ -409,6 +479,10 @@ def main():
                     help="comma list of T for the prefill configuration in the secondary measurement ('' = none of them, 'none' = skip the secondary measurement)")
     ap.add_argument("--prefill-only", action="store_true",
                     help="run only the int8 peak probe and the secondary measurement and print their JSON (used for profiling the grouped GEMM)")
+    ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: dispatch / combine by the kernels' own peer stores (default) or by NCCL all-to-all")
+    ap.add_argument("--ep-stack-layers", type=int, default=40,
+                    help="N > 1: layers of the secondary expert-parallel stack measurement (0 = skip it)")
     ap.add_argument("--layout", default="tiled", choices=["tiled", "ggml"],
                     help="weight layout the layer entry runs on: the library's tiled32 repack (default) or raw ggml blocks")
     args = ap.parse_args()

@@ -74,6 +74,10 @@ PROTOTYPES = {
     "chimere_b200_moe_experts_packed": (C.c_int, [_LAYER_P, C.c_int, _P, C.c_int, _WS_P, _P]),
     "chimere_b200_moe_ep_pack": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "chimere_b200_moe_ep_finish": (C.c_int, [_LAYER_P, _P, _P, C.c_int, _WS_P, _P, _P]),
+    "chimere_b200_moe_ep_pack_p2p": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
+    "chimere_b200_moe_ep_wait": (C.c_int, [_P, C.c_int, C.c_int, _WS_P, _P]),
+    "chimere_b200_moe_ep_return_p2p": (C.c_int, [_LAYER_P, _WS_P, _P, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
+    "chimere_b200_moe_ep_finish_p2p": (C.c_int, [_LAYER_P, _P, _P, C.c_int, C.c_int, _WS_P, _P, _P, _P]),
     "chimere_b200_moe_permute": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P]),
     "chimere_b200_block_sumi": (C.c_int, [C.c_int, _P, _P, _P, C.c_int, C.c_int, _P]),
     "chimere_b200_mma128_bytes": (C.c_size_t, [C.c_int, C.c_int]),
@@ -86,6 +90,7 @@ PROTOTYPES = {
     "chimere_b200_moe_forward_prefill": (C.c_int, [_LAYER_P, C.POINTER(PrefillWeights), _P, _P, C.c_int, _WS_P, _P]),
     "chimere_b200_moe_forward_residual_norm": (C.c_int, [_LAYER_P, C.POINTER(PrefillWeights), _P, _P, _P, C.c_float, _P, C.c_int, _WS_P, _P]),
     "chimere_b200_moe_routing_trace": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P, _P, _P]),
+    "chimere_b200_moe_experts_prefill": (C.c_int, [_LAYER_P, C.POINTER(PrefillWeights), C.c_int, _WS_P, _P]),
     "chimere_b200_rmsnorm": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_float, _P]),
     "chimere_b200_abi_version": (C.c_int, []),
     "chimere_b200_built_for_sm": (C.c_int, []),

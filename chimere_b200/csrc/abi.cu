@@ -279,6 +279,50 @@ int chimere_b200_moe_ep_finish(const chimere_moe_layer* w, const float* d_rows, 
     return cuda_rc(launch_ep_finish(d_rows, d_slot, ws->topk_w, shared_rows, logit, d_y, T, w->H, w->top_k, stream));
 }
 
+// ---- exchange by peer stores (decode-size batches) ----
+int chimere_b200_moe_ep_pack_p2p(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, void* const* d_peer_recv,
+                                 int32_t* const* d_peer_flags, int32_t* d_ctr, int rank, int experts_per_rank, int world, int cap,
+                                 int row_bytes, cudaStream_t stream) {
+    int rc = check_call(w, d_peer_recv, d_peer_flags, T, ws);
+    if (rc) return rc;
+    if (!d_ctr) return -1;
+    const int ds = (w->H / 32 + 3) & ~3;
+    if (experts_per_rank <= 0 || world <= 0 || world * experts_per_rank != w->E || cap < T * w->top_k || rank < 0 || rank >= world) return -2;
+    if (row_bytes % 16 || row_bytes < w->H + 4 * ds + 12 || w->H % 16) return -2;
+    (void)d_ctr;
+    return cuda_rc(launch_ep_pack_p2p(ws->topk_idx, ws->topk_w, ws->x_q, ws->x_d, ds, (uint8_t* const*)d_peer_recv, d_peer_flags, rank, T,
+                                      w->top_k, w->H, experts_per_rank, world, cap, row_bytes, stream));
+}
+
+int chimere_b200_moe_ep_wait(int32_t* d_flags, int world, int cap, chimere_moe_workspace* ws, cudaStream_t stream) {
+    if (!d_flags || !ws) return -1;
+    if (world <= 0 || world > 32 || cap <= 0) return -2;
+    return cuda_rc(launch_ep_wait_flags(d_flags, world, cap, ws->status, stream));
+}
+
+int chimere_b200_moe_ep_return_p2p(const chimere_moe_layer* w_local, chimere_moe_workspace* ws_owner, const void* d_rows, int row_bytes,
+                                   float* const* d_peer_back, int32_t* const* d_peer_flags, int32_t* d_ctr, int rank, int world, int T, int cap,
+                                   cudaStream_t stream) {
+    if (!w_local || !ws_owner || !ws_owner->pair_out || !d_rows || !d_peer_back || !d_peer_flags || !d_ctr) return -1;
+    const int ds = (w_local->H / 32 + 3) & ~3;
+    if (world <= 0 || rank < 0 || rank >= world || T <= 0 || cap <= 0 || world * cap > ws_owner->max_T) return -2;
+    if (row_bytes % 16 || row_bytes < w_local->H + 4 * ds + 12) return -2;
+    (void)d_ctr;
+    return cuda_rc(launch_ep_return_p2p(ws_owner->pair_out, (const uint8_t*)d_rows, row_bytes, w_local->H + 4 * ds, d_peer_back, d_peer_flags,
+                                        rank, world, T, cap, w_local->H, stream));
+}
+
+int chimere_b200_moe_ep_finish_p2p(const chimere_moe_layer* w, const float* d_back, int32_t* d_flags, int world, int T,
+                                   chimere_moe_workspace* ws, float* d_y, int32_t* d_ctr, cudaStream_t stream) {
+    int rc = check_call(w, d_back, d_y, T, ws);
+    if (rc) return rc;
+    if (!d_flags || !d_ctr) return -1;
+    if (world <= 0 || world > 32) return -2;
+    const float* shared_rows = w->F_s > 0 ? ws->pair_out + (size_t)T * w->top_k * w->H : nullptr;
+    const float* logit = (w->F_s > 0 && w->shexp_gate_w) ? ws->sh_gate_logit : nullptr;
+    return cuda_rc(launch_ep_finish_p2p(d_back, d_flags, world, shared_rows, logit, d_y, T, w->H, d_ctr, ws->status, stream));
+}
+
 static GemvParams gate_up_params(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, const Layout& L) {
     GemvParams g{};
     g.T = T; g.top_k = w->top_k; g.H = w->H;
@@ -598,10 +642,11 @@ size_t chimere_b200_moe_prefill_bytes(const chimere_moe_layer* w, int max_T) {
     return prefill_arena(w, max_T).total;
 }
 
-int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, const float* d_x, float* d_y,
-                                     int T, chimere_moe_workspace* ws, cudaStream_t stream) {
-    int rc = check_call(w, d_x, d_y, T, ws);
-    if (rc) return rc;
+// The expert products of a prefill-size batch whose routing (ws->offsets, ws->perm) and Q8_1 planes (ws->x_q, ws->x_d) are
+// in place: token tiles for the experts with at least kGemmMin pairs (and the shared expert, if any) on the grouped GEMM,
+// the rest on the GEMV kernels; per-pair rows land in ws->pair_out.
+static int prefill_experts(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, int T, chimere_moe_workspace* ws,
+                           cudaStream_t stream) {
     if (!pw || !ws->prefill_arena) return -1;
     if (w->layout != CHIMERE_LAYOUT_TILED32 || !prefill_dims_ok(w)) return -2;
     const PrefillArena A = prefill_arena(w, ws->max_T);
@@ -610,13 +655,7 @@ int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_m
     int32_t* tiles = (int32_t*)(base + A.tiles);
     const Layout L = make_layout(w, ws->max_T);
     const int n_tiles_max = n_tiles_max_for(w, T);
-    const bool dual = w->act == CHIMERE_ACT_SWIGLU;
-
-    RouteParams rp = route_params(w, d_x, T, ws);
-    rp.list_mode = 2;   // no work entries from the router: the tile builder below writes the list of the small experts
-    cudaError_t e = launch_route(rp, stream);
-    if (e != cudaSuccess) return cuda_rc(e);
-    e = launch_build_tiles(ws->offsets, ws->perm, tiles, ws->group_list, w->E, T, w->top_k, w->F_s > 0, kGemmMin, stream);
+    cudaError_t e = launch_build_tiles(ws->offsets, ws->perm, tiles, ws->group_list, w->E, T, w->top_k, w->F_s > 0, kGemmMin, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     e = launch_gather_tiles(tiles, ws->perm, ws->x_q, ws->x_d, L.x_d_stride, base + A.bx, A.bx_stride, w->H, w->top_k, n_tiles_max, stream);
     if (e != cudaSuccess) return cuda_rc(e);
@@ -630,7 +669,7 @@ int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_m
     gu.nrows_shared = 0; gu.ncols_shared = 0; gu.sh_a = nullptr; gu.sh_b = nullptr;
     e = launch_gate_up_tiled(gu, max_entries, stream);
     if (e != cudaSuccess) return cuda_rc(e);
-    GemvParams dn = down_params(w, d_y, T, ws, L);
+    GemvParams dn = down_params(w, nullptr, T, ws, L);
     dn.no_combine = 1;
     dn.nrows_shared = 0; dn.ncols_shared = 0; dn.sh_a = nullptr; dn.sh_b = nullptr;
     e = launch_down_tiled(dn, max_entries, stream);
@@ -647,7 +686,6 @@ int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_m
     g.nblk_routed = w->F / 32; g.nblk_shared = w->F_s / 32;
     g.row_tiles_max = g.row_tiles_routed > g.row_tiles_shared ? g.row_tiles_routed : g.row_tiles_shared;
     g.ncols_in = w->H; g.ncols_in_shared = w->H;
-    (void)dual;
     e = launch_prefill_gemm(g, false, n_tiles_max, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     g.a_exps = (const uint8_t*)pw->down_exps; g.stride_a = pw->stride_down; g.sh_a = (const uint8_t*)pw->sh_down;
@@ -655,12 +693,40 @@ int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_m
     g.out_tiles = nullptr; g.pair_out = ws->pair_out;
     g.row_tiles_routed = g.row_tiles_shared = g.row_tiles_max = w->H / 128;
     g.ncols_in = w->F; g.ncols_in_shared = w->F_s;
-    e = launch_prefill_gemm(g, true, n_tiles_max, stream);
+    return cuda_rc(launch_prefill_gemm(g, true, n_tiles_max, stream));
+}
+
+int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, const float* d_x, float* d_y,
+                                     int T, chimere_moe_workspace* ws, cudaStream_t stream) {
+    int rc = check_call(w, d_x, d_y, T, ws);
+    if (rc) return rc;
+    if (!pw || !ws->prefill_arena) return -1;
+    if (w->layout != CHIMERE_LAYOUT_TILED32 || !prefill_dims_ok(w)) return -2;
+    RouteParams rp = route_params(w, d_x, T, ws);
+    rp.list_mode = 2;   // no work entries from the router: the tile builder writes the list of the small experts
+    cudaError_t e = launch_route(rp, stream);
     if (e != cudaSuccess) return cuda_rc(e);
+    rc = prefill_experts(w, pw, T, ws, stream);
+    if (rc) return rc;
     // routing-weighted sum of every token's pair rows in slot order + the sigmoid-gated shared expert
     const float* shared_rows = w->F_s > 0 ? ws->pair_out + (size_t)T * w->top_k * w->H : nullptr;
     const float* logit = (w->F_s > 0 && w->shexp_gate_w) ? ws->sh_gate_logit : nullptr;
     return cuda_rc(launch_ep_finish(ws->pair_out, nullptr, ws->topk_w, shared_rows, logit, d_y, T, w->H, w->top_k, stream));
+}
+
+// Expert-parallel owner rank, prefill-size: as chimere_b200_moe_experts, with the large local experts on the grouped GEMM.
+int chimere_b200_moe_experts_prefill(const chimere_moe_layer* w_local, const chimere_moe_prefill_weights* pw_local, int n_rows,
+                                     chimere_moe_workspace* ws, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    int rc = check_call(w_local, ws, ws, n_rows, ws);
+    if (rc) return rc;
+    if (w_local->layout != CHIMERE_LAYOUT_TILED32 || w_local->top_k != 1 || w_local->F_s != 0) return -2;
+    RouteParams p = route_params(w_local, nullptr, n_rows, ws);
+    p.has_shared = 0;
+    p.list_mode = 2;
+    cudaError_t e = launch_permute(p, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    return prefill_experts(w_local, pw_local, n_rows, ws, stream);
 }
 
 int chimere_b200_moe_forward_residual_norm(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, const float* d_hidden,

@@ -87,6 +87,15 @@ cudaError_t launch_ep_finish(const float* rows, const int32_t* slot, const float
 // fixed-size dispatch: fill send[world*cap][row_bytes] with the pairs of each destination rank in pair order
 cudaError_t launch_ep_pack(const int32_t* topk_idx, const int8_t* x_q, const float* x_d, int d_stride, uint8_t* send, int32_t* slot,
                            int T, int k, int H, int experts_per_rank, int world, int cap, int row_bytes, cudaStream_t stream);
+// expert-parallel exchange by peer stores (decode-size batches); see router.cu
+cudaError_t launch_ep_pack_p2p(const int32_t* topk_idx, const float* topk_w, const int8_t* x_q, const float* x_d, int d_stride,
+                               uint8_t* const* peer_recv, int32_t* const* peer_flags, int rank, int T, int k, int H,
+                               int experts_per_rank, int world, int cap, int row_bytes, cudaStream_t stream);
+cudaError_t launch_ep_wait_flags(int32_t* flags, int n, int expect, int32_t* status, cudaStream_t stream);
+cudaError_t launch_ep_return_p2p(const float* pair_rows, const uint8_t* recv, int row_bytes, int tail_off, float* const* peer_back,
+                                 int32_t* const* peer_flags, int rank, int world, int T, int cap, int H, cudaStream_t stream);
+cudaError_t launch_ep_finish_p2p(const float* back, int32_t* flags, int world, const float* shared_rows, const float* sh_logit, float* y,
+                                 int T, int H, int32_t* ctr, int32_t* status, cudaStream_t stream);
 cudaError_t launch_gate_up(const GemvParams& p, int max_entries, cudaStream_t stream);
 cudaError_t launch_down(const GemvParams& p, int max_entries, cudaStream_t stream);
 

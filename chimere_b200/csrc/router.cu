@@ -746,6 +746,183 @@ __global__ void __launch_bounds__(128) ep_pack_kernel(const int32_t* topk_idx, c
     }
 }
 
+// ---- expert-parallel exchange by peer stores (decode-size batches) -----------------------------
+// Instead of handing the packed rows to a collective, the home rank writes every pair's row straight into its owner's
+// receive buffer (peer memory over NVLink, plain stores, no multicast), and the owner writes every (home rank, token)
+// partial sum straight into the home rank's buffer.  One counter per (buffer, source rank) says how many of the source's
+// CTAs have finished writing their part of this call: every CTA adds one with a system-scope release behind its stores,
+// the reader waits (acquire) for the full count and takes the counter down again.  A rank cannot be a call ahead of a peer
+// on the same buffers (it needs that peer's answer first), so one counter suffices.
+// Every wait is bounded; a wait that runs out raises the status bit and the kernel goes on.
+// Row: [H int8][d_stride f32][int32 local expert id | -1][int32 token][f32 routing weight], row_bytes a multiple of 16.
+__device__ __forceinline__ int ld_acquire_sys(const int32_t* p) { int v; asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
+__device__ __forceinline__ void red_release_sys_add(int32_t* p, int v) { asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+// true when *flag reached `expect` within the bound
+__device__ __forceinline__ bool wait_flag(const int32_t* flag, int expect) {
+    for (int it = 0; it < (1 << 22); ++it) {
+        if (ld_acquire_sys(flag) >= expect) return true;
+        __nanosleep(40);
+    }
+    return false;
+}
+
+// One CTA per slot s = (destination rank d, position i): the i-th pair (in pair order) whose expert lives on rank d goes
+// to row rank * cap + i of rank d's receive buffer; slots without a pair get id -1.
+__global__ void __launch_bounds__(128) ep_pack_p2p_kernel(const int32_t* topk_idx, const float* topk_w, const int8_t* x_q, const float* x_d,
+                                                          int d_stride, uint8_t* const* peer_recv, int32_t* const* peer_flags,
+                                                          int rank, int T, int k, int H, int experts_per_rank, int cap, int row_bytes) {
+    __shared__ int s_pair;
+    const int s = blockIdx.x, d = s / cap, i = s - d * cap, P = T * k;
+    if (threadIdx.x < 32) {
+        int found = -1, seen = 0;
+        for (int base = 0; base < P && found < 0; base += 32) {
+            const int q = base + threadIdx.x;
+            const bool hit = q < P && (__ldcg(topk_idx + q) / experts_per_rank) == d;
+            const unsigned m = __ballot_sync(0xffffffffu, hit);
+            const int c = __popc(m);
+            if (seen + c > i) {
+                unsigned mm = m;
+                for (int r = 0; r < i - seen; ++r) mm &= mm - 1;   // drop the first i - seen hits
+                found = base + __ffs(mm) - 1;
+            }
+            seen += c;
+        }
+        if (threadIdx.x == 0) s_pair = found;
+    }
+    __syncthreads();
+    const int pair = s_pair;
+    uint8_t* row = peer_recv[d] + ((size_t)rank * cap + i) * row_bytes;
+    int32_t* tail = reinterpret_cast<int32_t*>(row + H + 4 * d_stride);
+    if (pair < 0) {
+        if (threadIdx.x == 0) tail[0] = -1;
+    } else {
+        const int t = pair / k;
+        const uint4* sq = reinterpret_cast<const uint4*>(x_q + (size_t)t * H);
+        for (int v = threadIdx.x; v < H / 16; v += blockDim.x) reinterpret_cast<uint4*>(row)[v] = sq[v];
+        const float* sd = x_d + (size_t)t * d_stride;
+        for (int v = threadIdx.x; v < d_stride; v += blockDim.x) reinterpret_cast<float*>(row + H)[v] = sd[v];
+        if (threadIdx.x == 0) {
+            tail[0] = __ldcg(topk_idx + pair) - d * experts_per_rank;
+            tail[1] = t;
+            reinterpret_cast<float*>(tail)[2] = __ldcg(topk_w + pair);
+        }
+    }
+    // this CTA's stores, then one more on the destination's counter for this rank (the CTA barrier orders every thread's
+    // stores before thread 0's release; releases are cumulative): the reader waits for `cap` of them
+    __syncthreads();
+    if (threadIdx.x == 0) red_release_sys_add(peer_flags[d] + rank, 1);
+}
+
+// Owner side, before its kernels read the received rows: wait for every source rank's counter and take it down.
+__global__ void ep_wait_flags_kernel(int32_t* flags, int n, int expect, int32_t* status) {
+    const int i = threadIdx.x;
+    if (i < n) {
+        if (!wait_flag(flags + i, expect) && status) atomicOr(status, kStatusWaitTimeout);
+        flags[i] = 0;
+    }
+}
+
+// Owner side, after the down products: for every (source rank s, token t) the routing-weighted sum of the expert rows of
+// that token's pairs on this rank, in slot order, written into rank s's buffer at [this rank][t][H]; then this rank's flag
+// there.  grid = (world * T, ceil(H / 256)), 256 threads.
+__global__ void __launch_bounds__(256) ep_return_p2p_kernel(const float* pair_rows, const uint8_t* recv, int row_bytes, int tail_off,
+                                                            float* const* peer_back, int32_t* const* peer_flags, int rank, int T, int cap,
+                                                            int H) {
+    __shared__ float s_w[64];
+    __shared__ int s_slot[64];
+    __shared__ int s_n;
+    const int s = blockIdx.x / T, t = blockIdx.x - s * T;
+    // the slots of source s that carry a pair of token t (at most top_k <= 8 of them), kept in slot order
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        int n = 0;
+        for (int base = 0; base < cap; base += 32) {
+            const int i = base + lane;
+            bool hit = false;
+            float wgt = 0.0f;
+            if (i < cap) {
+                const int32_t* tail = reinterpret_cast<const int32_t*>(recv + ((size_t)s * cap + i) * row_bytes + tail_off);
+                hit = __ldcg(tail) >= 0 && __ldcg(tail + 1) == t;
+                wgt = __ldcg(reinterpret_cast<const float*>(tail) + 2);
+            }
+            const unsigned m = __ballot_sync(0xffffffffu, hit);
+            const int pos = n + __popc(m & ((1u << lane) - 1u));
+            if (hit && pos < 64) { s_slot[pos] = s * cap + i; s_w[pos] = wgt; }
+            n += __popc(m);
+        }
+        if (lane == 0) s_n = min(n, 64);
+    }
+    __syncthreads();
+    const int n = s_n;
+    const int h = blockIdx.y * 256 + threadIdx.x;
+    if (h < H) {
+        float sum = 0.0f;
+        for (int j = 0; j < n; ++j) sum = fmaf(s_w[j], __ldcg(pair_rows + (size_t)s_slot[j] * H + h), sum);
+        peer_back[s][((size_t)rank * T + t) * H + h] = sum;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) red_release_sys_add(peer_flags[s] + rank, 1);   // the home rank waits for T * gridDim.y of these
+}
+
+// Home side: y[t] = sum over owner ranks (ascending) of their partial sums + the sigmoid-gated shared expert.  Every CTA
+// waits for the owners' flags; the CTA that finishes last takes them down.  ctr: one int of local scratch.
+__global__ void __launch_bounds__(256) ep_finish_p2p_kernel(const float* back, int32_t* flags, int world, int expect, const float* shared_rows,
+                                                            const float* sh_logit, float* y, int T, int H, int32_t* ctr, int32_t* status) {
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < world && !wait_flag(flags + threadIdx.x, expect)) s_ok = 0;
+    __syncthreads();
+    if (!s_ok && threadIdx.x == 0 && status) atomicOr(status, kStatusWaitTimeout);
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < (int64_t)T * H) {
+        const int t = (int)(idx / H), h = (int)(idx - (int64_t)t * H);
+        float sum = 0.0f;
+        for (int o = 0; o < world; ++o) sum += __ldcg(back + ((size_t)o * T + t) * H + h);
+        if (shared_rows) {
+            const float sh = shared_rows[(size_t)t * H + h];
+            if (sh_logit) sum = fmaf(sh, sigmoid_ref(sh_logit[t]), sum);
+            else sum = sh + sum;
+        }
+        y[idx] = sum;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(ctr, 1) == (int)gridDim.x - 1) {
+            *ctr = 0;
+            for (int o = 0; o < world; ++o) flags[o] = 0;
+        }
+    }
+}
+
+cudaError_t launch_ep_pack_p2p(const int32_t* topk_idx, const float* topk_w, const int8_t* x_q, const float* x_d, int d_stride,
+                               uint8_t* const* peer_recv, int32_t* const* peer_flags, int rank, int T, int k, int H,
+                               int experts_per_rank, int world, int cap, int row_bytes, cudaStream_t stream) {
+    ep_pack_p2p_kernel<<<world * cap, 128, 0, stream>>>(topk_idx, topk_w, x_q, x_d, d_stride, peer_recv, peer_flags, rank, T, k, H,
+                                                        experts_per_rank, cap, row_bytes);
+    return cudaGetLastError();
+}
+cudaError_t launch_ep_wait_flags(int32_t* flags, int n, int expect, int32_t* status, cudaStream_t stream) {
+    ep_wait_flags_kernel<<<1, 32, 0, stream>>>(flags, n, expect, status);
+    return cudaGetLastError();
+}
+cudaError_t launch_ep_return_p2p(const float* pair_rows, const uint8_t* recv, int row_bytes, int tail_off, float* const* peer_back,
+                                 int32_t* const* peer_flags, int rank, int world, int T, int cap, int H, cudaStream_t stream) {
+    ep_return_p2p_kernel<<<dim3(world * T, (H + 255) / 256), 256, 0, stream>>>(pair_rows, recv, row_bytes, tail_off, peer_back, peer_flags, rank,
+                                                                              T, cap, H);
+    return cudaGetLastError();
+}
+// the home rank's counters reach T * ceil(H / 256) per owner rank
+cudaError_t launch_ep_finish_p2p(const float* back, int32_t* flags, int world, const float* shared_rows, const float* sh_logit, float* y,
+                                 int T, int H, int32_t* ctr, int32_t* status, cudaStream_t stream) {
+    const int64_t n = (int64_t)T * H;
+    if (n <= 0) return cudaSuccess;
+    ep_finish_p2p_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(back, flags, world, T * ((H + 255) / 256), shared_rows, sh_logit, y, T, H,
+                                                                         ctr, status);
+    return cudaGetLastError();
+}
+
 static size_t route_smem(int TT, int TE) {
     size_t a = (size_t)TT * TE * 256 * sizeof(float);
     size_t b = kDispatchSmemInts * sizeof(int);

@@ -19,7 +19,7 @@ import torch
 import torch.distributed as dist
 
 from . import abi
-from .layer import MoeScratch, MoeWeightsRaw, MoeWeightsTiled
+from .layer import MoeScratch, MoeWeightsPrefill, MoeWeightsRaw, MoeWeightsTiled
 
 
 # ------------------------------------------------------------------ exchange plan (pure torch) ----
@@ -61,7 +61,7 @@ class ExpertParallelMoE:
     """One MoE layer on `world` GPUs.  `full_raw` is the whole layer (same on every rank, e.g. seeded);
     only this rank's expert range is kept on the device after construction."""
 
-    def __init__(self, full_raw: MoeWeightsRaw, max_tokens: int, rank: int, world: int, device, group=None):
+    def __init__(self, full_raw: MoeWeightsRaw, max_tokens: int, rank: int, world: int, device, group=None, prefill: bool = False):
         assert full_raw.E % world == 0
         self.rank, self.world, self.group = rank, world, group
         self.k, self.E, self.H = full_raw.top_k, full_raw.E, full_raw.H
@@ -78,6 +78,8 @@ class ExpertParallelMoE:
             shexp_gate_raw=mv(full_raw.shexp_gate_raw), shexp_up_raw=mv(full_raw.shexp_up_raw), shexp_down_raw=mv(full_raw.shexp_down_raw),
             route_mode=full_raw.route_mode, route_scale=full_raw.route_scale, act=full_raw.act,
             type_sh_gate=full_raw.type_sh_gate, type_sh_up=full_raw.type_sh_up, type_sh_down=full_raw.type_sh_down)
+        # prefill-size batches: the local shard's copy for the grouped GEMM (built from the raw blocks before they are dropped)
+        self.pw_owner = MoeWeightsPrefill(local) if prefill else None
         self.packed = MoeWeightsTiled(local, keep_raw=False)
         self.router_weight = mv(full_raw.router_weight)
         self.router_bias = mv(full_raw.router_bias)
@@ -92,7 +94,7 @@ class ExpertParallelMoE:
         self.max_tokens = max_tokens
         self.max_rows = max_tokens * self.k * world   # worst case: every pair of every rank lands here
         self.ws_home = _Scratch(self.home, full_raw, max_tokens, dev)
-        self.ws_owner = _Scratch(self.owner, full_raw, self.max_rows, dev)
+        self.ws_owner = _Scratch(self.owner, full_raw, self.max_rows, dev, prefill=prefill)
         self.rows_pair = torch.empty(max_tokens * self.k, self.H, dtype=torch.float32, device=dev)
         self.back = torch.empty(max_tokens * self.k, self.H, dtype=torch.float32, device=dev)
         self.lib = abi.load()
@@ -118,7 +120,11 @@ class ExpertParallelMoE:
         all_to_all_rows(self.ws_home.x_q(T)[tok], send_counts, recv_counts, self.ws_owner.x_q(self.max_rows), self.group)
         all_to_all_rows(self.ws_home.x_d(T)[tok], send_counts, recv_counts, self.ws_owner.x_d(self.max_rows), self.group)
         all_to_all_rows(plan.local_ids, send_counts, recv_counts, self.ws_owner.topk_idx(self.max_rows, 1).reshape(-1), self.group)
-        abi.check(lib.chimere_b200_moe_experts(C.byref(self.owner), n, C.byref(self.ws_owner.ws), st), "experts")
+        if self.pw_owner is not None and n >= 512:   # many rows per expert: the grouped GEMM
+            abi.check(lib.chimere_b200_moe_experts_prefill(C.byref(self.owner), C.byref(self.pw_owner.struct), n, C.byref(self.ws_owner.ws), st),
+                      "experts_prefill")
+        else:
+            abi.check(lib.chimere_b200_moe_experts(C.byref(self.owner), n, C.byref(self.ws_owner.ws), st), "experts")
         # combine: the pairs' expert rows come home, back into (token, slot) order
         back = all_to_all_rows(self.ws_owner.pair_out(self.max_rows)[:n], recv_counts, send_counts, self.back, self.group)
         self.rows_pair[:T * k].index_copy_(0, plan.order, back)
@@ -162,10 +168,90 @@ class ExpertParallelMoE:
         return out
 
 
+    # ---- decode-size batches: the exchange done by the kernels themselves (peer stores over NVLink) ----
+    def enable_peer_exchange(self) -> None:
+        """Sets up the buffers the peers write into (one device allocation per rank, shared with the other ranks of the node
+        through CUDA IPC) for batches of exactly `max_tokens` tokens.  Collective: every rank must call it."""
+        T, k, H, G = self.max_tokens, self.k, self.H, self.world
+        cap = T * k
+        ds = self.ws_home.dstride
+        rb = (H + 4 * ds + 12 + 15) & ~15
+        recv_bytes = (G * cap * rb + 255) & ~255
+        back_bytes = (G * T * H * 4 + 255) & ~255
+        self._peer = PeerRegion(recv_bytes + back_bytes + 512, self.rank, G, self.group)
+        dev = self.rows_pair.device
+        ptrs = lambda off: torch.tensor([b + off for b in self._peer.bases], dtype=torch.int64, device=dev)
+        self._p2p = dict(cap=cap, rb=rb, recv=self._peer.bases[self.rank], back=self._peer.bases[self.rank] + recv_bytes,
+                         flags_in=self._peer.bases[self.rank] + recv_bytes + back_bytes, flags_back=self._peer.bases[self.rank] + recv_bytes + back_bytes + 256,
+                         peer_recv=ptrs(0), peer_back=ptrs(recv_bytes), peer_flags_in=ptrs(recv_bytes + back_bytes),
+                         peer_flags_back=ptrs(recv_bytes + back_bytes + 256),
+                         ctr=torch.zeros(3 * 64, dtype=torch.int32, device=dev))
+
+    def forward_peer(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """The layer with both exchanges done by peer stores and flags instead of collectives: no NCCL call, no host
+        synchronisation, capturable in a CUDA graph.  The owners return one partial sum per (home rank, token), so the result
+        equals forward() up to the order of those fp32 additions."""
+        lib, T, G = self.lib, x.shape[0], self.world
+        assert T == self.max_tokens and hasattr(self, "_p2p"), "call enable_peer_exchange() first; the batch size is fixed"
+        pp = self._p2p
+        st = torch.cuda.current_stream(x.device).cuda_stream
+        ctr = pp["ctr"].data_ptr()
+        abi.check(lib.chimere_b200_moe_route_home(C.byref(self.home), x.data_ptr(), T, C.byref(self.ws_home.ws), st), "route_home")
+        abi.check(lib.chimere_b200_moe_ep_pack_p2p(C.byref(self.home), T, C.byref(self.ws_home.ws), pp["peer_recv"].data_ptr(),
+                                                   pp["peer_flags_in"].data_ptr(), ctr, self.rank, self.E_loc, G, pp["cap"], pp["rb"], st), "ep_pack_p2p")
+        # the shared expert needs nothing from other ranks: it runs while the rows travel
+        abi.check(lib.chimere_b200_moe_shared_expert(C.byref(self.home), T, C.byref(self.ws_home.ws), st), "shared_expert")
+        abi.check(lib.chimere_b200_moe_ep_wait(pp["flags_in"], G, pp["cap"], C.byref(self.ws_owner.ws), st), "ep_wait")
+        n = G * pp["cap"]
+        abi.check(lib.chimere_b200_moe_experts_packed(C.byref(self.owner), n, pp["recv"], pp["rb"], C.byref(self.ws_owner.ws), st), "experts")
+        abi.check(lib.chimere_b200_moe_ep_return_p2p(C.byref(self.owner), C.byref(self.ws_owner.ws), pp["recv"], pp["rb"], pp["peer_back"].data_ptr(),
+                                                     pp["peer_flags_back"].data_ptr(), ctr + 256, self.rank, G, T, pp["cap"], st), "ep_return_p2p")
+        abi.check(lib.chimere_b200_moe_ep_finish_p2p(C.byref(self.home), pp["back"], pp["flags_back"], G, T, C.byref(self.ws_home.ws), out.data_ptr(),
+                                                     ctr + 512, st), "ep_finish_p2p")
+        self.last_recv_rows = n
+        return out
+
+
+class PeerRegion:
+    """One zeroed device allocation per rank that every rank of the node can address: allocated with cudaMalloc, exported with
+    CUDA IPC, the handles exchanged through the process group.  bases[r] is rank r's region as seen from this process (this
+    rank's own pointer for r == rank).  Peer access is plain load / store over NVLink; nothing here uses multicast."""
+
+    def __init__(self, nbytes: int, rank: int, world: int, group=None):
+        from cuda.bindings import runtime as rt
+        self._rt, self.nbytes = rt, nbytes
+        err, ptr = rt.cudaMalloc(nbytes)
+        if err != rt.cudaError_t.cudaSuccess:
+            raise RuntimeError(f"cudaMalloc({nbytes}) failed: {err}")
+        self.ptr = int(ptr)
+        (err,) = rt.cudaMemset(self.ptr, 0, nbytes)
+        assert err == rt.cudaError_t.cudaSuccess, err
+        torch.cuda.synchronize()
+        self.bases = [0] * world
+        self.bases[rank] = self.ptr
+        self._opened = []
+        if world > 1:
+            err, handle = rt.cudaIpcGetMemHandle(self.ptr)
+            assert err == rt.cudaError_t.cudaSuccess, err
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(handle.reserved), group=group)
+            for r in range(world):
+                if r == rank:
+                    continue
+                h = rt.cudaIpcMemHandle_t()
+                h.reserved = handles[r]
+                err, p = rt.cudaIpcOpenMemHandle(h, rt.cudaIpcMemLazyEnablePeerAccess)
+                if err != rt.cudaError_t.cudaSuccess:
+                    raise RuntimeError(f"cudaIpcOpenMemHandle(rank {r}) failed: {err}")
+                self.bases[r] = int(p)
+                self._opened.append(int(p))
+            dist.barrier(group=group)   # every region is zeroed and mapped before anyone writes into a peer
+
+
 class _Scratch:
     """Workspace of one layer view plus typed views of the buffers the exchanges touch."""
 
-    def __init__(self, struct: abi.MoeLayer, dims: MoeWeightsRaw, max_T: int, dev):
+    def __init__(self, struct: abi.MoeLayer, dims: MoeWeightsRaw, max_T: int, dev, prefill: bool = False):
         lib = abi.load()
         self.H = struct.H
         self.dstride = (struct.H // 32 + 3) & ~3
@@ -176,6 +262,13 @@ class _Scratch:
         self.ws = abi.MoeWorkspace()
         st = torch.cuda.current_stream(dev).cuda_stream
         abi.check(lib.chimere_b200_moe_workspace_init(C.byref(self.ws), self.arena.data_ptr(), nbytes, C.byref(struct), max_T, st), "workspace_init")
+        self.prefill = None
+        if prefill:
+            n = lib.chimere_b200_moe_prefill_bytes(C.byref(struct), max_T)
+            if n == 0:
+                raise RuntimeError("prefill_bytes rejected the layer view")
+            self.prefill = torch.zeros(n, dtype=torch.uint8, device=dev)
+            self.ws.prefill_arena, self.ws.prefill_bytes = self.prefill.data_ptr(), n
 
     def _view(self, ptr, nbytes):
         off = ptr - self.arena.data_ptr()

@@ -216,6 +216,31 @@ int chimere_b200_moe_ep_pack(const chimere_moe_layer* w, int T, chimere_moe_work
 int chimere_b200_moe_ep_finish(const chimere_moe_layer* w, const float* d_rows, const int32_t* d_slot, int T,
                                chimere_moe_workspace* ws, float* d_y, cudaStream_t stream);
 
+/* The same step with the two exchanges done by the kernels themselves: rows and partial sums are written straight into the
+ * peers' buffers (memory of the other GPUs of the node mapped into this process, e.g. by CUDA IPC; plain stores over
+ * NVLink, no collective call, no multicast), and one counter per (buffer, source rank), raised by the writers behind their
+ * stores and taken down by the reader, tells the reader that a call's rows are complete.  For decode-size batches, where two collective launches per layer cost more than the expert products.
+ *   row          = [H int8][ceil4(H/32) f32][int32 local expert id | -1][int32 token][f32 routing weight], row_bytes % 16 == 0
+ *   d_peer_recv  = device array of `world` pointers: rank r's receive buffer [world * cap][row_bytes]
+ *   d_peer_flags = device array of `world` pointers: rank r's counters [world] for that buffer (zero at start)
+ *   d_peer_back  = device array of `world` pointers: rank r's return buffer f32 [world][T][H]
+ *   d_ctr        = one int of this rank's scratch, zero at start (ep_finish_p2p; the other entries ignore it)
+ * Home rank: route_home -> ep_pack_p2p -> shared_expert -> ep_finish_p2p.
+ * Owner rank: ep_wait (the dispatch flags) -> experts_packed on its own receive buffer -> ep_return_p2p, which adds up,
+ * per (home rank, token), the routing-weighted expert rows in slot order and stores the sums in the home rank's return
+ * buffer; ep_finish_p2p waits for the return flags and adds the owners' sums in rank order.  The result differs from
+ * the single-GPU layer only in the order of those fp32 additions.  All waits are bounded (status word of `ws`).
+ * The reference is single-GPU: these entries have no counterpart there. */
+int chimere_b200_moe_ep_pack_p2p(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, void* const* d_peer_recv,
+                                 int32_t* const* d_peer_flags, int32_t* d_ctr, int rank, int experts_per_rank, int world, int cap,
+                                 int row_bytes, cudaStream_t stream);
+int chimere_b200_moe_ep_wait(int32_t* d_flags, int world, int cap, chimere_moe_workspace* ws, cudaStream_t stream);
+int chimere_b200_moe_ep_return_p2p(const chimere_moe_layer* w_local, chimere_moe_workspace* ws_owner, const void* d_rows, int row_bytes,
+                                   float* const* d_peer_back, int32_t* const* d_peer_flags, int32_t* d_ctr, int rank, int world, int T,
+                                   int cap, cudaStream_t stream);
+int chimere_b200_moe_ep_finish_p2p(const chimere_moe_layer* w, const float* d_back, int32_t* d_flags, int world, int T,
+                                   chimere_moe_workspace* ws, float* d_y, int32_t* d_ctr, cudaStream_t stream);
+
 /* Parity tap: integer block dot products.  For `nrows` weight rows of type `wtype` with `ncols`
  * columns and one Q8_1 input row, writes sumi[nrows][ncols/32] (int32): the exact integer sum of
  * each 32-wide block (for IQ3_S including the (1 + 2*scale) factor, chimere_kernels.cu:860). */
@@ -292,6 +317,13 @@ int chimere_b200_moe_forward_residual_norm(const chimere_moe_layer* w, const chi
  * expert received is added to it (the per-expert load metric the reference logs, moe_ffn.rs:120-131). */
 int chimere_b200_moe_routing_trace(const chimere_moe_layer* w, int T, const chimere_moe_workspace* ws, uint8_t* d_trace,
                                    int32_t* d_expert_load, cudaStream_t stream);
+
+/* Expert-parallel owner rank, prefill-size batches: as chimere_b200_moe_experts (planes in ws->x_q / ws->x_d, local expert
+ * ids in ws->topk_idx[n_rows], results in ws->pair_out[row][H]), with the local experts that received at least 8 rows on the
+ * grouped GEMM.  pw_local: the GEMM copy of the local shard (chimere_b200_moe_pack_prefill of the shard); ws needs the
+ * prefill arena.  No counterpart in the reference (single GPU, no prefill kernel). */
+int chimere_b200_moe_experts_prefill(const chimere_moe_layer* w_local, const chimere_moe_prefill_weights* pw_local, int n_rows,
+                                     chimere_moe_workspace* ws, cudaStream_t stream);
 
 /* RMSNorm with unit weight over rows of length H: y = x / sqrt(mean(x^2) + eps). Used between
  * stacked layers. */

@@ -1,17 +1,32 @@
-"""Run under torchrun on >= 2 GPUs: the expert-parallel layer must reproduce the single-GPU layer bit for
-bit on every rank's own tokens (same kernels, same Q8_1 bytes, same combine order)."""
+"""Run under torchrun on one or more GPUs: the expert-parallel layer against the single-GPU layer on every rank's own
+tokens.  The two exchange paths built on collectives must reproduce it bit for bit (same kernels, same Q8_1 bytes, same
+combine order); the peer-store path returns one partial sum per owner rank and may differ in the order of those fp32
+additions only (1e-5 of the row's largest value).  A three-layer stack with RMSNorm between the layers (the structure of the
+expert-parallel benchmark configuration) is checked the same way, against the CPU oracle too."""
 import os
 import sys
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-from chimere_b200 import configs  # noqa: E402
+from chimere_b200 import abi, configs  # noqa: E402
 from chimere_b200.ep import ExpertParallelMoE  # noqa: E402
 from chimere_b200.layer import MoeScratch, MoeWeightsTiled, forward_moe  # noqa: E402
+
+
+def close(a, b, tol):
+    return bool(((a - b).abs().amax(dim=1) <= tol * b.abs().amax(dim=1)).all())
+
+
+def rmsnorm(lib, x):
+    y = torch.empty_like(x)
+    abi.check(lib.chimere_b200_rmsnorm(x.data_ptr(), y.data_ptr(), x.shape[0], x.shape[1], 1e-6, torch.cuda.current_stream().cuda_stream), "rmsnorm")
+    return y
 
 
 def main():
@@ -19,24 +34,100 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
+    lib = abi.load()
     ok = True
-    for cfg, T in ((configs.scaled(configs.QWEN_IQ3S, E=32), 8), (configs.scaled(configs.QWEN_Q4_0_ZIPF, E=64), 40),
-                   (configs.scaled(configs.NEMOTRON_Q4_0, E=16), 3)):
+    cases = ((configs.scaled(configs.QWEN_IQ3S, E=32), 8), (configs.scaled(configs.QWEN_Q4_0_ZIPF, E=64), 40),
+             (configs.scaled(configs.NEMOTRON_Q4_0, E=16), 3),
+             # the shared expert quantized differently from the routed ones: two kernel instances per stage on the home rank
+             (configs.scaled(configs.QWEN_IQ3S, E=16, type_sh_gate_up=configs.Q8_0, type_sh_down=configs.Q8_0, name="iq3s, shared q8_0"), 8))
+    for cfg, T in cases:
         full = configs.make_layer(cfg, device=dev)                     # same seed on every rank
         ep = ExpertParallelMoE(full, max_tokens=T, rank=rank, world=world, device=dev)
+        ep.enable_peer_exchange()
         x = configs.make_input(cfg, T, device=dev, seed=50 + rank)     # this rank's tokens
         y_ep = ep.forward(x).clone()
         y_ep2 = ep.forward_padded(x, torch.empty_like(x)).clone()     # fixed-size exchange, workspaces reused
+        y_p2p = [ep.forward_peer(x, torch.empty_like(x)).clone() for _ in range(3)]   # repeated: flags and counters are reused
         packed = MoeWeightsTiled(full)
         y_ref = forward_moe(packed, MoeScratch(packed, T, device=dev), x)
         torch.cuda.synchronize()
         same = bool(torch.equal(y_ep, y_ref)) and bool(torch.equal(y_ep2, y_ref))
-        print(f"rank {rank} {cfg.name} T={T}: {'bit-exact' if same else 'MISMATCH'} (rows received {ep.last_recv_rows})", flush=True)
-        ok = ok and same
+        near = all(close(y, y_ref, 1e-5) for y in y_p2p) and bool(torch.equal(y_p2p[0], y_p2p[2]))
+        status = int(ep.ws_home.arena[ep.ws_home.ws.status - ep.ws_home.arena.data_ptr():][:4].view(torch.int32).item())
+        print(f"rank {rank} {cfg.name} T={T}: collectives {'bit-exact' if same else 'MISMATCH'}, peer stores {'ok' if near else 'MISMATCH'}"
+              f" (rows received {ep.last_recv_rows}, status {status})", flush=True)
+        ok = ok and same and near and status == 0
+
+    # ---- a prefill-size batch: exact split sizes, the owners' large experts on the grouped GEMM ----
+    cfg, T = configs.scaled(configs.QWEN_Q4_0_ZIPF, E=32), 600
+    full = configs.make_layer(cfg, device=dev)
+    ep = ExpertParallelMoE(full, max_tokens=T, rank=rank, world=world, device=dev, prefill=True)
+    x = configs.make_input(cfg, T, device=dev, seed=70 + rank)
+    y_big = ep.forward(x).clone()
+    packed = MoeWeightsTiled(full)
+    y_ref = forward_moe(packed, MoeScratch(packed, T, device=dev), x)
+    torch.cuda.synchronize()
+    big_ok = close(y_big, y_ref, 2e-3)      # same integer block dots; the GEMM adds the blocks' fp32 terms in another order
+    print(f"rank {rank} {cfg.name} T={T} (owner-side GEMM): {'ok' if big_ok else 'MISMATCH'} (rows received {ep.last_recv_rows})", flush=True)
+    ok = ok and big_ok
+    del ep, full, packed
+
+    # ---- a stack: three layers with independent weights, RMSNorm (unit weight, eps 1e-6) between them ----
+    cfg, T, L = configs.scaled(configs.QWEN_Q4_0_ZIPF, E=32), 16, 3
+    fulls = [configs.make_layer(cfg, device=dev, seed=400 + i) for i in range(L)]
+    eps_ = [ExpertParallelMoE(f, max_tokens=T, rank=rank, world=world, device=dev) for f in fulls]
+    for e in eps_:
+        e.enable_peer_exchange()
+    singles = [MoeWeightsTiled(f) for f in fulls]
+    x0 = configs.make_input(cfg, T, device=dev, seed=90 + rank)
+    outs, per_layer = {}, []
+    peer_layers_ok = True
+    for name in ("single", "padded", "peer"):
+        h = x0
+        for i in range(L):
+            h_in = h
+            if name == "single":
+                h = forward_moe(singles[i], MoeScratch(singles[i], T, device=dev), h)
+            elif name == "padded":
+                h = eps_[i].forward_padded(h, torch.empty_like(h))
+                per_layer.append((h_in.clone(), h.clone(), eps_[i].ws_home.topk_idx(T, cfg.top_k).clone()))
+            else:
+                # The peer-store path adds each token's expert rows in another order (1e-6 or so).  Behind the next layer's
+                # 8-bit rounding, or its top-k, such a difference can grow, so every layer is compared with the single-GPU
+                # layer on the input this path gave it, and the stack as a whole only against the benchmark's bar.
+                h = eps_[i].forward_peer(h, torch.empty_like(h))
+                ref_i = forward_moe(singles[i], MoeScratch(singles[i], T, device=dev), h_in)
+                torch.cuda.synchronize()
+                peer_layers_ok = peer_layers_ok and close(h, ref_i, 1e-5)
+            h = rmsnorm(lib, h)
+        outs[name] = h.clone()
+    torch.cuda.synchronize()
+    pad_same = bool(torch.equal(outs["padded"], outs["single"]))
+    if not (pad_same and peer_layers_ok):
+        d1 = float(((outs["padded"] - outs["single"]).abs().amax(dim=1) / outs["single"].abs().amax(dim=1)).max())
+        print(f"rank {rank} stack: collectives vs single {d1:.3e}, peer-store layers {'ok' if peer_layers_ok else 'MISMATCH'}", flush=True)
+    stack_ok = pad_same and peer_layers_ok
+    # ... and every layer of the stack against the CPU oracle on the input that layer saw (the benchmark's bar for fp32
+    # outputs holds per layer; errors of earlier layers are inputs of later ones, not errors of theirs)
+    import oracle
+    from parity_util import check_rows, oracle_on_gpu_routing
+    try:
+        for i, (h_in, h_out, idx) in enumerate(per_layer):
+            o = oracle_on_gpu_routing(fulls[i].to("cpu"), h_in.cpu().numpy(), idx.cpu().numpy())
+            check_rows(h_out.cpu().numpy(), o["y"])
+        np.testing.assert_allclose(rmsnorm(lib, per_layer[0][1]).cpu().numpy(), oracle.rmsnorm(per_layer[0][1].cpu().numpy()), rtol=1e-5, atol=1e-7)
+    except AssertionError as exc:
+        print(f"rank {rank} stack vs oracle: {exc}", flush=True)
+        stack_ok = False
+    print(f"rank {rank} stack of {L} layers T={T}: {'ok' if stack_ok else 'MISMATCH'}", flush=True)
+    ok = ok and stack_ok
+
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-    dist.destroy_process_group()
-    sys.exit(0 if int(flag.item()) == 1 else 1)
+    torch.cuda.synchronize()
+    dist.barrier()
+    sys.stdout.flush()
+    os._exit(0 if int(flag.item()) == 1 else 1)   # (no communicator teardown: peer mappings stay until the processes end)
 
 
 if __name__ == "__main__":
