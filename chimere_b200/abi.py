@@ -76,6 +76,7 @@ PROTOTYPES = {
     "chimere_b200_moe_ep_finish": (C.c_int, [_LAYER_P, _P, _P, C.c_int, _WS_P, _P, _P]),
     "chimere_b200_moe_ep_pack_p2p": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "chimere_b200_moe_ep_wait": (C.c_int, [_P, C.c_int, C.c_int, _WS_P, _P]),
+    "chimere_b200_moe_experts_packed_p2p": (C.c_int, [_LAYER_P, C.c_int, _P, C.c_int, _P, C.c_int, C.c_int, _WS_P, _P]),
     "chimere_b200_moe_ep_return_p2p": (C.c_int, [_LAYER_P, _WS_P, _P, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "chimere_b200_moe_ep_finish_p2p": (C.c_int, [_LAYER_P, _P, _P, C.c_int, C.c_int, _WS_P, _P, _P, _P]),
     "chimere_b200_moe_permute": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P]),

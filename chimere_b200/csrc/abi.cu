@@ -218,7 +218,7 @@ int chimere_b200_moe_shared_expert(const chimere_moe_layer* w, int T, chimere_mo
 }
 
 static int run_experts(const chimere_moe_layer* w_local, int n_rows, const void* d_packed, int row_bytes, chimere_moe_workspace* ws,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, int32_t* wait_flags = nullptr, int wait_n = 0, int wait_expect = 0) {
     if (n_rows == 0) return 0;
     int rc = check_call(w_local, ws, ws, n_rows, ws);
     if (rc) return rc;
@@ -231,6 +231,7 @@ static int run_experts(const chimere_moe_layer* w_local, int n_rows, const void*
         p.topk_idx = (int32_t*)((uint8_t*)d_packed + w_local->H + 4 * ds);
         p.idx_stride = row_bytes / 4;
     }
+    p.wait_flags = wait_flags; p.wait_n = wait_n; p.wait_expect = wait_expect;
     cudaError_t e = launch_permute(p, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     const Layout L = make_layout(w_local, ws->max_T);
@@ -257,6 +258,13 @@ int chimere_b200_moe_experts_packed(const chimere_moe_layer* w_local, int n_rows
                                     chimere_moe_workspace* ws, cudaStream_t stream) {
     if (!d_rows) return -1;
     return run_experts(w_local, n_rows, d_rows, row_bytes, ws, stream);
+}
+
+int chimere_b200_moe_experts_packed_p2p(const chimere_moe_layer* w_local, int n_rows, const void* d_rows, int row_bytes, int32_t* d_flags,
+                                        int world, int cap, chimere_moe_workspace* ws, cudaStream_t stream) {
+    if (!d_rows || !d_flags) return -1;
+    if (world <= 0 || world > 32 || cap <= 0) return -2;
+    return run_experts(w_local, n_rows, d_rows, row_bytes, ws, stream, d_flags, world, cap);
 }
 
 int chimere_b200_moe_ep_pack(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, void* d_send, int32_t* d_slot,

@@ -34,6 +34,8 @@ struct RouteParams {
     int32_t* group_list;
     int32_t* counters;
     int32_t* status;            // workspace status word (may be null): a bounded wait that ran out raises a bit here
+    int32_t* wait_flags;        // dispatch step alone (expert-parallel owner): counters of the peer-store exchange to wait for first
+    int wait_n, wait_expect;    // ... `wait_n` of them, each has to reach `wait_expect`; they are taken down again (null = none)
     int32_t* dispatch_scratch;  // zeroed scratch for the dispatch of large batches: ceil(T*top_k / 128) * 256 + 260 ints, left
                                 // zeroed again; null = always sort in one CTA
 };

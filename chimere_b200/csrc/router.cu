@@ -673,10 +673,30 @@ static cudaError_t launch_dispatch_split(const RouteParams& p, cudaStream_t stre
 constexpr int kSplitDispatchPairs = 4096;
 static bool use_split_dispatch(const RouteParams& p) { return p.dispatch_scratch != nullptr && p.T * p.top_k >= kSplitDispatchPairs; }
 
-// The dispatch step alone, for callers that bring their own expert ids in p.topk_idx.
+// ---- counters of the expert-parallel exchange by peer stores (see the kernels further down) ----
+__device__ __forceinline__ int ld_acquire_sys(const int32_t* p) { int v; asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
+__device__ __forceinline__ void red_release_sys_add(int32_t* p, int v) { asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+// true when *flag reached `expect` within the bound
+__device__ __forceinline__ bool wait_flag(const int32_t* flag, int expect) {
+    for (int it = 0; it < (1 << 22); ++it) {
+        if (ld_acquire_sys(flag) >= expect) return true;
+        __nanosleep(40);
+    }
+    return false;
+}
+
+// The dispatch step alone, for callers that bring their own expert ids in p.topk_idx.  An expert-parallel owner rank
+// whose rows arrive by peer stores first waits (bounded) for the source ranks' counters and takes them down.
 constexpr int kPermuteIdsRoom = 8192;
 __global__ void __launch_bounds__(256) permute_kernel(const RouteParams p) {
     extern __shared__ __align__(16) float smem_f[];
+    if (p.wait_flags) {
+        if ((int)threadIdx.x < p.wait_n) {
+            if (!wait_flag(p.wait_flags + threadIdx.x, p.wait_expect) && p.status) atomicOr(p.status, kStatusWaitTimeout);
+            p.wait_flags[threadIdx.x] = 0;
+        }
+        __syncthreads();
+    }
     build_dispatch(p, reinterpret_cast<int*>(smem_f), nullptr, kPermuteIdsRoom);
 }
 
@@ -755,17 +775,6 @@ __global__ void __launch_bounds__(128) ep_pack_kernel(const int32_t* topk_idx, c
 // on the same buffers (it needs that peer's answer first), so one counter suffices.
 // Every wait is bounded; a wait that runs out raises the status bit and the kernel goes on.
 // Row: [H int8][d_stride f32][int32 local expert id | -1][int32 token][f32 routing weight], row_bytes a multiple of 16.
-__device__ __forceinline__ int ld_acquire_sys(const int32_t* p) { int v; asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
-__device__ __forceinline__ void red_release_sys_add(int32_t* p, int v) { asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-// true when *flag reached `expect` within the bound
-__device__ __forceinline__ bool wait_flag(const int32_t* flag, int expect) {
-    for (int it = 0; it < (1 << 22); ++it) {
-        if (ld_acquire_sys(flag) >= expect) return true;
-        __nanosleep(40);
-    }
-    return false;
-}
-
 // One CTA per slot s = (destination rank d, position i): the i-th pair (in pair order) whose expert lives on rank d goes
 // to row rank * cap + i of rank d's receive buffer; slots without a pair get id -1.
 __global__ void __launch_bounds__(128) ep_pack_p2p_kernel(const int32_t* topk_idx, const float* topk_w, const int8_t* x_q, const float* x_d,
@@ -930,7 +939,7 @@ static size_t route_smem(int TT, int TE) {
 }
 
 cudaError_t launch_permute(const RouteParams& p, cudaStream_t stream) {
-    if (use_split_dispatch(p)) return launch_dispatch_split(p, stream);
+    if (use_split_dispatch(p) && !p.wait_flags) return launch_dispatch_split(p, stream);
     permute_kernel<<<1, 256, (kDispatchSmemInts + kPermuteIdsRoom) * sizeof(int), stream>>>(p);
     return cudaGetLastError();
 }

@@ -201,9 +201,9 @@ class ExpertParallelMoE:
                                                    pp["peer_flags_in"].data_ptr(), ctr, self.rank, self.E_loc, G, pp["cap"], pp["rb"], st), "ep_pack_p2p")
         # the shared expert needs nothing from other ranks: it runs while the rows travel
         abi.check(lib.chimere_b200_moe_shared_expert(C.byref(self.home), T, C.byref(self.ws_home.ws), st), "shared_expert")
-        abi.check(lib.chimere_b200_moe_ep_wait(pp["flags_in"], G, pp["cap"], C.byref(self.ws_owner.ws), st), "ep_wait")
         n = G * pp["cap"]
-        abi.check(lib.chimere_b200_moe_experts_packed(C.byref(self.owner), n, pp["recv"], pp["rb"], C.byref(self.ws_owner.ws), st), "experts")
+        abi.check(lib.chimere_b200_moe_experts_packed_p2p(C.byref(self.owner), n, pp["recv"], pp["rb"], pp["flags_in"], G, pp["cap"],
+                                                          C.byref(self.ws_owner.ws), st), "experts")
         abi.check(lib.chimere_b200_moe_ep_return_p2p(C.byref(self.owner), C.byref(self.ws_owner.ws), pp["recv"], pp["rb"], pp["peer_back"].data_ptr(),
                                                      pp["peer_flags_back"].data_ptr(), ctr + 256, self.rank, G, T, pp["cap"], st), "ep_return_p2p")
         abi.check(lib.chimere_b200_moe_ep_finish_p2p(C.byref(self.home), pp["back"], pp["flags_back"], G, T, C.byref(self.ws_home.ws), out.data_ptr(),

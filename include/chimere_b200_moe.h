@@ -226,7 +226,7 @@ int chimere_b200_moe_ep_finish(const chimere_moe_layer* w, const float* d_rows, 
  *   d_peer_back  = device array of `world` pointers: rank r's return buffer f32 [world][T][H]
  *   d_ctr        = one int of this rank's scratch, zero at start (ep_finish_p2p; the other entries ignore it)
  * Home rank: route_home -> ep_pack_p2p -> shared_expert -> ep_finish_p2p.
- * Owner rank: ep_wait (the dispatch flags) -> experts_packed on its own receive buffer -> ep_return_p2p, which adds up,
+ * Owner rank: ep_wait -> experts_packed on its own receive buffer (or experts_packed_p2p, which does both) -> ep_return_p2p, which adds up,
  * per (home rank, token), the routing-weighted expert rows in slot order and stores the sums in the home rank's return
  * buffer; ep_finish_p2p waits for the return flags and adds the owners' sums in rank order.  The result differs from
  * the single-GPU layer only in the order of those fp32 additions.  All waits are bounded (status word of `ws`).
@@ -235,6 +235,10 @@ int chimere_b200_moe_ep_pack_p2p(const chimere_moe_layer* w, int T, chimere_moe_
                                  int32_t* const* d_peer_flags, int32_t* d_ctr, int rank, int experts_per_rank, int world, int cap,
                                  int row_bytes, cudaStream_t stream);
 int chimere_b200_moe_ep_wait(int32_t* d_flags, int world, int cap, chimere_moe_workspace* ws, cudaStream_t stream);
+/* experts_packed with the wait folded into its first kernel: waits for `cap` arrivals from each of the `world` source ranks on
+ * d_flags, takes the counters down, then runs the experts on the received rows. */
+int chimere_b200_moe_experts_packed_p2p(const chimere_moe_layer* w_local, int n_rows, const void* d_rows, int row_bytes,
+                                        int32_t* d_flags, int world, int cap, chimere_moe_workspace* ws, cudaStream_t stream);
 int chimere_b200_moe_ep_return_p2p(const chimere_moe_layer* w_local, chimere_moe_workspace* ws_owner, const void* d_rows, int row_bytes,
                                    float* const* d_peer_back, int32_t* const* d_peer_flags, int32_t* d_ctr, int rank, int world, int T,
                                    int cap, cudaStream_t stream);
