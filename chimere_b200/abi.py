@@ -54,6 +54,18 @@ _P = C.c_void_p
 _LAYER_P, _WS_P = C.POINTER(MoeLayer), C.POINTER(MoeWorkspace)
 
 # name -> (restype, argtypes); exactly the declarations of include/chimere_b200_moe.h
+class GgufTensor(C.Structure):
+    """struct chimere_gguf_tensor"""
+    _fields_ = [("ggml_type", C.c_int32), ("n_dims", C.c_int32), ("dims", C.c_int64 * 4), ("file_offset", C.c_int64),
+                ("nbytes", C.c_int64)]
+
+
+class GgufMoeLayer(C.Structure):
+    """struct chimere_gguf_moe_layer"""
+    _fields_ = [(n, GgufTensor) for n in ("router", "gate_exps", "up_exps", "down_exps", "sh_gate", "sh_up", "sh_down", "sh_gate_proj")] + \
+               [(n, C.c_int32) for n in ("has_gate", "has_shared", "has_shared_gate", "has_shared_gate_proj", "H", "E", "F", "F_s")]
+
+
 PROTOTYPES = {
     "chimere_b200_moe_workspace_bytes": (C.c_size_t, [_LAYER_P, C.c_int]),
     "chimere_b200_moe_workspace_init": (C.c_int, [_WS_P, _P, C.c_size_t, _LAYER_P, C.c_int, _P]),
@@ -93,6 +105,15 @@ PROTOTYPES = {
     "chimere_b200_moe_routing_trace": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P, _P, _P]),
     "chimere_b200_moe_experts_prefill": (C.c_int, [_LAYER_P, C.POINTER(PrefillWeights), C.c_int, _WS_P, _P]),
     "chimere_b200_rmsnorm": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_float, _P]),
+    "chimere_b200_gguf_open": (C.c_int, [C.c_char_p, C.POINTER(_P)]),
+    "chimere_b200_gguf_close": (None, [_P]),
+    "chimere_b200_gguf_n_tensors": (C.c_int64, [_P]),
+    "chimere_b200_gguf_tensor_name": (C.c_int, [_P, C.c_int64, C.c_char_p, C.c_int]),
+    "chimere_b200_gguf_find": (C.c_int, [_P, C.c_char_p, C.POINTER(GgufTensor)]),
+    "chimere_b200_gguf_read": (C.c_int, [_P, C.POINTER(GgufTensor), _P, C.c_int64]),
+    "chimere_b200_gguf_meta_u64": (C.c_int, [_P, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "chimere_b200_gguf_meta_str": (C.c_int, [_P, C.c_char_p, C.c_char_p, C.c_int]),
+    "chimere_b200_gguf_moe_layer": (C.c_int, [_P, C.c_int, C.POINTER(GgufMoeLayer)]),
     "chimere_b200_abi_version": (C.c_int, []),
     "chimere_b200_built_for_sm": (C.c_int, []),
     "chimere_quantize_q8_1": (None, [_P, _P, C.c_int64, C.c_int64, _P]),
@@ -103,6 +124,12 @@ PROTOTYPES = {
     "chimere_mmvq_iq3s_f32": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P]),
     "chimere_mmvq_q8_0_f32": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P]),
     "chimere_mmvq_q4_0_f32": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P]),
+    "chimere_mmvq_q5k": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "chimere_mmvq_q4k": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "chimere_mmvq_q6k": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "chimere_mmvq_q5k_f32": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P]),
+    "chimere_mmvq_q4k_f32": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P]),
+    "chimere_mmvq_q6k_f32": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P]),
     "chimere_mmvq_iq3s_batched": (None, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int, _P]),
     "chimere_mmvq_q4_0_batched": (None, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int, _P]),
     "chimere_mmvq_q8_0_batched": (None, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int, _P]),
@@ -131,7 +158,8 @@ def load() -> C.CDLL:
 
 ERRORS = {-1: "null pointer", -2: "bad dimension", -3: "unsupported weight type", -4: "workspace too small",
           -5: "misaligned arena", -6: "entry not available", -7: "larger than the built-in scratch",
-          -8: "first call on this device was made during stream capture"}
+          -8: "first call on this device was made during stream capture", -9: "file I/O", -10: "not a GGUF v2/v3 file or truncated",
+          -11: "no such tensor or key"}
 
 
 def check(rc: int, what: str) -> None:

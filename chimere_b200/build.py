@@ -16,7 +16,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libchimere_b200_moe.so")
-SOURCES = ["abi.cu", "gemm_i8.cu", "gemv.cu", "gemv_tiled.cu", "pack.cu", "router.cu"]
+SOURCES = ["abi.cu", "gemm_i8.cu", "gemv.cu", "gemv_tiled.cu", "gguf.cpp", "kquant.cu", "pack.cu", "router.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--compiler-options", "-fPIC", "-shared"]
 

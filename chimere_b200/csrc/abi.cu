@@ -800,6 +800,32 @@ void chimere_mmvq_q4_0_f32(const void* weights, const float* input_f32, float* o
                            void* q8_scratch, cudaStream_t stream) {
     mmvq_f32(CHIMERE_TYPE_Q4_0, weights, input_f32, output, ncols, nrows, ncols_padded, q8_scratch, stream);
 }
+void chimere_mmvq_q5k(const void* weights, const void* input_q8, float* output, int ncols, int nrows, int, cudaStream_t stream) {
+    launch_mmvq_kquant(CHIMERE_TYPE_Q5_K, weights, input_q8, output, ncols, nrows, stream);
+}
+void chimere_mmvq_q4k(const void* weights, const void* input_q8, float* output, int ncols, int nrows, int, cudaStream_t stream) {
+    launch_mmvq_kquant(CHIMERE_TYPE_Q4_K, weights, input_q8, output, ncols, nrows, stream);
+}
+void chimere_mmvq_q6k(const void* weights, const void* input_q8, float* output, int ncols, int nrows, int, cudaStream_t stream) {
+    launch_mmvq_kquant(CHIMERE_TYPE_Q6_K, weights, input_q8, output, ncols, nrows, stream);
+}
+static void mmvq_kquant_f32(int wtype, const void* weights, const float* input_f32, float* output, int ncols, int nrows, int ncols_padded,
+                            void* q8_scratch, cudaStream_t stream) {
+    launch_quantize_q8_1(input_f32, q8_scratch, ncols, ncols_padded, 1, stream);
+    launch_mmvq_kquant(wtype, weights, q8_scratch, output, ncols, nrows, stream);
+}
+void chimere_mmvq_q5k_f32(const void* weights, const float* input_f32, float* output, int ncols, int nrows, int ncols_padded,
+                          void* q8_scratch, cudaStream_t stream) {
+    mmvq_kquant_f32(CHIMERE_TYPE_Q5_K, weights, input_f32, output, ncols, nrows, ncols_padded, q8_scratch, stream);
+}
+void chimere_mmvq_q4k_f32(const void* weights, const float* input_f32, float* output, int ncols, int nrows, int ncols_padded,
+                          void* q8_scratch, cudaStream_t stream) {
+    mmvq_kquant_f32(CHIMERE_TYPE_Q4_K, weights, input_f32, output, ncols, nrows, ncols_padded, q8_scratch, stream);
+}
+void chimere_mmvq_q6k_f32(const void* weights, const float* input_f32, float* output, int ncols, int nrows, int ncols_padded,
+                          void* q8_scratch, cudaStream_t stream) {
+    mmvq_kquant_f32(CHIMERE_TYPE_Q6_K, weights, input_f32, output, ncols, nrows, ncols_padded, q8_scratch, stream);
+}
 void chimere_mmvq_iq3s_batched(const void* all_weights, const void* input_q8, float* output, const int* expert_ids, int ncols,
                                int nrows, int, int64_t expert_stride, int64_t input_stride, int top_k, cudaStream_t stream) {
     launch_mmvq(CHIMERE_TYPE_IQ3_S, all_weights, input_q8, output, expert_ids, ncols, nrows, expert_stride, input_stride, top_k, stream);

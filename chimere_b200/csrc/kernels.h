@@ -104,6 +104,8 @@ cudaError_t launch_down(const GemvParams& p, int max_entries, cudaStream_t strea
 // Plain batched GEMV (legacy operator entries): y[slot][row] = W[ids[slot]][row] . xq8[slot].
 cudaError_t launch_mmvq(int wtype, const void* w, const void* xq8, float* y, const int* ids, int ncols, int nrows,
                         int64_t expert_stride, int64_t input_stride, int nslots, cudaStream_t stream);
+// K-quant rows (CHIMERE_TYPE_Q4_K / Q5_K / Q6_K) against one Q8_1 row: y[nrows] = W . x_q8
+cudaError_t launch_mmvq_kquant(int wtype, const void* w, const void* xq8, float* y, int ncols, int nrows, cudaStream_t stream);
 cudaError_t launch_block_sumi(int wtype, const void* w, const void* xq8, int32_t* sumi, int ncols, int nrows,
                               cudaStream_t stream);
 cudaError_t launch_quantize_q8_1(const float* x, void* out, int64_t ncols, int64_t ncols_padded, int batch,

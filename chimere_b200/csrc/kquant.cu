@@ -1,0 +1,116 @@
+// Plain GEMV on K-quant super-blocks (Q4_K, Q5_K, Q6_K) against one Q8_1 row: the entries chimere_mmvq_q4k / _q5k / _q6k
+// that the reference binds to its dependency's mul_mat_vec_*_K_q8_1 kernels (ffi/ggml_cuda_gemv.cu:118-172).  The
+// production files keep the shared expert in Q5_K (moe_ffn.rs:1597-1650); the routed experts never use these types.
+//
+// A warp owns one output row.  Lane l takes the 32-weight sub-blocks l, l+32, ... of the row: it reads the sub-block's
+// quants as eight 32-bit words, the Q8_1 block beside it, and adds
+//     d * d8 * sc_j * dot - dmin * m_j * s8        (Q4_K, Q5_K: six-bit scale sc_j and min m_j, s8 = d8 * sum of the quants)
+//     d * d8 * (sc_a * dot_a + sc_b * dot_b)       (Q6_K: one int8 scale per 16 weights)
+// in ascending sub-block order; the lanes' sums meet in a butterfly.  HBM-bound: a row is read once, coalesced by
+// super-block (consecutive lanes read consecutive 32-weight pieces), the Q8_1 row stays in L1/L2.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace chimere {
+
+namespace {
+
+constexpr int kRowsPerCta = 8;   // warps per CTA
+
+__device__ __forceinline__ uint32_t ld32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
+
+// six-bit scale and min of sub-block j from the twelve packed bytes (ffi/src/lib.rs:368-383)
+__device__ __forceinline__ void scale_min_k4(int j, const uint8_t* sc, int& s, int& m) {
+    if (j < 4) { s = sc[j] & 63; m = sc[j + 4] & 63; }
+    else { s = (sc[j + 4] & 0x0F) | ((sc[j - 4] >> 6) << 4); m = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4); }
+}
+
+template <int TYPE> struct KBlock;
+template <> struct KBlock<CHIMERE_TYPE_Q4_K> { static constexpr int kBytes = 144, kQs = 16; };
+template <> struct KBlock<CHIMERE_TYPE_Q5_K> { static constexpr int kBytes = 176, kQs = 48; };
+template <> struct KBlock<CHIMERE_TYPE_Q6_K> { static constexpr int kBytes = 210, kQs = 0; };
+
+// One 32-weight sub-block j of super-block `blk` against the Q8_1 block `xb` (36 bytes: f16 d, f16 s, 32 int8).
+template <int TYPE>
+__device__ __forceinline__ float sub_block(const uint8_t* blk, int j, const uint8_t* xb) {
+    const __half2 ds = *reinterpret_cast<const __half2*>(xb);
+    const float d8 = __low2float(ds), s8 = __high2float(ds);
+    int q8[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) q8[g] = (int)ld32(xb + 4 + 4 * g);
+    if (TYPE == CHIMERE_TYPE_Q6_K) {
+        // 210-byte blocks are only 2-byte aligned
+        const int grp = j >> 2, s = j & 3;
+        const uint8_t* ql = blk + 64 * grp + 32 * (s & 1);
+        const uint8_t* qh = blk + 128 + 32 * grp;
+        const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192) + 8 * grp + 2 * s;
+        const float d = h2f(ld_u16(blk + 208));
+        int da = 0, db = 0;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            const uint32_t lo = ld_u32_a2(ql + 4 * g), hi = ld_u32_a2(qh + 4 * g);
+            const uint32_t nib = (s >> 1) ? (lo >> 4) & 0x0F0F0F0Fu : lo & 0x0F0F0F0Fu;
+            const uint32_t v = nib | (((hi >> (2 * s)) & 0x03030303u) << 4);      // 0..63 per byte
+            const int w = (int)__vsub4(v, 0x20202020u);                           // -32..31 per byte
+            if (g < 4) da = __dp4a(w, q8[g], da); else db = __dp4a(w, q8[g], db);
+        }
+        return d * d8 * (float)((int)sc[0] * da + (int)sc[1] * db);
+    } else {
+        const float d = h2f(ld_u16(blk)), dmin = h2f(ld_u16(blk + 2));
+        int sc, mn;
+        scale_min_k4(j, blk + 4, sc, mn);
+        const uint8_t* qs = blk + KBlock<TYPE>::kQs + 32 * (j >> 1);
+        int dot = 0;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            const uint32_t lo = ld32(qs + 4 * g);
+            uint32_t v = (j & 1) ? (lo >> 4) & 0x0F0F0F0Fu : lo & 0x0F0F0F0Fu;
+            if (TYPE == CHIMERE_TYPE_Q5_K) v |= ((ld32(blk + 16 + 4 * g) >> j) & 0x01010101u) << 4;
+            dot = __dp4a((int)v, q8[g], dot);
+        }
+        return fmaf(-(dmin * (float)mn), s8, d * d8 * (float)(sc * dot));
+    }
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(32 * kRowsPerCta) kquant_mmvq_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ xq8,
+                                                                      float* __restrict__ y, int ncols, int nrows) {
+    const int lane = threadIdx.x & 31, row = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
+    if (row >= nrows) return;
+    const int nsub = ncols >> 5;
+    const uint8_t* rowp = w + (size_t)row * (size_t)(ncols >> 8) * KBlock<TYPE>::kBytes;
+    float acc = 0.0f;
+    for (int sb = lane; sb < nsub; sb += 32)
+        acc += sub_block<TYPE>(rowp + (size_t)(sb >> 3) * KBlock<TYPE>::kBytes, sb & 7, xq8 + (size_t)sb * kQ81Bytes);
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (lane == 0) y[row] = acc;
+}
+
+}  // namespace
+
+cudaError_t launch_mmvq_kquant(int wtype, const void* w, const void* xq8, float* y, int ncols, int nrows, cudaStream_t stream) {
+    if (nrows <= 0) return cudaSuccess;
+    if (ncols <= 0 || (ncols & 255) || ((uintptr_t)xq8 & 3)) return cudaErrorInvalidValue;
+    const dim3 grid((nrows + kRowsPerCta - 1) / kRowsPerCta);
+    const uint8_t* wp = (const uint8_t*)w;
+    const uint8_t* xp = (const uint8_t*)xq8;
+    switch (wtype) {
+        case CHIMERE_TYPE_Q4_K:
+            if ((uintptr_t)w & 3) return cudaErrorInvalidValue;
+            kquant_mmvq_kernel<CHIMERE_TYPE_Q4_K><<<grid, 32 * kRowsPerCta, 0, stream>>>(wp, xp, y, ncols, nrows); break;
+        case CHIMERE_TYPE_Q5_K:
+            if ((uintptr_t)w & 3) return cudaErrorInvalidValue;
+            kquant_mmvq_kernel<CHIMERE_TYPE_Q5_K><<<grid, 32 * kRowsPerCta, 0, stream>>>(wp, xp, y, ncols, nrows); break;
+        case CHIMERE_TYPE_Q6_K:
+            if ((uintptr_t)w & 1) return cudaErrorInvalidValue;
+            kquant_mmvq_kernel<CHIMERE_TYPE_Q6_K><<<grid, 32 * kRowsPerCta, 0, stream>>>(wp, xp, y, ncols, nrows); break;
+        default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace chimere

@@ -24,10 +24,32 @@ import numpy as np
 import torch
 
 TYPE_Q4_0, TYPE_Q8_0, TYPE_IQ3_S = 2, 8, 21
-TYPE_NAMES = {TYPE_Q4_0: "Q4_0", TYPE_Q8_0: "Q8_0", TYPE_IQ3_S: "IQ3_S"}
-BLOCK_ELEMS = {TYPE_Q4_0: 32, TYPE_Q8_0: 32, TYPE_IQ3_S: 256}
-BLOCK_BYTES = {TYPE_Q4_0: 18, TYPE_Q8_0: 34, TYPE_IQ3_S: 110}
+# K-quant super-blocks: only the plain GEMV entries (chimere_mmvq_q4k / _q5k / _q6k) take them
+TYPE_Q4_K, TYPE_Q5_K, TYPE_Q6_K = 12, 13, 14
+TYPE_NAMES = {TYPE_Q4_0: "Q4_0", TYPE_Q8_0: "Q8_0", TYPE_IQ3_S: "IQ3_S", TYPE_Q4_K: "Q4_K", TYPE_Q5_K: "Q5_K", TYPE_Q6_K: "Q6_K"}
+BLOCK_ELEMS = {TYPE_Q4_0: 32, TYPE_Q8_0: 32, TYPE_IQ3_S: 256, TYPE_Q4_K: 256, TYPE_Q5_K: 256, TYPE_Q6_K: 256}
+BLOCK_BYTES = {TYPE_Q4_0: 18, TYPE_Q8_0: 34, TYPE_IQ3_S: 110, TYPE_Q4_K: 144, TYPE_Q5_K: 176, TYPE_Q6_K: 210}
 Q8_1_BYTES = 36
+
+
+def random_kquant_rows(qtype: int, rows: int, cols: int, seed: int = 0, scale: float = 0.02) -> np.ndarray:
+    """Seeded rows of valid K-quant super-blocks with every bit field drawn at random (quants, six-bit scales and mins or
+    int8 scales, high bits) and f16 super-block scales sized so that the weights come out near N(0, scale).  Stands in
+    for a quantizer: the GEMV entries decode blocks, they never make them.  Returns u8 [rows, row_bytes]."""
+    assert qtype in (TYPE_Q4_K, TYPE_Q5_K, TYPE_Q6_K) and cols % 256 == 0
+    rng = np.random.default_rng(seed)
+    nb, bb = rows * (cols // 256), BLOCK_BYTES[qtype]
+    blk = rng.integers(0, 256, size=(nb, bb), dtype=np.uint8)
+    if qtype == TYPE_Q6_K:       # weight = d * sc * q, sc int8, q in -32..31
+        d = (scale / (64.0 * 18.0)) * rng.uniform(0.5, 1.5, nb)
+        blk[:, 208:210] = d.astype(np.float16).view(np.uint8).reshape(nb, 2)
+    else:                        # weight = d * sc * q - dmin * m, sc and m in 0..63, q in 0..15 or 0..31
+        qmax = 15.0 if qtype == TYPE_Q4_K else 31.0
+        d = (scale / (32.0 * qmax * 0.3)) * rng.uniform(0.5, 1.5, nb)
+        dmin = d * qmax * 0.5 * rng.uniform(0.8, 1.2, nb)
+        blk[:, 0:2] = d.astype(np.float16).view(np.uint8).reshape(nb, 2)
+        blk[:, 2:4] = dmin.astype(np.float16).view(np.uint8).reshape(nb, 2)
+    return blk.reshape(rows, cols // 256 * bb)
 
 
 def row_bytes(qtype: int, ncols: int) -> int:

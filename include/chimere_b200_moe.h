@@ -36,7 +36,9 @@ typedef struct CUstream_st* cudaStream_t;
 #endif
 
 /* ggml tensor-type ids of the weight formats this path supports. */
-enum { CHIMERE_TYPE_Q4_0 = 2, CHIMERE_TYPE_Q8_0 = 8, CHIMERE_TYPE_IQ3_S = 21 };
+enum { CHIMERE_TYPE_Q4_0 = 2, CHIMERE_TYPE_Q8_0 = 8, CHIMERE_TYPE_IQ3_S = 21,
+       /* K-quant super-blocks: plain GEMV entries (chimere_mmvq_q4k / _q5k / _q6k) only, not a chimere_moe_layer weight type */
+       CHIMERE_TYPE_Q4_K = 12, CHIMERE_TYPE_Q5_K = 13, CHIMERE_TYPE_Q6_K = 14 };
 /* Router variants. */
 enum { CHIMERE_ROUTE_SOFTMAX_RENORM = 0,  /* softmax over E, top-k on probabilities, renormalise (chimere_kernels.cu:1150-1223) */
        CHIMERE_ROUTE_SIGMOID_NORM_SCALE = 1 /* sigmoid scores, top-k, normalise to sum 1, multiply by route_scale (Nemotron-H style) */ };
@@ -363,6 +365,21 @@ void chimere_mmvq_q8_0_f32(const void* weights, const float* input_f32, float* o
                            int ncols_padded, void* q8_scratch, cudaStream_t stream);
 void chimere_mmvq_q4_0_f32(const void* weights, const float* input_f32, float* output, int ncols, int nrows,
                            int ncols_padded, void* q8_scratch, cudaStream_t stream);
+/* ggml_cuda_gemv.cu:118-131, 147-172 and :302-321, 353-391 (Rust declarations src/kernels/ggml_gpu.rs:113-151, 162-216): the
+ * K-quant matrices of the production files (the shared expert is Q5_K there, moe_ffn.rs:1597-1650).  ncols a multiple of
+ * 256.  y = sum over 32-weight sub-blocks of d*d8*sc*dot - dmin*m*s8 (Q4_K, Q5_K) or d*d8*(sc_a*dot_a + sc_b*dot_b) (Q6_K). */
+void chimere_mmvq_q5k(const void* weights, const void* input_q8, float* output, int ncols, int nrows, int nrows_y_padded,
+                      cudaStream_t stream);
+void chimere_mmvq_q4k(const void* weights, const void* input_q8, float* output, int ncols, int nrows, int nrows_y_padded,
+                      cudaStream_t stream);
+void chimere_mmvq_q6k(const void* weights, const void* input_q8, float* output, int ncols, int nrows, int nrows_y_padded,
+                      cudaStream_t stream);
+void chimere_mmvq_q5k_f32(const void* weights, const float* input_f32, float* output, int ncols, int nrows, int ncols_padded,
+                          void* q8_scratch, cudaStream_t stream);
+void chimere_mmvq_q4k_f32(const void* weights, const float* input_f32, float* output, int ncols, int nrows, int ncols_padded,
+                          void* q8_scratch, cudaStream_t stream);
+void chimere_mmvq_q6k_f32(const void* weights, const float* input_f32, float* output, int ncols, int nrows, int ncols_padded,
+                          void* q8_scratch, cudaStream_t stream);
 /* ggml_cuda_gemv.cu:243-279: top_k expert GEMVs in one launch, expert ids read on the device.
  * input_stride = 0: one shared Q8_1 input; otherwise bytes between the per-slot inputs. */
 void chimere_mmvq_iq3s_batched(const void* all_weights, const void* input_q8, float* output,
@@ -382,6 +399,39 @@ void chimere_mmvq_q8_0_batched(const void* all_weights, const void* input_q8, fl
 int chimere_q8_1_block_bytes(void);   /* 36 */
 int chimere_q8_1_block_elems(void);   /* 32 */
 int chimere_matrix_row_padding(void); /* 512 */
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * GGUF ingestion for this path (host side).  Replaces, for the MoE tensors, the reference's file parser
+ * (src/gguf_loader.rs:286-455: header, metadata, tensor infos, data offset) and the per-layer tensor look-up of
+ * compute_graph.rs:992-999, 1400-1500.  Tensor bytes are handed over as they lie in the file (the raw ggml blocks the
+ * pack entries above take).  Errors: -1 bad argument, -2 shapes that do not fit, -9 I/O, -10 not a GGUF v2/v3 file or a
+ * truncated one, -11 no such tensor / key. */
+typedef struct chimere_gguf chimere_gguf;
+typedef struct {
+    int32_t ggml_type;     /* ggml type id (0 F32, 2 Q4_0, 8 Q8_0, 12-14 Q4_K/Q5_K/Q6_K, 21 IQ3_S, ...) */
+    int32_t n_dims;
+    int64_t dims[4];       /* innermost first, 1 beyond n_dims */
+    int64_t file_offset;   /* absolute */
+    int64_t nbytes;        /* -1: a type whose block size is not known here */
+} chimere_gguf_tensor;
+typedef struct {
+    chimere_gguf_tensor router, gate_exps, up_exps, down_exps, sh_gate, sh_up, sh_down, sh_gate_proj;
+    int32_t has_gate, has_shared, has_shared_gate, has_shared_gate_proj;
+    int32_t H, E, F, F_s;
+} chimere_gguf_moe_layer;
+int chimere_b200_gguf_open(const char* path, chimere_gguf** out);
+void chimere_b200_gguf_close(chimere_gguf* g);
+int64_t chimere_b200_gguf_n_tensors(const chimere_gguf* g);
+/* name of tensor i into buf (truncated to buflen - 1); returns its full length */
+int chimere_b200_gguf_tensor_name(const chimere_gguf* g, int64_t i, char* buf, int buflen);
+int chimere_b200_gguf_find(const chimere_gguf* g, const char* name, chimere_gguf_tensor* out);
+/* the tensor's bytes into host memory (pinned, if an upload follows) */
+int chimere_b200_gguf_read(const chimere_gguf* g, const chimere_gguf_tensor* t, void* dst, int64_t dst_bytes);
+/* integer-valued metadata (any integer width, bool), e.g. "<arch>.expert_count", "<arch>.expert_used_count" */
+int chimere_b200_gguf_meta_u64(const chimere_gguf* g, const char* key, uint64_t* out);
+int chimere_b200_gguf_meta_str(const chimere_gguf* g, const char* key, char* buf, int buflen);
+/* blk.<layer>.ffn_gate_inp / ffn_{gate,up,down}_exps / ffn_{gate,up,down}_shexp / ffn_gate_inp_shexp, shapes checked */
+int chimere_b200_gguf_moe_layer(const chimere_gguf* g, int layer, chimere_gguf_moe_layer* out);
 
 #ifdef __cplusplus
 }

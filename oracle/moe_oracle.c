@@ -37,6 +37,9 @@ static const uint32_t iq3s_grid[512] = {
 #define Q4_0_BYTES 18
 #define Q8_0_BYTES 34
 #define IQ3S_BYTES 110
+#define Q4_K_BYTES 144
+#define Q5_K_BYTES 176
+#define Q6_K_BYTES 210
 
 /* ------------------------------------------------------------------ f16 <-> f32 (IEEE) --- */
 
@@ -256,6 +259,9 @@ int64_t orc_row_bytes(int type, int ncols) {
         case CHIMERE_TYPE_Q4_0: return (int64_t)(ncols / 32) * Q4_0_BYTES;
         case CHIMERE_TYPE_Q8_0: return (int64_t)(ncols / 32) * Q8_0_BYTES;
         case CHIMERE_TYPE_IQ3_S: return (int64_t)(ncols / 256) * IQ3S_BYTES;
+        case CHIMERE_TYPE_Q4_K: return (int64_t)(ncols / 256) * Q4_K_BYTES;
+        case CHIMERE_TYPE_Q5_K: return (int64_t)(ncols / 256) * Q5_K_BYTES;
+        case CHIMERE_TYPE_Q6_K: return (int64_t)(ncols / 256) * Q6_K_BYTES;
         default: return -1;
     }
 }
@@ -299,18 +305,112 @@ static inline float row_dot(int type, const uint8_t* row, const uint8_t* xq8, in
     return acc;
 }
 
-/* y[nrows] = W . x_q8 for one Q8_1 input row (chimere_mmvq_* semantics, ffi/ggml_cuda_gemv.cu:105-116). */
+/* ---- K-quant super-blocks of 256 weights (the shared expert of the production files is Q5_K; wrappers
+ * ffi/ggml_cuda_gemv.cu:118-172).  Layouts as the reference reads them:
+ *   Q5_K 176 B: f16 d, f16 dmin, scales[12] (eight 6-bit scales and eight 6-bit mins), qh[32], qs[128]
+ *               -- ffi/src/lib.rs:51-54,396-443, src/gguf_loader.rs (dequantize_q5_k)
+ *   Q4_K 144 B: the same without qh -- src/gguf_loader.rs:1274-1345
+ *   Q6_K 210 B: ql[128], qh[64], int8 scales[16] (one per 16 weights), f16 d -- src/gguf_loader.rs:855-927
+ * Sub-block j (32 weights) of a Q4_K/Q5_K super-block: nibbles of qs[32*(j/2) .. +32), low for even j, high for
+ * odd j; Q5_K adds 16 where bit j of qh[l] is set.  weight = d*sc_j*q - dmin*m_j. */
+static inline void scale_min_k4(int j, const uint8_t* sc, int* s, int* m) {   /* ffi/src/lib.rs:368-383 */
+    if (j < 4) { *s = sc[j] & 63; *m = sc[j + 4] & 63; }
+    else { *s = (sc[j + 4] & 0x0F) | ((sc[j - 4] >> 6) << 4); *m = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4); }
+}
+/* the 32 unsigned quants of sub-block j */
+static inline void q45k_sub_quants(int type, const uint8_t* blk, int j, int32_t* q) {
+    const uint8_t* qh = blk + 16;
+    const uint8_t* qs = blk + (type == CHIMERE_TYPE_Q5_K ? 48 : 16) + 32 * (j / 2);
+    for (int l = 0; l < 32; l++) {
+        int v = (j & 1) ? (qs[l] >> 4) : (qs[l] & 0x0F);
+        if (type == CHIMERE_TYPE_Q5_K && ((qh[l] >> j) & 1)) v += 16;
+        q[l] = v;
+    }
+}
+/* the 32 signed quants of sub-block j (0..7) of a Q6_K super-block and its two scales (first / second 16 weights) */
+static inline void q6k_sub_quants(const uint8_t* blk, int j, int32_t* q, int* sc_a, int* sc_b) {
+    const int grp = j / 4, s = j % 4;
+    const uint8_t* ql = blk + 64 * grp + 32 * (s & 1);
+    const uint8_t* qh = blk + 128 + 32 * grp;
+    const int8_t* sc = (const int8_t*)(blk + 192) + 8 * grp + 2 * s;
+    for (int l = 0; l < 32; l++) {
+        const int nib = (s >> 1) ? (ql[l] >> 4) : (ql[l] & 0x0F);
+        q[l] = (nib | (((qh[l] >> (2 * s)) & 3) << 4)) - 32;
+    }
+    *sc_a = sc[0]; *sc_b = sc[1];
+}
+static int is_kquant(int type) { return type == CHIMERE_TYPE_Q4_K || type == CHIMERE_TYPE_Q5_K || type == CHIMERE_TYPE_Q6_K; }
+
+/* One row of a K-quant matrix against one Q8_1 row (f16 d, f16 s = d * sum of quants): the formula of
+ * vec_dot_q5_k_q8_1, ffi/src/lib.rs:385-499 -- per sub-block d*d8*sc*dot, minus dmin*m*s8 -- in f32, sub-blocks ascending. */
+static float kquant_row_dot(int type, const uint8_t* row, const uint8_t* xq8, int ncols) {
+    float acc = 0.0f;
+    const int bytes = type == CHIMERE_TYPE_Q4_K ? Q4_K_BYTES : type == CHIMERE_TYPE_Q5_K ? Q5_K_BYTES : Q6_K_BYTES;
+    for (int sb = 0; sb < ncols / 256; sb++) {
+        const uint8_t* blk = row + (size_t)sb * bytes;
+        uint16_t h;
+        float d, dmin = 0.0f;
+        if (type == CHIMERE_TYPE_Q6_K) { memcpy(&h, blk + 208, 2); d = orc_f16_to_f32(h); }
+        else { memcpy(&h, blk, 2); d = orc_f16_to_f32(h); memcpy(&h, blk + 2, 2); dmin = orc_f16_to_f32(h); }
+        for (int j = 0; j < 8; j++) {
+            const uint8_t* xb = xq8 + (size_t)(sb * 8 + j) * Q8_1_BYTES;
+            const int8_t* q8 = (const int8_t*)xb + 4;
+            memcpy(&h, xb, 2); const float d8 = orc_f16_to_f32(h);
+            memcpy(&h, xb + 2, 2); const float s8 = orc_f16_to_f32(h);
+            int32_t q[32];
+            if (type == CHIMERE_TYPE_Q6_K) {
+                int sa, sb2; q6k_sub_quants(blk, j, q, &sa, &sb2);
+                int32_t da = 0, db = 0;
+                for (int l = 0; l < 16; l++) { da += q[l] * (int32_t)q8[l]; db += q[16 + l] * (int32_t)q8[16 + l]; }
+                acc = fmaf(d * d8, (float)(sa * da + sb2 * db), acc);
+            } else {
+                int sc, mn; scale_min_k4(j, blk + 4, &sc, &mn);
+                q45k_sub_quants(type, blk, j, q);
+                int32_t dot = 0;
+                for (int l = 0; l < 32; l++) dot += q[l] * (int32_t)q8[l];
+                acc = fmaf(d * d8, (float)(sc * dot), acc);
+                acc = fmaf(-(dmin * (float)mn), s8, acc);
+            }
+        }
+    }
+    return acc;
+}
+
+/* y[nrows] = W . x_q8 for one Q8_1 input row (chimere_mmvq_* semantics, ffi/ggml_cuda_gemv.cu:105-172). */
 void orc_gemv(int type, const void* W, const void* xq8, float* y, int ncols, int nrows) {
     int nb = ncols / 32; int64_t rb = orc_row_bytes(type, ncols);
     #pragma omp parallel for schedule(static)
     for (int r = 0; r < nrows; r++)
-        y[r] = row_dot(type, (const uint8_t*)W + (size_t)r * rb, (const uint8_t*)xq8, nb);
+        y[r] = is_kquant(type) ? kquant_row_dot(type, (const uint8_t*)W + (size_t)r * rb, (const uint8_t*)xq8, ncols)
+                               : row_dot(type, (const uint8_t*)W + (size_t)r * rb, (const uint8_t*)xq8, nb);
 }
 
 /* Dequantise n elements (n multiple of the block size) -- gguf_loader.rs:752-772 (Q4_0),
  * :793-837 (Q8_0), :1022-1170 (IQ3_S) / dequant_iq3s chimere_kernels.cu:203-290. */
 void orc_dequant(int type, const void* W, float* out, int64_t n) {
     const uint8_t* p = (const uint8_t*)W;
+    if (is_kquant(type)) {   /* gguf_loader.rs:855-927 (Q6_K), :1274-1345 (Q4_K); ffi/src/lib.rs:576-640 (Q5_K) */
+        const int bytes = type == CHIMERE_TYPE_Q4_K ? Q4_K_BYTES : type == CHIMERE_TYPE_Q5_K ? Q5_K_BYTES : Q6_K_BYTES;
+        for (int64_t b = 0; b < n / 256; b++) {
+            const uint8_t* blk = p + b * bytes;
+            uint16_t h;
+            for (int j = 0; j < 8; j++) {
+                int32_t q[32];
+                if (type == CHIMERE_TYPE_Q6_K) {
+                    memcpy(&h, blk + 208, 2); const float d = orc_f16_to_f32(h);
+                    int sa, sb; q6k_sub_quants(blk, j, q, &sa, &sb);
+                    for (int l = 0; l < 32; l++) out[b * 256 + j * 32 + l] = d * (float)(l < 16 ? sa : sb) * (float)q[l];
+                } else {
+                    memcpy(&h, blk, 2); const float d = orc_f16_to_f32(h);
+                    memcpy(&h, blk + 2, 2); const float dmin = orc_f16_to_f32(h);
+                    int sc, mn; scale_min_k4(j, blk + 4, &sc, &mn);
+                    q45k_sub_quants(type, blk, j, q);
+                    for (int l = 0; l < 32; l++) out[b * 256 + j * 32 + l] = d * (float)sc * (float)q[l] - dmin * (float)mn;
+                }
+            }
+        }
+        return;
+    }
     if (type == CHIMERE_TYPE_Q4_0) {
         for (int64_t b = 0; b < n / 32; b++) {
             const uint8_t* blk = p + b * Q4_0_BYTES; uint16_t dh; memcpy(&dh, blk, 2); float d = orc_f16_to_f32(dh);

@@ -408,3 +408,54 @@ def test_routing_trace_layout_and_load():
         assert np.array_equal(data[i], idx.astype(np.uint8))
     ref_load = np.bincount(np.concatenate([i.reshape(-1) for i in idx_layers]), minlength=cfg.E)
     assert np.array_equal(load.cpu().numpy(), ref_load)
+
+
+@pytest.mark.parametrize("qtype,fn", [(formats.TYPE_Q4_K, "chimere_mmvq_q4k"), (formats.TYPE_Q5_K, "chimere_mmvq_q5k"),
+                                      (formats.TYPE_Q6_K, "chimere_mmvq_q6k")])
+@pytest.mark.parametrize("rows,cols", [(512, 2048), (2048, 512), (77, 256)])
+def test_legacy_mmvq_kquants(qtype, fn, rows, cols):
+    """The K-quant GEMV entries (ffi/ggml_cuda_gemv.cu:118-172) at the shared expert's shapes (F_s x H, H x F_s) and a ragged
+    one, with the f32-input forms beside them (:302-321, :353-391)."""
+    lib = abi.load()
+    W = formats.random_kquant_rows(qtype, rows, cols, seed=rows + qtype)
+    x = np.random.default_rng(rows).standard_normal(cols).astype(np.float32)
+    ref_q = oracle.quantize_q8_1(x)
+    ref = oracle.gemv(qtype, W, ref_q, cols, rows)
+    Wd, xd = torch.from_numpy(W).cuda(), torch.from_numpy(x).cuda()
+    pad = (cols + 511) // 512 * 512
+    xq = torch.zeros(pad // 32 * 36, dtype=torch.uint8, device="cuda")
+    lib.chimere_quantize_q8_1(xd.data_ptr(), xq.data_ptr(), cols, pad, None)
+    y = torch.empty(rows, device="cuda")
+    getattr(lib, fn)(Wd.data_ptr(), xq.data_ptr(), y.data_ptr(), cols, rows, pad // 32, None)
+    scratch = torch.full((pad // 32 * 36,), 0xCD, dtype=torch.uint8, device="cuda")
+    y2 = torch.empty(rows, device="cuda")
+    getattr(lib, fn + "_f32")(Wd.data_ptr(), xd.data_ptr(), y2.data_ptr(), cols, rows, pad, scratch.data_ptr(), None)
+    torch.cuda.synchronize()
+    assert np.array_equal(xq.cpu().numpy()[:ref_q.size], ref_q)
+    assert np.array_equal(scratch.cpu().numpy()[:ref_q.size], ref_q)
+    # same integer dots and scales; only the order of the fp32 additions differs
+    tol = 2e-5 * np.abs(ref).max()
+    np.testing.assert_allclose(y.cpu().numpy(), ref, rtol=0, atol=tol)
+    assert torch.equal(y, y2)
+
+
+def test_layer_loaded_from_a_gguf_file_gives_the_same_output(tmp_path):
+    """File -> C-ABI reader -> pinned buffer -> device -> pack -> layer call, against the same layer built in memory."""
+    pytest.importorskip("gguf")
+    from chimere_b200.gguf_io import GgufFile, load_moe_layer
+    from test_gguf_ingest import _write
+    cfg = configs.scaled(configs.QWEN_IQ3S, E=16, F=256, F_s=256, H=512)
+    host = configs.make_layer(cfg, seed=21)
+    path = tmp_path / "layer.gguf"
+    _write(path, {2: host})
+    with GgufFile(path) as g:
+        loaded = load_moe_layer(g, 2, device="cuda")
+    x = configs.make_input(cfg, 8, device="cuda")
+    outs = []
+    for raw in (host.to("cuda"), loaded):
+        tiled = MoeWeightsTiled(raw)
+        sc = MoeScratch(tiled, 8)
+        outs.append(forward_moe(tiled, sc, x).clone())
+        assert sc.status() == 0
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1])
