@@ -45,6 +45,9 @@ QWEN_Q8_0 = LayerConfig("qwen35-moe-q8_0-zipf", 2048, 256, 512, 512, 8, Q8_0, Q8
 NEMOTRON_Q4_0 = LayerConfig("nemotron-h-moe-q4_0", 2688, 128, 1856, 3712, 6, Q4_0, Q4_0, act=abi.ACT_RELU2,
                             route_mode=abi.ROUTE_SIGMOID_NORM_SCALE, route_scale=2.5, shared_gate=False, seed=3)
 QWEN_Q4_0_ZIPF = LayerConfig("qwen35-moe-q4_0-zipf", 2048, 256, 512, 512, 8, Q4_0, Q4_0, zipf_bias=True, seed=4)
+# the production mix: IQ3_S routed experts, Q5_K shared expert (moe_ffn.rs:1597-1650); not one of the benchmark's five
+QWEN_IQ3S_Q5K = LayerConfig("qwen35-moe-iq3s-q4_0-shared-q5k", 2048, 256, 512, 512, 8, IQ3_S, Q4_0, seed=5,
+                            type_sh_gate_up=formats.TYPE_Q5_K, type_sh_down=formats.TYPE_Q5_K)
 CONFIGS = [QWEN_Q4_0, QWEN_IQ3S, QWEN_Q8_0, NEMOTRON_Q4_0, QWEN_Q4_0_ZIPF]
 
 
@@ -58,6 +61,9 @@ def scaled(cfg: LayerConfig, **kw) -> LayerConfig:
 def _quant_matrix_stack(qtype: int, n: int, rows: int, cols: int, gen: torch.Generator, device, chunk: int = 16) -> torch.Tensor:
     """n matrices [rows, cols] ~N(0, 0.02), quantized; returns u8 [n, rows*row_bytes]."""
     rb = formats.row_bytes(qtype, cols)
+    if qtype in (formats.TYPE_Q4_K, formats.TYPE_Q5_K, formats.TYPE_Q6_K):   # no quantizer for these: seeded valid blocks
+        seed = int(torch.randint(0, 2 ** 31 - 1, (1,), generator=gen, device=device).item())
+        return torch.from_numpy(formats.random_kquant_rows(qtype, n * rows, cols, seed=seed)).reshape(n, rows * rb).to(device)
     out = torch.empty(n, rows * rb, dtype=torch.uint8, device=device)
     for e0 in range(0, n, chunk):
         e1 = min(n, e0 + chunk)

@@ -22,8 +22,30 @@ inline size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
 inline bool type_ok(int t) { return t == CHIMERE_TYPE_Q4_0 || t == CHIMERE_TYPE_Q8_0 || t == CHIMERE_TYPE_IQ3_S; }
 inline int type_cols_multiple(int t) { return t == CHIMERE_TYPE_IQ3_S ? 256 : 32; }
 
+inline bool kquant_type(int t) { return t == CHIMERE_TYPE_Q4_K || t == CHIMERE_TYPE_Q5_K || t == CHIMERE_TYPE_Q6_K; }
+// A layer whose shared expert is kept in K-quant super-blocks (the production files: Q5_K, moe_ffn.rs:1597-1650).  Its routed
+// experts run as a layer without a shared expert; the shared expert follows as plain GEMVs on the raw blocks
+// (kshared_chain below), which is how the reference runs it (three GEMV calls, an activation, the sigmoid-gated add).
+inline bool kshared(const chimere_moe_layer* w) { return w && w->F_s > 0 && kquant_type(w->type_sh_up); }
+inline chimere_moe_layer routed_only(const chimere_moe_layer* w) {
+    chimere_moe_layer r = *w;
+    r.F_s = 0; r.sh_gate = nullptr; r.sh_up = nullptr; r.sh_down = nullptr;
+    r.type_sh_gate = r.type_sh_up = r.type_sh_down = 0;
+    return r;   // (keeps shexp_gate_w: the router still computes the gate logit)
+}
+
 int validate_layer(const chimere_moe_layer* w) {
     if (!w) return -1;
+    if (kshared(w)) {
+        const bool dual_k = w->act == CHIMERE_ACT_SWIGLU;
+        if (!kquant_type(w->type_sh_down) || (dual_k && !kquant_type(w->type_sh_gate))) return -3;
+        if (w->H % 256 || w->F_s % 256) return -2;
+        if (!w->sh_up || !w->sh_down || (dual_k && !w->sh_gate)) return -1;
+        // the shared expert's f32 rows and Q8_1 intermediates borrow the routed pairs' areas of the workspace
+        if (2 * (int64_t)w->F_s > (int64_t)w->top_k * w->H || (int64_t)w->F_s > (int64_t)w->top_k * w->F) return -2;
+        const chimere_moe_layer r = routed_only(w);
+        return validate_layer(&r);
+    }
     if (w->H <= 0 || w->E <= 0 || w->E > kMaxExperts || w->F <= 0 || w->F_s < 0) return -2;
     if (w->top_k <= 0 || w->top_k > kMaxTopK || w->top_k > w->E) return -2;
     if (w->H % 32 || w->F % 32 || w->F_s % 32) return -2;
@@ -60,6 +82,7 @@ int max_entries_for(const chimere_moe_layer* w, int T) {
 }
 
 Layout make_layout(const chimere_moe_layer* w, int T) {
+    if (kshared(w)) { const chimere_moe_layer r = routed_only(w); return make_layout(&r, T); }
     Layout L{};
     const int k = w->top_k, H = w->H, E = w->E;
     const int Fmax = w->F > w->F_s ? w->F : w->F_s;
@@ -144,13 +167,13 @@ int chimere_b200_moe_workspace_init(chimere_moe_workspace* ws, void* d_arena, si
     return cuda_rc(e);
 }
 
-static RouteParams route_params(const chimere_moe_layer* w, const float* d_x, int T, chimere_moe_workspace* ws) {
+static RouteParams route_params(const chimere_moe_layer* w, const float* d_x, int T, chimere_moe_workspace* ws, bool keep_gate_vector = false) {
     RouteParams p{};
     p.T = T; p.H = w->H; p.E = w->E; p.top_k = w->top_k; p.route_mode = w->route_mode;
     p.has_shared = w->F_s > 0;
     p.route_scale = w->route_scale;
     p.x = d_x; p.router_w = w->router_w; p.router_bias = w->router_bias;
-    p.shexp_gate_w = (w->F_s > 0) ? w->shexp_gate_w : nullptr;
+    p.shexp_gate_w = (w->F_s > 0 || keep_gate_vector) ? w->shexp_gate_w : nullptr;
     p.router_logits = ws->router_logits; p.sh_gate_logit = ws->sh_gate_logit;
     p.topk_idx = ws->topk_idx; p.topk_w = ws->topk_w; p.x_q8 = ws->x_q8;
     p.perm = ws->perm; p.offsets = ws->offsets; p.group_list = ws->group_list; p.counters = ws->counters;
@@ -165,9 +188,11 @@ static RouteParams route_params(const chimere_moe_layer* w, const float* d_x, in
     return p;
 }
 
-static int check_call(const chimere_moe_layer* w, const void* a, const void* b, int T, const chimere_moe_workspace* ws) {
+static int check_call(const chimere_moe_layer* w, const void* a, const void* b, int T, const chimere_moe_workspace* ws,
+                      bool allow_kquant_shared = false) {
     int rc = validate_layer(w);
     if (rc) return rc;
+    if (kshared(w) && !allow_kquant_shared) return -6;   // only the whole-layer entries take a K-quant shared expert
     if (!a || !b || !ws || !ws->counters) return -1;
     if (T <= 0 || T > ws->max_T) return -2;
     return 0;
@@ -180,6 +205,7 @@ int chimere_b200_moe_route(const chimere_moe_layer* w, const float* d_x, int T, 
     return cuda_rc(launch_route(route_params(w, d_x, T, ws), stream));
 }
 
+static int kshared_chain(const chimere_moe_layer* w, int T, float* d_y, chimere_moe_workspace* ws, cudaStream_t stream);
 static GemvParams gate_up_params(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, const Layout& L);
 static GemvParams down_params(const chimere_moe_layer* w, float* d_y, int T, chimere_moe_workspace* ws, const Layout& L);
 
@@ -405,6 +431,7 @@ static PackPlan pack_plan(const chimere_moe_layer* w) {
 
 size_t chimere_b200_moe_pack_bytes(const chimere_moe_layer* raw) {
     if (validate_layer(raw) != 0 || raw->layout != CHIMERE_LAYOUT_GGML) return 0;
+    if (kshared(raw)) { const chimere_moe_layer r = routed_only(raw); return pack_plan(&r).total; }
     return pack_plan(raw).total;
 }
 
@@ -413,6 +440,14 @@ int chimere_b200_moe_pack(const chimere_moe_layer* raw, void* d_arena, size_t by
     int rc = validate_layer(raw);
     if (rc) return rc;
     if (!d_arena || !packed) return -1;
+    if (kshared(raw)) {   // the routed experts are re-tiled; the K-quant shared matrices stay where and as they are
+        const chimere_moe_layer r = routed_only(raw);
+        rc = chimere_b200_moe_pack(&r, d_arena, bytes, packed, stream);
+        if (rc) return rc;
+        packed->F_s = raw->F_s; packed->sh_gate = raw->sh_gate; packed->sh_up = raw->sh_up; packed->sh_down = raw->sh_down;
+        packed->type_sh_gate = raw->type_sh_gate; packed->type_sh_up = raw->type_sh_up; packed->type_sh_down = raw->type_sh_down;
+        return 0;
+    }
     if (raw->layout != CHIMERE_LAYOUT_GGML) return -2;
     if ((uintptr_t)d_arena & 255) return -5;
     const PackPlan P = pack_plan(raw);
@@ -480,22 +515,26 @@ int chimere_b200_moe_down_combine(const chimere_moe_layer* w, float* d_y, int T,
 
 int chimere_b200_moe_forward(const chimere_moe_layer* w, const float* d_x, float* d_y, int T, chimere_moe_workspace* ws,
                              cudaStream_t stream) {
-    int rc = check_call(w, d_x, d_y, T, ws);
+    int rc = check_call(w, d_x, d_y, T, ws, true);
     if (rc) return rc;
-    const Layout L = make_layout(w, ws->max_T);
-    const int max_entries = max_entries_for(w, T);
-    cudaError_t e = launch_route(route_params(w, d_x, T, ws), stream);
+    const bool ks = kshared(w);
+    const chimere_moe_layer wr_ = ks ? routed_only(w) : *w;
+    const chimere_moe_layer* wr = &wr_;
+    const Layout L = make_layout(wr, ws->max_T);
+    const int max_entries = max_entries_for(wr, T);
+    cudaError_t e = launch_route(route_params(wr, d_x, T, ws, ks), stream);
     if (e != cudaSuccess) return cuda_rc(e);
-    e = run_gate_up(w, gate_up_params(w, T, ws, L), max_entries, stream);
+    e = run_gate_up(wr, gate_up_params(wr, T, ws, L), max_entries, stream);
     if (e != cudaSuccess) return cuda_rc(e);
-    e = run_down(w, down_params(w, d_y, T, ws, L), max_entries, stream);
-    return cuda_rc(e);
+    e = run_down(wr, down_params(wr, d_y, T, ws, L), max_entries, stream);
+    if (e != cudaSuccess || !ks) return cuda_rc(e);
+    return kshared_chain(w, T, d_y, ws, stream);
 }
 
 int chimere_b200_moe_forward_host(const chimere_moe_layer* w, const float* h_x, float* h_y, int T, float* d_x, float* d_y,
                                   chimere_moe_workspace* ws, cudaStream_t stream) {
     if (!h_x || !h_y) return -1;
-    int rc = check_call(w, d_x, d_y, T, ws);
+    int rc = check_call(w, d_x, d_y, T, ws, true);
     if (rc) return rc;
     const size_t bytes = (size_t)T * w->H * sizeof(float);
     cudaError_t e = cudaMemcpyAsync(d_x, h_x, bytes, cudaMemcpyHostToDevice, stream);
@@ -612,7 +651,9 @@ PrefillArena prefill_arena(const chimere_moe_layer* w, int T) {
 }  // namespace
 
 size_t chimere_b200_moe_pack_prefill_bytes(const chimere_moe_layer* raw) {
-    if (validate_layer(raw) != 0 || raw->layout != CHIMERE_LAYOUT_GGML || !prefill_dims_ok(raw)) return 0;
+    if (validate_layer(raw) != 0) return 0;
+    if (kshared(raw)) { const chimere_moe_layer r = routed_only(raw); return chimere_b200_moe_pack_prefill_bytes(&r); }
+    if (raw->layout != CHIMERE_LAYOUT_GGML || !prefill_dims_ok(raw)) return 0;
     return prefill_plan(raw).total;
 }
 
@@ -621,6 +662,7 @@ int chimere_b200_moe_pack_prefill(const chimere_moe_layer* raw, void* d_arena, s
     int rc = validate_layer(raw);
     if (rc) return rc;
     if (!d_arena || !out) return -1;
+    if (kshared(raw)) { const chimere_moe_layer r = routed_only(raw); return chimere_b200_moe_pack_prefill(&r, d_arena, bytes, out, stream); }
     if (raw->layout != CHIMERE_LAYOUT_GGML || !prefill_dims_ok(raw)) return -2;
     if ((uintptr_t)d_arena & 255) return -5;
     const PrefillPlan P = prefill_plan(raw);
@@ -646,8 +688,28 @@ int chimere_b200_moe_pack_prefill(const chimere_moe_layer* raw, void* d_arena, s
 }
 
 size_t chimere_b200_moe_prefill_bytes(const chimere_moe_layer* w, int max_T) {
-    if (validate_layer(w) != 0 || max_T <= 0 || !prefill_dims_ok(w)) return 0;
+    if (validate_layer(w) != 0 || max_T <= 0) return 0;
+    if (kshared(w)) { const chimere_moe_layer r = routed_only(w); return chimere_b200_moe_prefill_bytes(&r, max_T); }
+    if (!prefill_dims_ok(w)) return 0;
     return prefill_arena(w, max_T).total;
+}
+
+// The K-quant shared expert of `w` for T tokens whose Q8_1 rows (ws->x_q8) and gate logits (ws->sh_gate_logit) the router
+// left behind, added to d_y: up (and gate) GEMVs, activation + Q8_1, down GEMV with the sigmoid-gated add.  The f32 rows
+// borrow ws->pair_out and the intermediates ws->inter_q8: the routed part of the call is done with both by then.
+static int kshared_chain(const chimere_moe_layer* w, int T, float* d_y, chimere_moe_workspace* ws, cudaStream_t stream) {
+    const bool dual = w->act == CHIMERE_ACT_SWIGLU;
+    const int64_t x_stride = (int64_t)(w->H / 32) * kQ81Bytes, i_stride = (int64_t)(w->F_s / 32) * kQ81Bytes;
+    float* up = ws->pair_out;
+    float* gate = dual ? ws->pair_out + (size_t)T * w->F_s : nullptr;
+    cudaError_t e = launch_mmvq_kquant_batched(w->type_sh_up, w->sh_up, ws->x_q8, x_stride, up, w->F_s, T, w->H, w->F_s, 0, nullptr, stream);
+    if (e == cudaSuccess && dual)
+        e = launch_mmvq_kquant_batched(w->type_sh_gate, w->sh_gate, ws->x_q8, x_stride, gate, w->F_s, T, w->H, w->F_s, 0, nullptr, stream);
+    if (e == cudaSuccess) e = launch_act_q8_1(gate, up, w->F_s, ws->inter_q8, i_stride, T, w->F_s, stream);
+    if (e == cudaSuccess)
+        e = launch_mmvq_kquant_batched(w->type_sh_down, w->sh_down, ws->inter_q8, i_stride, d_y, w->H, T, w->F_s, w->H, w->shexp_gate_w ? 2 : 1,
+                                       w->shexp_gate_w ? ws->sh_gate_logit : nullptr, stream);
+    return cuda_rc(e);
 }
 
 // The expert products of a prefill-size batch whose routing (ws->offsets, ws->perm) and Q8_1 planes (ws->x_q, ws->x_d) are
@@ -706,20 +768,25 @@ static int prefill_experts(const chimere_moe_layer* w, const chimere_moe_prefill
 
 int chimere_b200_moe_forward_prefill(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, const float* d_x, float* d_y,
                                      int T, chimere_moe_workspace* ws, cudaStream_t stream) {
-    int rc = check_call(w, d_x, d_y, T, ws);
+    int rc = check_call(w, d_x, d_y, T, ws, true);
     if (rc) return rc;
     if (!pw || !ws->prefill_arena) return -1;
-    if (w->layout != CHIMERE_LAYOUT_TILED32 || !prefill_dims_ok(w)) return -2;
-    RouteParams rp = route_params(w, d_x, T, ws);
+    const bool ks = kshared(w);   // (a K-quant shared expert runs as GEMVs per token behind the routed part, at any batch size)
+    const chimere_moe_layer wr_ = ks ? routed_only(w) : *w;
+    const chimere_moe_layer* wr = &wr_;
+    if (wr->layout != CHIMERE_LAYOUT_TILED32 || !prefill_dims_ok(wr)) return -2;
+    RouteParams rp = route_params(wr, d_x, T, ws, ks);
     rp.list_mode = 2;   // no work entries from the router: the tile builder writes the list of the small experts
     cudaError_t e = launch_route(rp, stream);
     if (e != cudaSuccess) return cuda_rc(e);
-    rc = prefill_experts(w, pw, T, ws, stream);
+    rc = prefill_experts(wr, pw, T, ws, stream);
     if (rc) return rc;
     // routing-weighted sum of every token's pair rows in slot order + the sigmoid-gated shared expert
-    const float* shared_rows = w->F_s > 0 ? ws->pair_out + (size_t)T * w->top_k * w->H : nullptr;
-    const float* logit = (w->F_s > 0 && w->shexp_gate_w) ? ws->sh_gate_logit : nullptr;
-    return cuda_rc(launch_ep_finish(ws->pair_out, nullptr, ws->topk_w, shared_rows, logit, d_y, T, w->H, w->top_k, stream));
+    const float* shared_rows = wr->F_s > 0 ? ws->pair_out + (size_t)T * wr->top_k * wr->H : nullptr;
+    const float* logit = (wr->F_s > 0 && wr->shexp_gate_w) ? ws->sh_gate_logit : nullptr;
+    e = launch_ep_finish(ws->pair_out, nullptr, ws->topk_w, shared_rows, logit, d_y, T, wr->H, wr->top_k, stream);
+    if (e != cudaSuccess || !ks) return cuda_rc(e);
+    return kshared_chain(w, T, d_y, ws, stream);
 }
 
 // Expert-parallel owner rank, prefill-size: as chimere_b200_moe_experts, with the large local experts on the grouped GEMM.
@@ -740,7 +807,7 @@ int chimere_b200_moe_experts_prefill(const chimere_moe_layer* w_local, const chi
 int chimere_b200_moe_forward_residual_norm(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, const float* d_hidden,
                                            float* d_residual, const float* d_norm_weight, float eps, float* d_y, int T,
                                            chimere_moe_workspace* ws, cudaStream_t stream) {
-    int rc = check_call(w, d_hidden, d_y, T, ws);
+    int rc = check_call(w, d_hidden, d_y, T, ws, true);
     if (rc) return rc;
     if (!d_residual || !d_norm_weight || !ws->pair_out) return -1;
     // the normalised rows live in the first T rows of the per-pair output area until the router and the Q8_1 step have

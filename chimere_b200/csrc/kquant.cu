@@ -75,41 +75,87 @@ __device__ __forceinline__ float sub_block(const uint8_t* blk, int j, const uint
     }
 }
 
+// grid = (row groups, input rows).  mode 0: y = v; 1: y += v; 2: y += sigmoid(logit[t]) * v (the sigmoid-gated shared
+// expert added to the routed sum, scratch_pool.rs:266-277).
 template <int TYPE>
 __global__ void __launch_bounds__(32 * kRowsPerCta) kquant_mmvq_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ xq8,
-                                                                      float* __restrict__ y, int ncols, int nrows) {
-    const int lane = threadIdx.x & 31, row = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
+                                                                      int64_t x_stride, float* __restrict__ y, int64_t y_stride, int ncols,
+                                                                      int nrows, int mode, const float* __restrict__ logit) {
+    const int lane = threadIdx.x & 31, row = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5), t = blockIdx.y;
     if (row >= nrows) return;
     const int nsub = ncols >> 5;
     const uint8_t* rowp = w + (size_t)row * (size_t)(ncols >> 8) * KBlock<TYPE>::kBytes;
+    const uint8_t* xr = xq8 + (size_t)t * x_stride;
     float acc = 0.0f;
     for (int sb = lane; sb < nsub; sb += 32)
-        acc += sub_block<TYPE>(rowp + (size_t)(sb >> 3) * KBlock<TYPE>::kBytes, sb & 7, xq8 + (size_t)sb * kQ81Bytes);
+        acc += sub_block<TYPE>(rowp + (size_t)(sb >> 3) * KBlock<TYPE>::kBytes, sb & 7, xr + (size_t)sb * kQ81Bytes);
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-    if (lane == 0) y[row] = acc;
+    if (lane == 0) {
+        float* out = y + (size_t)t * y_stride + row;
+        if (mode == 0) *out = acc;
+        else if (mode == 1) *out = acc + *out;
+        else *out = fmaf(acc, sigmoid_ref(logit[t]), *out);
+    }
+}
+
+// One warp per (row t, block b of 32): v = silu(g) * u (or relu(u)^2 without a gate row) -> one Q8_1 block, as the gate/up
+// kernels write their intermediates (d = amax / 127 in f16, s = the sum of the 32 values).
+__global__ void __launch_bounds__(256) act_q8_1_kernel(const float* __restrict__ g, const float* __restrict__ u, int64_t in_stride,
+                                                       uint8_t* __restrict__ out, int64_t out_stride, int T, int F) {
+    const int lane = threadIdx.x & 31, nb = F >> 5;
+    const int64_t wid = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (wid >= (int64_t)T * nb) return;
+    const int t = (int)(wid / nb), b = (int)(wid - (int64_t)t * nb);
+    const float uu = u[(size_t)t * in_stride + b * 32 + lane];
+    float v;
+    if (g) v = silu_mul_ref(g[(size_t)t * in_stride + b * 32 + lane], uu);
+    else { const float r = fmaxf(uu, 0.0f); v = r * r; }
+    float amax = fabsf(v), sum = v;
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+        sum += __shfl_xor_sync(0xffffffffu, sum, s);
+    }
+    const float d = amax / 127.0f;
+    uint8_t* blk = out + (size_t)t * out_stride + (size_t)b * kQ81Bytes;
+    reinterpret_cast<int8_t*>(blk)[4 + lane] = (amax == 0.0f) ? (int8_t)0 : (int8_t)roundf(v / d);
+    if (lane == 0) *reinterpret_cast<__half2*>(blk) = __halves2half2(__float2half(d), __float2half(sum));
 }
 
 }  // namespace
 
-cudaError_t launch_mmvq_kquant(int wtype, const void* w, const void* xq8, float* y, int ncols, int nrows, cudaStream_t stream) {
-    if (nrows <= 0) return cudaSuccess;
-    if (ncols <= 0 || (ncols & 255) || ((uintptr_t)xq8 & 3)) return cudaErrorInvalidValue;
-    const dim3 grid((nrows + kRowsPerCta - 1) / kRowsPerCta);
+cudaError_t launch_mmvq_kquant_batched(int wtype, const void* w, const void* xq8, int64_t x_stride, float* y, int64_t y_stride, int n_inputs,
+                                       int ncols, int nrows, int mode, const float* logit, cudaStream_t stream) {
+    if (nrows <= 0 || n_inputs <= 0) return cudaSuccess;
+    if (ncols <= 0 || (ncols & 255) || ((uintptr_t)xq8 & 3) || (x_stride & 3) || n_inputs > 65535 || (mode == 2 && !logit)) return cudaErrorInvalidValue;
+    const dim3 grid((nrows + kRowsPerCta - 1) / kRowsPerCta, n_inputs);
     const uint8_t* wp = (const uint8_t*)w;
     const uint8_t* xp = (const uint8_t*)xq8;
     switch (wtype) {
         case CHIMERE_TYPE_Q4_K:
             if ((uintptr_t)w & 3) return cudaErrorInvalidValue;
-            kquant_mmvq_kernel<CHIMERE_TYPE_Q4_K><<<grid, 32 * kRowsPerCta, 0, stream>>>(wp, xp, y, ncols, nrows); break;
+            kquant_mmvq_kernel<CHIMERE_TYPE_Q4_K><<<grid, 32 * kRowsPerCta, 0, stream>>>(wp, xp, x_stride, y, y_stride, ncols, nrows, mode, logit); break;
         case CHIMERE_TYPE_Q5_K:
             if ((uintptr_t)w & 3) return cudaErrorInvalidValue;
-            kquant_mmvq_kernel<CHIMERE_TYPE_Q5_K><<<grid, 32 * kRowsPerCta, 0, stream>>>(wp, xp, y, ncols, nrows); break;
+            kquant_mmvq_kernel<CHIMERE_TYPE_Q5_K><<<grid, 32 * kRowsPerCta, 0, stream>>>(wp, xp, x_stride, y, y_stride, ncols, nrows, mode, logit); break;
         case CHIMERE_TYPE_Q6_K:
             if ((uintptr_t)w & 1) return cudaErrorInvalidValue;
-            kquant_mmvq_kernel<CHIMERE_TYPE_Q6_K><<<grid, 32 * kRowsPerCta, 0, stream>>>(wp, xp, y, ncols, nrows); break;
+            kquant_mmvq_kernel<CHIMERE_TYPE_Q6_K><<<grid, 32 * kRowsPerCta, 0, stream>>>(wp, xp, x_stride, y, y_stride, ncols, nrows, mode, logit); break;
         default: return cudaErrorInvalidValue;
     }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_mmvq_kquant(int wtype, const void* w, const void* xq8, float* y, int ncols, int nrows, cudaStream_t stream) {
+    return launch_mmvq_kquant_batched(wtype, w, xq8, 0, y, 0, 1, ncols, nrows, 0, nullptr, stream);
+}
+
+cudaError_t launch_act_q8_1(const float* g, const float* u, int64_t in_stride, void* out, int64_t out_stride, int T, int F, cudaStream_t stream) {
+    if (T <= 0 || F <= 0) return cudaSuccess;
+    if (F & 31) return cudaErrorInvalidValue;
+    const int64_t warps = (int64_t)T * (F >> 5);
+    act_q8_1_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(g, u, in_stride, (uint8_t*)out, out_stride, T, F);
     return cudaGetLastError();
 }
 

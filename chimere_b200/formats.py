@@ -33,8 +33,8 @@ Q8_1_BYTES = 36
 
 
 def random_kquant_rows(qtype: int, rows: int, cols: int, seed: int = 0, scale: float = 0.02) -> np.ndarray:
-    """Seeded rows of valid K-quant super-blocks with every bit field drawn at random (quants, six-bit scales and mins or
-    int8 scales, high bits) and f16 super-block scales sized so that the weights come out near N(0, scale).  Stands in
+    """Seeded rows of valid K-quant super-blocks with the quants, high bits and scales drawn at random and f16 super-block
+    scales sized so that the weights come out zero-mean with a standard deviation near `scale`.  Stands in
     for a quantizer: the GEMV entries decode blocks, they never make them.  Returns u8 [rows, row_bytes]."""
     assert qtype in (TYPE_Q4_K, TYPE_Q5_K, TYPE_Q6_K) and cols % 256 == 0
     rng = np.random.default_rng(seed)
@@ -43,10 +43,18 @@ def random_kquant_rows(qtype: int, rows: int, cols: int, seed: int = 0, scale: f
     if qtype == TYPE_Q6_K:       # weight = d * sc * q, sc int8, q in -32..31
         d = (scale / (64.0 * 18.0)) * rng.uniform(0.5, 1.5, nb)
         blk[:, 208:210] = d.astype(np.float16).view(np.uint8).reshape(nb, 2)
-    else:                        # weight = d * sc * q - dmin * m, sc and m in 0..63, q in 0..15 or 0..31
+    else:
+        # weight = d * sc_j * q - dmin * m_j with six-bit sc_j, m_j and q in 0..15 (Q4_K) or 0..31 (Q5_K).  m_j = sc_j and
+        # dmin = d * qmax / 2 centre every sub-block on zero, as a quantizer's blocks of zero-mean weights are.
         qmax = 15.0 if qtype == TYPE_Q4_K else 31.0
-        d = (scale / (32.0 * qmax * 0.3)) * rng.uniform(0.5, 1.5, nb)
-        dmin = d * qmax * 0.5 * rng.uniform(0.8, 1.2, nb)
+        sc = rng.integers(1, 64, size=(nb, 8), dtype=np.uint8)
+        packed = np.empty((nb, 12), np.uint8)
+        packed[:, 0:4] = sc[:, 0:4] | ((sc[:, 4:8] >> 4) << 6)          # scales of sub-blocks 0..3, top bits of 4..7
+        packed[:, 4:8] = sc[:, 0:4] | ((sc[:, 4:8] >> 4) << 6)          # mins: the same values
+        packed[:, 8:12] = (sc[:, 4:8] & 0x0F) | ((sc[:, 4:8] & 0x0F) << 4)
+        blk[:, 4:16] = packed
+        d = (scale / (32.0 * qmax * 0.29)) * rng.uniform(0.5, 1.5, nb)
+        dmin = d * qmax * 0.5 * rng.uniform(0.9, 1.1, nb)
         blk[:, 0:2] = d.astype(np.float16).view(np.uint8).reshape(nb, 2)
         blk[:, 2:4] = dmin.astype(np.float16).view(np.uint8).reshape(nb, 2)
     return blk.reshape(rows, cols // 256 * bb)

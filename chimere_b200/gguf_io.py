@@ -16,6 +16,7 @@ from . import abi, formats
 from .layer import MoeWeightsRaw
 
 LAYER_TYPES = (formats.TYPE_Q4_0, formats.TYPE_Q8_0, formats.TYPE_IQ3_S)
+KQUANT_TYPES = (formats.TYPE_Q4_K, formats.TYPE_Q5_K, formats.TYPE_Q6_K)
 
 
 class GgufFile:
@@ -88,9 +89,9 @@ def load_moe_layer(g: GgufFile, layer: int, device="cuda", top_k: Optional[int] 
     """Layer `layer`'s MoE tensors as raw ggml bytes on `device`.
 
     top_k defaults to the file's `<arch>.expert_used_count`.  Experts without a gate tensor are taken as ungated
-    (squared ReLU) unless `act` says otherwise.  The routed experts must be Q4_0, Q8_0 or IQ3_S; a shared expert in
-    another type (the production files keep it in Q5_K) is left out when with_shared is False and refused otherwise:
-    it then runs through the plain GEMV entries (chimere_mmvq_q5k and friends) beside the layer call.
+    (squared ReLU) unless `act` says otherwise.  The routed experts must be Q4_0, Q8_0 or IQ3_S; the shared expert
+    either one of those or K-quant throughout (the production files keep it in Q5_K: the whole-layer entries then run it
+    as plain GEMVs on the raw blocks behind the routed part).  with_shared=False leaves it out.
     """
     info = g.moe_layer_info(layer)
     if top_k is None:
@@ -104,10 +105,10 @@ def load_moe_layer(g: GgufFile, layer: int, device="cuda", top_k: Optional[int] 
     kw = {}
     shared = bool(info.has_shared) and with_shared
     if shared:
-        for t in (info.sh_up, info.sh_down) + ((info.sh_gate,) if info.has_shared_gate else ()):
-            if t.ggml_type not in LAYER_TYPES:
-                raise ValueError(f"shared expert of ggml type {t.ggml_type}: load with with_shared=False and run it through the "
-                                 "plain GEMV entries")
+        sh = (info.sh_up, info.sh_down) + ((info.sh_gate,) if info.has_shared_gate else ())
+        if not (all(t.ggml_type in LAYER_TYPES for t in sh) or all(t.ggml_type in KQUANT_TYPES for t in sh)):
+            raise ValueError(f"shared expert of ggml types {[t.ggml_type for t in sh]}: neither all Q4_0/Q8_0/IQ3_S nor all K-quant; "
+                             "load with with_shared=False")
         kw["shexp_up_raw"] = g.read(info.sh_up, device)
         kw["shexp_down_raw"] = g.read(info.sh_down, device)
         kw["type_sh_up"], kw["type_sh_down"] = info.sh_up.ggml_type, info.sh_down.ggml_type

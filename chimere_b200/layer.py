@@ -96,6 +96,11 @@ class MoeWeightsRaw:
         return self._struct
 
 
+def formats_kquant_types():
+    from . import formats
+    return (formats.TYPE_Q4_K, formats.TYPE_Q5_K, formats.TYPE_Q6_K)
+
+
 class MoeWeightsTiled:
     """The layer after the one-time load-side rewrite into the library's tiled32 layout
     (chimere_b200_moe_pack).  Router tensors are shared with the raw object; the expert matrices live
@@ -117,6 +122,8 @@ class MoeWeightsTiled:
         abi.check(lib.chimere_b200_moe_pack(C.byref(rs), self.arena.data_ptr(), nbytes, C.byref(self._struct), stream),
                   "chimere_b200_moe_pack")
         self._keep = [raw.router_weight, raw.router_bias, raw.shexp_gate_proj]
+        if raw.F_s > 0 and raw.type_sh_up in formats_kquant_types():   # a K-quant shared expert stays in its raw blocks
+            self._keep += [raw.shexp_gate_raw, raw.shexp_up_raw, raw.shexp_down_raw]
         if not keep_raw:
             torch.cuda.current_stream(self.arena.device).synchronize()
             self.raw = None

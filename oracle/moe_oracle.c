@@ -294,7 +294,10 @@ void orc_block_sumi(int type, const void* W, const void* xq8, int32_t* sumi, int
  * gemv_q8_0_q8, src/kernels/gemv_q8_0.rs:253-254.  Blocks are added in ascending order
  * (the reference's order is a property of its launch shape; fp32 results are compared with a
  * tolerance). */
+static float kquant_row_dot(int type, const uint8_t* row, const uint8_t* xq8, int ncols);
+static int is_kquant(int type);
 static inline float row_dot(int type, const uint8_t* row, const uint8_t* xq8, int nb) {
+    if (is_kquant(type)) return kquant_row_dot(type, row, xq8, nb * 32);   /* a K-quant shared expert (moe_ffn.rs:1597-1650) */
     float acc = 0.0f;
     for (int b = 0; b < nb; b++) {
         const uint8_t* xb = xq8 + (size_t)b * Q8_1_BYTES;
@@ -381,8 +384,7 @@ void orc_gemv(int type, const void* W, const void* xq8, float* y, int ncols, int
     int nb = ncols / 32; int64_t rb = orc_row_bytes(type, ncols);
     #pragma omp parallel for schedule(static)
     for (int r = 0; r < nrows; r++)
-        y[r] = is_kquant(type) ? kquant_row_dot(type, (const uint8_t*)W + (size_t)r * rb, (const uint8_t*)xq8, ncols)
-                               : row_dot(type, (const uint8_t*)W + (size_t)r * rb, (const uint8_t*)xq8, nb);
+        y[r] = row_dot(type, (const uint8_t*)W + (size_t)r * rb, (const uint8_t*)xq8, nb);
 }
 
 /* Dequantise n elements (n multiple of the block size) -- gguf_loader.rs:752-772 (Q4_0),

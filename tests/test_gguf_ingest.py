@@ -83,7 +83,7 @@ def test_round_trip_through_a_gguf_file(tmp_path, cfg):
             g.moe_layer_info(1)          # no such layer
 
 
-def test_kquant_shared_expert_is_refused_by_the_layer_loader_and_readable_raw(tmp_path):
+def test_kquant_shared_expert_loads_as_raw_blocks(tmp_path):
     cfg = configs.scaled(configs.QWEN_Q4_0, E=4, F=256, F_s=256, H=256)
     L = configs.make_layer(cfg, seed=5)
     for name, rows, cols in (("shexp_gate_raw", cfg.F_s, cfg.H), ("shexp_up_raw", cfg.F_s, cfg.H), ("shexp_down_raw", cfg.H, cfg.F_s)):
@@ -94,8 +94,8 @@ def test_kquant_shared_expert_is_refused_by_the_layer_loader_and_readable_raw(tm
     with GgufFile(path) as g:
         info = g.moe_layer_info(0)
         assert info.sh_up.ggml_type == formats.TYPE_Q5_K and info.sh_up.nbytes == cfg.F_s * formats.row_bytes(formats.TYPE_Q5_K, cfg.H)
-        with pytest.raises(ValueError):
-            load_moe_layer(g, 0, device="cpu")
+        full = load_moe_layer(g, 0, device="cpu")
+        assert full.F_s == cfg.F_s and full.type_sh_up == formats.TYPE_Q5_K and torch.equal(full.shexp_up_raw, L.shexp_up_raw)
         routed = load_moe_layer(g, 0, device="cpu", with_shared=False)
         assert routed.F_s == 0 and torch.equal(routed.up_exps_raw.reshape(-1), L.up_exps_raw.reshape(-1))
         assert torch.equal(g.read(info.sh_down), L.shexp_down_raw)

@@ -459,3 +459,30 @@ def test_layer_loaded_from_a_gguf_file_gives_the_same_output(tmp_path):
         assert sc.status() == 0
     torch.cuda.synchronize()
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("sh_types", [(formats.TYPE_Q5_K, formats.TYPE_Q5_K), (formats.TYPE_Q4_K, formats.TYPE_Q6_K)])
+@pytest.mark.parametrize("T,entry", [(1, "decode"), (8, "decode"), (40, "decode"), (96, "prefill")])
+def test_layer_with_kquant_shared_expert(sh_types, T, entry):
+    """The production mix: IQ3_S / Q4_0 routed experts with the shared expert in K-quant super-blocks (moe_ffn.rs:1597-1730).
+    The whole-layer entries run the routed part as usual and the shared expert as GEMVs on the raw blocks."""
+    from chimere_b200.layer import MoeWeightsPrefill, forward_moe_prefill
+    cfg = configs.scaled(configs.QWEN_IQ3S, E=32, F=256, F_s=512, H=1024, type_sh_gate_up=sh_types[0], type_sh_down=sh_types[1], seed=31)
+    raw = configs.make_layer(cfg, device="cuda")
+    wh = raw.to("cpu")
+    tiled = MoeWeightsTiled(raw)
+    x = configs.make_input(cfg, T, device="cuda")
+    sc = MoeScratch(tiled, T)
+    y = forward_moe_prefill(tiled, MoeWeightsPrefill(raw), sc, x) if entry == "prefill" else forward_moe(tiled, sc, x)
+    torch.cuda.synchronize()
+    assert sc.status() == 0
+    idx = sc.topk_indices(T).cpu().numpy()
+    o = oracle_on_gpu_routing(wh, x.cpu().numpy(), idx)
+    assert np.array_equal(sc.x_q8(T).cpu().numpy(), o["x_q8"])
+    np.testing.assert_allclose(sc.sh_gate_logit(T).cpu().numpy(), o["sh_logit"], rtol=1e-5, atol=1e-6)
+    check_rows(y.cpu().numpy(), o["y"])
+    # the shared expert must have arrived: the same layer without it differs
+    routed_only = configs.make_layer(configs.scaled(cfg, F_s=0), device="cuda")
+    t2 = MoeWeightsTiled(routed_only)
+    y2 = forward_moe(t2, MoeScratch(t2, T), x)
+    assert (y - y2).abs().max() > 1e-3 * y.abs().max()
