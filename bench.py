@@ -235,7 +235,8 @@ def measure_secondary(lib, dev, hbm_peak, i8_peak_tops, prefill_tokens):
     """The configurations beside the headline one, each on one seeded layer, one layer call per timed sample with the L2
     flushed before it: the prefill configuration (all experts Q8_0, Zipf-skewed routing) at the given batch sizes on the
     tensor-core path (and, for comparison, everything on the GEMV kernels), the Nemotron-H-style layer at T = 1 and 256,
-    and the CPU-runnable Q4_0 layer at T = 16.  Every entry carries its algorithmic bytes (with the measured number of
+    the CPU-runnable Q4_0 layer at T = 16, and the production mix (IQ3_S / Q4_0 routed experts, Q5_K shared expert) at
+    T = 1 and 8.  Every entry carries its algorithmic bytes (with the measured number of
     distinct experts), its int8 operations and frac = max(bytes / HBM peak, ops / int8 peak) / time."""
     import torch
     from chimere_b200 import configs
@@ -246,6 +247,7 @@ def measure_secondary(lib, dev, hbm_peak, i8_peak_tops, prefill_tokens):
         plan.append((configs.QWEN_Q8_0, [(T, ("gemm", "gemv")) for T in prefill_tokens]))
     plan.append((configs.NEMOTRON_Q4_0, [(1, ("gemv",)), (256, ("gemm", "gemv"))]))
     plan.append((configs.QWEN_Q4_0, [(16, ("gemv", "gemm"))]))
+    plan.append((configs.QWEN_IQ3S_Q5K, [(1, ("gemv",)), (8, ("gemv",))]))   # the production mix: shared expert in Q5_K super-blocks
     out = []
     for cfg, cases in plan:
         raw = configs.make_layer(cfg, device=dev)

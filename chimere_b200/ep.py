@@ -12,6 +12,7 @@ tests) carries the exchanges; all arithmetic is in the CUDA library.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -185,7 +186,9 @@ class ExpertParallelMoE:
                          flags_in=self._peer.bases[self.rank] + recv_bytes + back_bytes, flags_back=self._peer.bases[self.rank] + recv_bytes + back_bytes + 256,
                          peer_recv=ptrs(0), peer_back=ptrs(recv_bytes), peer_flags_in=ptrs(recv_bytes + back_bytes),
                          peer_flags_back=ptrs(recv_bytes + back_bytes + 256),
-                         ctr=torch.zeros(3 * 64, dtype=torch.int32, device=dev))
+                         ctr=torch.zeros(3 * 64, dtype=torch.int32, device=dev),
+                         side=torch.cuda.Stream(device=dev), fork=torch.cuda.Event(), join=torch.cuda.Event())
+        self.overlap_shared = os.environ.get("CHIMERE_EP_SERIAL_SHARED", "") == "" and self.home.F_s > 0
 
     def forward_peer(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """The layer with both exchanges done by peer stores and flags instead of collectives: no NCCL call, no host
@@ -197,15 +200,25 @@ class ExpertParallelMoE:
         st = torch.cuda.current_stream(x.device).cuda_stream
         ctr = pp["ctr"].data_ptr()
         abi.check(lib.chimere_b200_moe_route_home(C.byref(self.home), x.data_ptr(), T, C.byref(self.ws_home.ws), st), "route_home")
+        # The shared expert needs nothing from other ranks and nothing the exchange writes: it runs on a second stream beside
+        # the pack -> wait -> experts -> return chain (the fork and the join are captured with the rest in a CUDA graph).
+        main = torch.cuda.current_stream(x.device)
+        if self.overlap_shared:
+            pp["fork"].record(main)
+            pp["side"].wait_event(pp["fork"])
+            abi.check(lib.chimere_b200_moe_shared_expert(C.byref(self.home), T, C.byref(self.ws_home.ws), pp["side"].cuda_stream), "shared_expert")
+            pp["join"].record(pp["side"])
         abi.check(lib.chimere_b200_moe_ep_pack_p2p(C.byref(self.home), T, C.byref(self.ws_home.ws), pp["peer_recv"].data_ptr(),
                                                    pp["peer_flags_in"].data_ptr(), ctr, self.rank, self.E_loc, G, pp["cap"], pp["rb"], st), "ep_pack_p2p")
-        # the shared expert needs nothing from other ranks: it runs while the rows travel
-        abi.check(lib.chimere_b200_moe_shared_expert(C.byref(self.home), T, C.byref(self.ws_home.ws), st), "shared_expert")
+        if not self.overlap_shared:
+            abi.check(lib.chimere_b200_moe_shared_expert(C.byref(self.home), T, C.byref(self.ws_home.ws), st), "shared_expert")
         n = G * pp["cap"]
         abi.check(lib.chimere_b200_moe_experts_packed_p2p(C.byref(self.owner), n, pp["recv"], pp["rb"], pp["flags_in"], G, pp["cap"],
                                                           C.byref(self.ws_owner.ws), st), "experts")
         abi.check(lib.chimere_b200_moe_ep_return_p2p(C.byref(self.owner), C.byref(self.ws_owner.ws), pp["recv"], pp["rb"], pp["peer_back"].data_ptr(),
                                                      pp["peer_flags_back"].data_ptr(), ctr + 256, self.rank, G, T, pp["cap"], st), "ep_return_p2p")
+        if self.overlap_shared:
+            main.wait_event(pp["join"])
         abi.check(lib.chimere_b200_moe_ep_finish_p2p(C.byref(self.home), pp["back"], pp["flags_back"], G, T, C.byref(self.ws_home.ws), out.data_ptr(),
                                                      ctr + 512, st), "ep_finish_p2p")
         self.last_recv_rows = n
