@@ -702,13 +702,17 @@ static int kshared_chain(const chimere_moe_layer* w, int T, float* d_y, chimere_
     const int64_t x_stride = (int64_t)(w->H / 32) * kQ81Bytes, i_stride = (int64_t)(w->F_s / 32) * kQ81Bytes;
     float* up = ws->pair_out;
     float* gate = dual ? ws->pair_out + (size_t)T * w->F_s : nullptr;
-    cudaError_t e = launch_mmvq_kquant_batched(w->type_sh_up, w->sh_up, ws->x_q8, x_stride, up, w->F_s, T, w->H, w->F_s, 0, nullptr, stream);
-    if (e == cudaSuccess && dual)
-        e = launch_mmvq_kquant_batched(w->type_sh_gate, w->sh_gate, ws->x_q8, x_stride, gate, w->F_s, T, w->H, w->F_s, 0, nullptr, stream);
+    // gate and up share a launch when they have the same type; the three (or four) kernels are chained programmatically
+    const bool one = dual && w->type_sh_gate == w->type_sh_up;
+    cudaError_t e = launch_mmvq_kquant_batched(w->type_sh_up, w->sh_up, one ? w->sh_gate : nullptr, ws->x_q8, x_stride, up, one ? gate : nullptr,
+                                               w->F_s, T, w->H, w->F_s, 0, nullptr, true, stream);
+    if (e == cudaSuccess && dual && !one)
+        e = launch_mmvq_kquant_batched(w->type_sh_gate, w->sh_gate, nullptr, ws->x_q8, x_stride, gate, nullptr, w->F_s, T, w->H, w->F_s, 0, nullptr,
+                                       true, stream);
     if (e == cudaSuccess) e = launch_act_q8_1(gate, up, w->F_s, ws->inter_q8, i_stride, T, w->F_s, stream);
     if (e == cudaSuccess)
-        e = launch_mmvq_kquant_batched(w->type_sh_down, w->sh_down, ws->inter_q8, i_stride, d_y, w->H, T, w->F_s, w->H, w->shexp_gate_w ? 2 : 1,
-                                       w->shexp_gate_w ? ws->sh_gate_logit : nullptr, stream);
+        e = launch_mmvq_kquant_batched(w->type_sh_down, w->sh_down, nullptr, ws->inter_q8, i_stride, d_y, nullptr, w->H, T, w->F_s, w->H,
+                                       w->shexp_gate_w ? 2 : 1, w->shexp_gate_w ? ws->sh_gate_logit : nullptr, true, stream);
     return cuda_rc(e);
 }
 

@@ -106,9 +106,11 @@ cudaError_t launch_mmvq(int wtype, const void* w, const void* xq8, float* y, con
                         int64_t expert_stride, int64_t input_stride, int nslots, cudaStream_t stream);
 // K-quant rows (CHIMERE_TYPE_Q4_K / Q5_K / Q6_K) against one Q8_1 row: y[nrows] = W . x_q8
 cudaError_t launch_mmvq_kquant(int wtype, const void* w, const void* xq8, float* y, int ncols, int nrows, cudaStream_t stream);
-// ... `n_inputs` Q8_1 rows x_stride bytes apart, outputs y_stride floats apart; mode 0 store, 1 add, 2 add sigmoid(logit[t]) * v
-cudaError_t launch_mmvq_kquant_batched(int wtype, const void* w, const void* xq8, int64_t x_stride, float* y, int64_t y_stride, int n_inputs,
-                                       int ncols, int nrows, int mode, const float* logit, cudaStream_t stream);
+// ... `n_inputs` Q8_1 rows x_stride bytes apart, outputs y_stride floats apart; mode 0 store, 1 add, 2 add sigmoid(logit[t]) * v;
+// w2 / y2 (optional): a second matrix against the same inputs in the same launch; chained: programmatic launch
+cudaError_t launch_mmvq_kquant_batched(int wtype, const void* w, const void* w2, const void* xq8, int64_t x_stride, float* y, float* y2,
+                                       int64_t y_stride, int n_inputs, int ncols, int nrows, int mode, const float* logit, bool chained,
+                                       cudaStream_t stream);
 // out[t] (Q8_1 blocks, out_stride bytes apart) = Q8_1(silu(g[t]) * u[t]) or, without g, Q8_1(relu(u[t])^2); rows in_stride floats apart
 cudaError_t launch_act_q8_1(const float* g, const float* u, int64_t in_stride, void* out, int64_t out_stride, int T, int F, cudaStream_t stream);
 cudaError_t launch_block_sumi(int wtype, const void* w, const void* xq8, int32_t* sumi, int ncols, int nrows,

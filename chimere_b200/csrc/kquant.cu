@@ -77,12 +77,17 @@ __device__ __forceinline__ float sub_block(const uint8_t* blk, int j, const uint
 
 // grid = (row groups, input rows).  mode 0: y = v; 1: y += v; 2: y += sigmoid(logit[t]) * v (the sigmoid-gated shared
 // expert added to the routed sum, scratch_pool.rs:266-277).
+// blockIdx.z = 1 takes the second matrix / output (gate beside up: one launch for both).
 template <int TYPE>
-__global__ void __launch_bounds__(32 * kRowsPerCta) kquant_mmvq_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ xq8,
-                                                                      int64_t x_stride, float* __restrict__ y, int64_t y_stride, int ncols,
-                                                                      int nrows, int mode, const float* __restrict__ logit) {
+__global__ void __launch_bounds__(32 * kRowsPerCta) kquant_mmvq_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ w2,
+                                                                      const uint8_t* __restrict__ xq8, int64_t x_stride, float* __restrict__ y,
+                                                                      float* __restrict__ y2, int64_t y_stride, int ncols, int nrows, int mode,
+                                                                      const float* __restrict__ logit) {
     const int lane = threadIdx.x & 31, row = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5), t = blockIdx.y;
+    griddep_wait();   // (a no-op unless launched programmatically behind the kernel that writes the inputs)
+    if (threadIdx.x == 0) griddep_launch();
     if (row >= nrows) return;
+    if (blockIdx.z) { w = w2; y = y2; }
     const int nsub = ncols >> 5;
     const uint8_t* rowp = w + (size_t)row * (size_t)(ncols >> 8) * KBlock<TYPE>::kBytes;
     const uint8_t* xr = xq8 + (size_t)t * x_stride;
@@ -105,6 +110,8 @@ __global__ void __launch_bounds__(256) act_q8_1_kernel(const float* __restrict__
                                                        uint8_t* __restrict__ out, int64_t out_stride, int T, int F) {
     const int lane = threadIdx.x & 31, nb = F >> 5;
     const int64_t wid = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    griddep_wait();
+    if (threadIdx.x == 0) griddep_launch();
     if (wid >= (int64_t)T * nb) return;
     const int t = (int)(wid / nb), b = (int)(wid - (int64_t)t * nb);
     const float uu = u[(size_t)t * in_stride + b * 32 + lane];
@@ -125,38 +132,40 @@ __global__ void __launch_bounds__(256) act_q8_1_kernel(const float* __restrict__
 
 }  // namespace
 
-cudaError_t launch_mmvq_kquant_batched(int wtype, const void* w, const void* xq8, int64_t x_stride, float* y, int64_t y_stride, int n_inputs,
-                                       int ncols, int nrows, int mode, const float* logit, cudaStream_t stream) {
+// w2 / y2 (optional): a second matrix of the same type and shape against the same inputs, in the same launch.
+// chained: launch programmatically behind the previous kernel of the stream.
+cudaError_t launch_mmvq_kquant_batched(int wtype, const void* w, const void* w2, const void* xq8, int64_t x_stride, float* y, float* y2,
+                                       int64_t y_stride, int n_inputs, int ncols, int nrows, int mode, const float* logit, bool chained,
+                                       cudaStream_t stream) {
     if (nrows <= 0 || n_inputs <= 0) return cudaSuccess;
     if (ncols <= 0 || (ncols & 255) || ((uintptr_t)xq8 & 3) || (x_stride & 3) || n_inputs > 65535 || (mode == 2 && !logit)) return cudaErrorInvalidValue;
-    const dim3 grid((nrows + kRowsPerCta - 1) / kRowsPerCta, n_inputs);
+    const uintptr_t wbits = (uintptr_t)w | (uintptr_t)w2;
+    const dim3 grid((nrows + kRowsPerCta - 1) / kRowsPerCta, n_inputs, w2 ? 2 : 1);
     const uint8_t* wp = (const uint8_t*)w;
+    const uint8_t* wp2 = (const uint8_t*)w2;
     const uint8_t* xp = (const uint8_t*)xq8;
+    auto go = [&](auto kernel) {
+        if (chained) return launch_pdl(kernel, grid, 32 * kRowsPerCta, 0, stream, wp, wp2, xp, x_stride, y, y2, y_stride, ncols, nrows, mode, logit);
+        kernel<<<grid, 32 * kRowsPerCta, 0, stream>>>(wp, wp2, xp, x_stride, y, y2, y_stride, ncols, nrows, mode, logit);
+        return cudaGetLastError();
+    };
     switch (wtype) {
-        case CHIMERE_TYPE_Q4_K:
-            if ((uintptr_t)w & 3) return cudaErrorInvalidValue;
-            kquant_mmvq_kernel<CHIMERE_TYPE_Q4_K><<<grid, 32 * kRowsPerCta, 0, stream>>>(wp, xp, x_stride, y, y_stride, ncols, nrows, mode, logit); break;
-        case CHIMERE_TYPE_Q5_K:
-            if ((uintptr_t)w & 3) return cudaErrorInvalidValue;
-            kquant_mmvq_kernel<CHIMERE_TYPE_Q5_K><<<grid, 32 * kRowsPerCta, 0, stream>>>(wp, xp, x_stride, y, y_stride, ncols, nrows, mode, logit); break;
-        case CHIMERE_TYPE_Q6_K:
-            if ((uintptr_t)w & 1) return cudaErrorInvalidValue;
-            kquant_mmvq_kernel<CHIMERE_TYPE_Q6_K><<<grid, 32 * kRowsPerCta, 0, stream>>>(wp, xp, x_stride, y, y_stride, ncols, nrows, mode, logit); break;
+        case CHIMERE_TYPE_Q4_K: return (wbits & 3) ? cudaErrorInvalidValue : go(kquant_mmvq_kernel<CHIMERE_TYPE_Q4_K>);
+        case CHIMERE_TYPE_Q5_K: return (wbits & 3) ? cudaErrorInvalidValue : go(kquant_mmvq_kernel<CHIMERE_TYPE_Q5_K>);
+        case CHIMERE_TYPE_Q6_K: return (wbits & 1) ? cudaErrorInvalidValue : go(kquant_mmvq_kernel<CHIMERE_TYPE_Q6_K>);
         default: return cudaErrorInvalidValue;
     }
-    return cudaGetLastError();
 }
 
 cudaError_t launch_mmvq_kquant(int wtype, const void* w, const void* xq8, float* y, int ncols, int nrows, cudaStream_t stream) {
-    return launch_mmvq_kquant_batched(wtype, w, xq8, 0, y, 0, 1, ncols, nrows, 0, nullptr, stream);
+    return launch_mmvq_kquant_batched(wtype, w, nullptr, xq8, 0, y, nullptr, 0, 1, ncols, nrows, 0, nullptr, false, stream);
 }
 
 cudaError_t launch_act_q8_1(const float* g, const float* u, int64_t in_stride, void* out, int64_t out_stride, int T, int F, cudaStream_t stream) {
     if (T <= 0 || F <= 0) return cudaSuccess;
     if (F & 31) return cudaErrorInvalidValue;
     const int64_t warps = (int64_t)T * (F >> 5);
-    act_q8_1_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(g, u, in_stride, (uint8_t*)out, out_stride, T, F);
-    return cudaGetLastError();
+    return launch_pdl(act_q8_1_kernel, dim3((unsigned)((warps + 7) / 8)), 256, 0, stream, g, u, in_stride, (uint8_t*)out, out_stride, T, F);
 }
 
 }  // namespace chimere
