@@ -539,10 +539,21 @@ int chimere_b200_moe_forward_host(const chimere_moe_layer* w, const float* h_x, 
     const size_t bytes = (size_t)T * w->H * sizeof(float);
     cudaError_t e = cudaMemcpyAsync(d_x, h_x, bytes, cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) return cuda_rc(e);
-    rc = chimere_b200_moe_forward(w, d_x, d_y, T, ws, stream);
+    // A pinned result buffer is addressable from the device under a pointer of its own: the last kernel then stores y
+    // straight into host memory and the copy back (a second trip through the copy engine, serial behind the kernels) is
+    // not needed.  Pageable memory, or a K-quant shared expert (whose last step reads y back), takes the staged copy.
+    float* y_dev = d_y;
+    cudaPointerAttributes attr{};
+    if (!kshared(w) && cudaPointerGetAttributes(&attr, h_y) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer)
+        y_dev = static_cast<float*>(attr.devicePointer);
+    else
+        (void)cudaGetLastError();   // (an unregistered pointer leaves an error behind on older runtimes)
+    rc = chimere_b200_moe_forward(w, d_x, y_dev, T, ws, stream);
     if (rc) return rc;
-    e = cudaMemcpyAsync(h_y, d_y, bytes, cudaMemcpyDeviceToHost, stream);
-    if (e != cudaSuccess) return cuda_rc(e);
+    if (y_dev == d_y) {
+        e = cudaMemcpyAsync(h_y, d_y, bytes, cudaMemcpyDeviceToHost, stream);
+        if (e != cudaSuccess) return cuda_rc(e);
+    }
     return cuda_rc(cudaStreamSynchronize(stream));
 }
 

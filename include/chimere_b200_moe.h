@@ -138,7 +138,9 @@ int chimere_b200_moe_forward(const chimere_moe_layer* w, const float* d_x, float
                              chimere_moe_workspace* ws, cudaStream_t stream);
 
 /* Same, with HOST buffers: copies x in, runs the layer, copies y out, all on `stream`, and
- * waits for the stream.  h_x / h_y should be pinned.  d_x / d_y are caller-provided staging. */
+ * waits for the stream.  h_x / h_y should be pinned.  d_x / d_y are caller-provided staging.
+ * When h_y is pinned (cudaHostAlloc / cudaHostRegister) the last kernel stores the result straight into it and d_y
+ * is not used; pageable memory goes through d_y and a copy. */
 int chimere_b200_moe_forward_host(const chimere_moe_layer* w, const float* h_x, float* h_y, int T,
                                   float* d_x, float* d_y, chimere_moe_workspace* ws,
                                   cudaStream_t stream);

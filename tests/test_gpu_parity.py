@@ -273,6 +273,10 @@ def test_host_entry_and_rmsnorm():
         forward_moe_host(wd, sc, x, y)
         check_rows(y.numpy(), oracle.moe_forward(wh, x.numpy(), taps=False)["y"])
         assert not torch.equal(y, first)
+    # pageable result buffer: the staged copy; bit-identical to the direct store into pinned memory
+    y_pageable = torch.empty(T, cfg.H)
+    forward_moe_host(wd, sc, x, y_pageable)
+    assert torch.equal(y_pageable, y)
     lib = abi.load()
     yd = y.cuda()
     out = torch.empty_like(yd)
