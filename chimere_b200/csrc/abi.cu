@@ -731,7 +731,7 @@ static int kshared_chain(const chimere_moe_layer* w, int T, float* d_y, chimere_
 // in place: token tiles for the experts with at least kGemmMin pairs (and the shared expert, if any) on the grouped GEMM,
 // the rest on the GEMV kernels; per-pair rows land in ws->pair_out.
 static int prefill_experts(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, int T, chimere_moe_workspace* ws,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, const void* d_packed = nullptr, int row_bytes = 0) {
     if (!pw || !ws->prefill_arena) return -1;
     if (w->layout != CHIMERE_LAYOUT_TILED32 || !prefill_dims_ok(w)) return -2;
     const PrefillArena A = prefill_arena(w, ws->max_T);
@@ -742,7 +742,12 @@ static int prefill_experts(const chimere_moe_layer* w, const chimere_moe_prefill
     const int n_tiles_max = n_tiles_max_for(w, T);
     cudaError_t e = launch_build_tiles(ws->offsets, ws->perm, tiles, ws->group_list, w->E, T, w->top_k, w->F_s > 0, kGemmMin, stream);
     if (e != cudaSuccess) return cuda_rc(e);
-    e = launch_gather_tiles(tiles, ws->perm, ws->x_q, ws->x_d, L.x_d_stride, base + A.bx, A.bx_stride, w->H, w->top_k, n_tiles_max, stream);
+    // the rows' Q8_1 planes: the workspace's, or (expert-parallel owner) the received packed rows in place
+    const int8_t* xq = d_packed ? (const int8_t*)d_packed : ws->x_q;
+    const float* xd = d_packed ? (const float*)((const uint8_t*)d_packed + w->H) : ws->x_d;
+    const int64_t xq_stride = d_packed ? row_bytes : w->H;
+    const int xd_stride = d_packed ? row_bytes / 4 : L.x_d_stride;
+    e = launch_gather_tiles(tiles, ws->perm, xq, xq_stride, xd, xd_stride, base + A.bx, A.bx_stride, w->H, w->top_k, n_tiles_max, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     // the small experts: GEMV kernels on the rewritten work list, per-pair rows only
     // (the shared expert is not on this list: the kernels are sized for the routed matrices alone)
@@ -752,6 +757,7 @@ static int prefill_experts(const chimere_moe_layer* w, const chimere_moe_prefill
     const int max_entries = w->E < T * w->top_k ? w->E : T * w->top_k;
     GemvParams gu = gate_up_params(w, T, ws, L);
     gu.nrows_shared = 0; gu.ncols_shared = 0; gu.sh_a = nullptr; gu.sh_b = nullptr;
+    if (d_packed) { gu.in_soa_q = xq; gu.in_soa_q_stride = xq_stride; gu.in_soa_d = xd; gu.in_soa_d_stride = xd_stride; }
     e = launch_gate_up_tiled(gu, max_entries, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     GemvParams dn = down_params(w, nullptr, T, ws, L);
@@ -817,6 +823,36 @@ int chimere_b200_moe_experts_prefill(const chimere_moe_layer* w_local, const chi
     cudaError_t e = launch_permute(p, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     return prefill_experts(w_local, pw_local, n_rows, ws, stream);
+}
+
+// ... with the rows where an exchange left them: packed rows [H int8][d_stride f32][int32 local expert id] (see ep_pack).
+int chimere_b200_moe_experts_packed_prefill(const chimere_moe_layer* w_local, const chimere_moe_prefill_weights* pw_local, int n_rows,
+                                            const void* d_rows, int row_bytes, chimere_moe_workspace* ws, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    if (!d_rows) return -1;
+    int rc = check_call(w_local, ws, ws, n_rows, ws);
+    if (rc) return rc;
+    if (w_local->layout != CHIMERE_LAYOUT_TILED32 || w_local->top_k != 1 || w_local->F_s != 0) return -2;
+    const int ds = (w_local->H / 32 + 3) & ~3;
+    if (row_bytes % 16 || row_bytes < w_local->H + 4 * ds + 4) return -2;
+    RouteParams p = route_params(w_local, nullptr, n_rows, ws);
+    p.has_shared = 0;
+    p.list_mode = 2;
+    p.topk_idx = (int32_t*)((uint8_t*)d_rows + w_local->H + 4 * ds);
+    p.idx_stride = row_bytes / 4;
+    cudaError_t e = launch_permute(p, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    return prefill_experts(w_local, pw_local, n_rows, ws, stream, d_rows, row_bytes);
+}
+
+int chimere_b200_moe_ep_pack_sorted(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, void* d_send, int32_t* d_slot,
+                                    int experts_per_rank, int row_bytes, cudaStream_t stream) {
+    int rc = check_call(w, d_send, d_slot, T, ws);
+    if (rc) return rc;
+    const int ds = (w->H / 32 + 3) & ~3;
+    if (experts_per_rank <= 0 || row_bytes % 16 || row_bytes < w->H + 4 * ds + 4) return -2;
+    return cuda_rc(launch_ep_pack_sorted(ws->perm, ws->topk_idx, ws->x_q, ws->x_d, ds, (uint8_t*)d_send, d_slot, T, w->top_k, w->H,
+                                         experts_per_rank, row_bytes, stream));
 }
 
 int chimere_b200_moe_forward_residual_norm(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, const float* d_hidden,

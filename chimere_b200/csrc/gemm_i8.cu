@@ -731,8 +731,9 @@ __global__ void __launch_bounds__(256) build_tiles_kernel(const int32_t* offsets
 // grid = (max tiles, 16 groups of 8 token slots), 256 threads = 8 slots x 32 chunk lanes: the eight slots of a group
 // are the 8 x 16 bytes of one core-matrix row group, so every 128-byte segment of the tile is written whole, and a
 // token's 16-byte chunks are read four in a row.
-__global__ void __launch_bounds__(256) gather_tiles_kernel(const int32_t* tiles, const int32_t* perm, const int8_t* x_q, const float* x_d,
-                                                           int x_d_stride, uint8_t* b_tiles, int64_t b_tile_stride, int H, int top_k) {
+__global__ void __launch_bounds__(256) gather_tiles_kernel(const int32_t* tiles, const int32_t* perm, const int8_t* x_q, int64_t x_q_stride,
+                                                           const float* x_d, int x_d_stride, uint8_t* b_tiles, int64_t b_tile_stride, int H,
+                                                           int top_k) {
     const int j = blockIdx.x, grp = blockIdx.y;
     if (j >= __ldcg(tiles)) return;
     const int4 t = __ldcg(reinterpret_cast<const int4*>(tiles + kTileHeader) + j);
@@ -742,7 +743,7 @@ __global__ void __launch_bounds__(256) gather_tiles_kernel(const int32_t* tiles,
     const int tok = !valid ? 0 : (t.x < 0 ? t.y + c : __ldcg(perm + t.y + c) / top_k);
     uint8_t* base = b_tiles + (size_t)j * b_tile_stride;
     for (int ch = lane_ch; ch < H / 16; ch += 32) {
-        const uint4 v = valid ? __ldcg(reinterpret_cast<const uint4*>(x_q + (size_t)tok * H) + ch) : make_uint4(0, 0, 0, 0);
+        const uint4 v = valid ? __ldcg(reinterpret_cast<const uint4*>(x_q + (size_t)tok * x_q_stride) + ch) : make_uint4(0, 0, 0, 0);
         const int b = ch >> 1, khalf = ch & 1;
         *reinterpret_cast<uint4*>(base + (size_t)b * kG_TileBytes + khalf * 2048 + grp * 128 + sl * 16) = v;
     }
@@ -756,10 +757,10 @@ cudaError_t launch_build_tiles(const int32_t* offsets, const int32_t* perm, int3
     return cudaGetLastError();
 }
 
-cudaError_t launch_gather_tiles(const int32_t* tiles, const int32_t* perm, const int8_t* x_q, const float* x_d, int x_d_stride,
-                                uint8_t* b_tiles, int64_t b_tile_stride, int H, int top_k, int n_tiles_max, cudaStream_t stream) {
+cudaError_t launch_gather_tiles(const int32_t* tiles, const int32_t* perm, const int8_t* x_q, int64_t x_q_stride, const float* x_d,
+                                int x_d_stride, uint8_t* b_tiles, int64_t b_tile_stride, int H, int top_k, int n_tiles_max, cudaStream_t stream) {
     if (n_tiles_max <= 0) return cudaSuccess;
-    gather_tiles_kernel<<<dim3(n_tiles_max, 16), 256, 0, stream>>>(tiles, perm, x_q, x_d, x_d_stride, b_tiles, b_tile_stride, H, top_k);
+    gather_tiles_kernel<<<dim3(n_tiles_max, 16), 256, 0, stream>>>(tiles, perm, x_q, x_q_stride, x_d, x_d_stride, b_tiles, b_tile_stride, H, top_k);
     return cudaGetLastError();
 }
 

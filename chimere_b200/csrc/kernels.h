@@ -87,6 +87,9 @@ cudaError_t launch_permute(const RouteParams& p, cudaStream_t stream);
 cudaError_t launch_ep_finish(const float* rows, const int32_t* slot, const float* topk_w, const float* shared_rows, const float* sh_logit,
                              float* y, int T, int H, int k, cudaStream_t stream);
 // fixed-size dispatch: fill send[world*cap][row_bytes] with the pairs of each destination rank in pair order
+// exact-size dispatch: send row j = the pair perm[j] (pairs sorted by expert, hence by owner rank), slot[pair] = j
+cudaError_t launch_ep_pack_sorted(const int32_t* perm, const int32_t* topk_idx, const int8_t* x_q, const float* x_d, int d_stride, uint8_t* send,
+                                  int32_t* slot, int T, int k, int H, int experts_per_rank, int row_bytes, cudaStream_t stream);
 cudaError_t launch_ep_pack(const int32_t* topk_idx, const int8_t* x_q, const float* x_d, int d_stride, uint8_t* send, int32_t* slot,
                            int T, int k, int H, int experts_per_rank, int world, int cap, int row_bytes, cudaStream_t stream);
 // expert-parallel exchange by peer stores (decode-size batches); see router.cu
@@ -157,8 +160,8 @@ cudaError_t launch_pack_mma128_ggml(int type, const void* raw, void* out, int n_
                                     int64_t raw_stride, int64_t out_stride, cudaStream_t stream);
 cudaError_t launch_build_tiles(const int32_t* offsets, const int32_t* perm, int32_t* tiles, int32_t* list, int E, int T, int top_k,
                                int has_shared, int gemm_min, cudaStream_t stream);
-cudaError_t launch_gather_tiles(const int32_t* tiles, const int32_t* perm, const int8_t* x_q, const float* x_d, int x_d_stride,
-                                uint8_t* b_tiles, int64_t b_tile_stride, int H, int top_k, int n_tiles_max, cudaStream_t stream);
+cudaError_t launch_gather_tiles(const int32_t* tiles, const int32_t* perm, const int8_t* x_q, int64_t x_q_stride, const float* x_d,
+                                int x_d_stride, uint8_t* b_tiles, int64_t b_tile_stride, int H, int top_k, int n_tiles_max, cudaStream_t stream);
 cudaError_t launch_pack_mma128(const int8_t* q, const float* scales, uint8_t* out, int rows, int cols, cudaStream_t stream);
 
 // tiled32 layout (tiled.cuh): pack, kernels on packed weights, parity tap

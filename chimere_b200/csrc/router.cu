@@ -971,6 +971,31 @@ cudaError_t launch_ep_finish(const float* rows, const int32_t* slot, const float
     return cudaGetLastError();
 }
 
+// Exact-size dispatch (prefill-size batches): the routing kernel's dispatch has already sorted the pairs by expert, and the
+// experts of an owner rank are contiguous, so perm[] lists the pairs grouped by destination.  One CTA per sorted position j
+// copies pair perm[j]'s row in the same row format as above and notes slot[pair] = j for the way back.
+__global__ void __launch_bounds__(128) ep_pack_sorted_kernel(const int32_t* perm, const int32_t* topk_idx, const int8_t* x_q, const float* x_d,
+                                                             int d_stride, uint8_t* send, int32_t* slot, int k, int H, int experts_per_rank,
+                                                             int row_bytes) {
+    const int j = blockIdx.x, pair = __ldcg(perm + j), t = pair / k;
+    const int e = __ldcg(topk_idx + pair);
+    uint8_t* row = send + (size_t)j * row_bytes;
+    const uint4* sq = reinterpret_cast<const uint4*>(x_q + (size_t)t * H);
+    for (int v = threadIdx.x; v < H / 16; v += blockDim.x) reinterpret_cast<uint4*>(row)[v] = sq[v];
+    const float* sd = x_d + (size_t)t * d_stride;
+    for (int v = threadIdx.x; v < d_stride; v += blockDim.x) reinterpret_cast<float*>(row + H)[v] = sd[v];
+    if (threadIdx.x == 0) {
+        *reinterpret_cast<int32_t*>(row + H + 4 * d_stride) = e % experts_per_rank;
+        slot[pair] = j;
+    }
+}
+cudaError_t launch_ep_pack_sorted(const int32_t* perm, const int32_t* topk_idx, const int8_t* x_q, const float* x_d, int d_stride, uint8_t* send,
+                                  int32_t* slot, int T, int k, int H, int experts_per_rank, int row_bytes, cudaStream_t stream) {
+    if (T * k <= 0) return cudaSuccess;
+    ep_pack_sorted_kernel<<<T * k, 128, 0, stream>>>(perm, topk_idx, x_q, x_d, d_stride, send, slot, k, H, experts_per_rank, row_bytes);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_ep_pack(const int32_t* topk_idx, const int8_t* x_q, const float* x_d, int d_stride, uint8_t* send, int32_t* slot,
                            int T, int k, int H, int experts_per_rank, int world, int cap, int row_bytes, cudaStream_t stream) {
     ep_pack_kernel<<<world * cap, 128, 0, stream>>>(topk_idx, x_q, x_d, d_stride, send, slot, T, k, H, experts_per_rank, cap, row_bytes);

@@ -32,7 +32,9 @@ class DispatchPlan:
 
 
 def plan_dispatch(topk_idx: torch.Tensor, experts_per_rank: int, world: int) -> DispatchPlan:
-    """Pairs in row-major (token, slot) order -> send order grouped by owner rank (stable)."""
+    """Pairs in row-major (token, slot) order -> send order grouped by owner rank (stable).  Host-side statement of the
+    exchange plan, used by the CPU tests of the collective plumbing; the GPU path takes the order from the dispatch kernel's
+    permutation instead (ExpertParallelMoE.forward)."""
     flat = topk_idx.reshape(-1).to(torch.int64)
     dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
     order = torch.sort(dest, stable=True).indices
@@ -102,34 +104,45 @@ class ExpertParallelMoE:
         self.last_recv_rows = 0
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        lib, T, k, H = self.lib, x.shape[0], self.k, self.H
+        """Exact split sizes (prefill-size batches).  The routing kernel's dispatch has sorted the pairs by expert, which
+        groups them by owner rank; a kernel packs the rows in that order, the per-rank counts are differences of the
+        dispatch offsets (the one value the host needs: the split sizes of the collectives), one all-to-all carries the
+        packed rows, the owner's experts run on them in place, one all-to-all carries the per-pair rows back."""
+        lib, T, k, H, G = self.lib, x.shape[0], self.k, self.H, self.world
         assert T <= self.max_tokens and x.is_contiguous()
         if out is None:
             out = torch.empty_like(x)
-        st = torch.cuda.current_stream(x.device).cuda_stream
+        dev = x.device
+        st = torch.cuda.current_stream(dev).cuda_stream
+        if not hasattr(self, "_exact"):
+            ds = self.ws_home.dstride
+            rb = (H + 4 * ds + 4 + 15) & ~15
+            self._exact = dict(rb=rb, send=torch.empty(self.max_tokens * k, rb, dtype=torch.uint8, device=dev),
+                               recv=torch.empty(self.max_rows, rb, dtype=torch.uint8, device=dev),
+                               slot=torch.zeros(self.max_tokens * k, dtype=torch.int32, device=dev),
+                               bounds=torch.arange(0, self.E + 1, self.E_loc, device=dev))
+        ex = self._exact
+        rb = ex["rb"]
         abi.check(lib.chimere_b200_moe_route_home(C.byref(self.home), x.data_ptr(), T, C.byref(self.ws_home.ws), st), "route_home")
+        abi.check(lib.chimere_b200_moe_ep_pack_sorted(C.byref(self.home), T, C.byref(self.ws_home.ws), ex["send"].data_ptr(), ex["slot"].data_ptr(),
+                                                      self.E_loc, rb, st), "ep_pack_sorted")
         # the shared expert needs nothing from other ranks: enqueue it before the exchanges
         abi.check(lib.chimere_b200_moe_shared_expert(C.byref(self.home), T, C.byref(self.ws_home.ws), st), "shared_expert")
-        plan = plan_dispatch(self.ws_home.topk_idx(T, k), self.E_loc, self.world)
-        recv_counts_t = exchange_counts(plan.send_counts, self.group)
-        send_counts, recv_counts = plan.send_counts.tolist(), recv_counts_t.tolist()   # host sync: split sizes
+        send_counts_t = self.ws_home.offsets(self.E)[ex["bounds"]].diff().to(torch.int64)
+        recv_counts_t = exchange_counts(send_counts_t, self.group)
+        send_counts, recv_counts = send_counts_t.tolist(), recv_counts_t.tolist()   # host sync: split sizes
         n = sum(recv_counts)
         assert n <= self.max_rows
         self.last_recv_rows = n
-        tok = torch.div(plan.order, k, rounding_mode="floor")
-        # dispatch: int8 plane, scale plane and local expert id of every pair, straight into the owner's workspace
-        all_to_all_rows(self.ws_home.x_q(T)[tok], send_counts, recv_counts, self.ws_owner.x_q(self.max_rows), self.group)
-        all_to_all_rows(self.ws_home.x_d(T)[tok], send_counts, recv_counts, self.ws_owner.x_d(self.max_rows), self.group)
-        all_to_all_rows(plan.local_ids, send_counts, recv_counts, self.ws_owner.topk_idx(self.max_rows, 1).reshape(-1), self.group)
+        recv = all_to_all_rows(ex["send"][:T * k], send_counts, recv_counts, ex["recv"], self.group)
         if self.pw_owner is not None and n >= 512:   # many rows per expert: the grouped GEMM
-            abi.check(lib.chimere_b200_moe_experts_prefill(C.byref(self.owner), C.byref(self.pw_owner.struct), n, C.byref(self.ws_owner.ws), st),
-                      "experts_prefill")
+            abi.check(lib.chimere_b200_moe_experts_packed_prefill(C.byref(self.owner), C.byref(self.pw_owner.struct), n, recv.data_ptr(), rb,
+                                                                  C.byref(self.ws_owner.ws), st), "experts_packed_prefill")
         else:
-            abi.check(lib.chimere_b200_moe_experts(C.byref(self.owner), n, C.byref(self.ws_owner.ws), st), "experts")
-        # combine: the pairs' expert rows come home, back into (token, slot) order
+            abi.check(lib.chimere_b200_moe_experts_packed(C.byref(self.owner), n, recv.data_ptr(), rb, C.byref(self.ws_owner.ws), st), "experts")
+        # combine: the pairs' expert rows come home in send order; the finish kernel finds a pair's row through its slot
         back = all_to_all_rows(self.ws_owner.pair_out(self.max_rows)[:n], recv_counts, send_counts, self.back, self.group)
-        self.rows_pair[:T * k].index_copy_(0, plan.order, back)
-        abi.check(lib.chimere_b200_moe_ep_finish(C.byref(self.home), self.rows_pair.data_ptr(), None, T, C.byref(self.ws_home.ws),
+        abi.check(lib.chimere_b200_moe_ep_finish(C.byref(self.home), back.data_ptr(), ex["slot"].data_ptr(), T, C.byref(self.ws_home.ws),
                                                  out.data_ptr(), st), "ep_finish")
         return out
 
@@ -289,6 +302,9 @@ class _Scratch:
 
     def topk_idx(self, T, k):
         return self._view(self.ws.topk_idx, T * k * 4).view(torch.int32).reshape(T, k)
+
+    def offsets(self, E):
+        return self._view(self.ws.offsets, (E + 1) * 4).view(torch.int32)
 
     def x_q(self, T):
         return self._view(self.ws.x_q, T * self.H).view(torch.int8).reshape(T, self.H)

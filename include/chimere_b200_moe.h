@@ -332,6 +332,16 @@ int chimere_b200_moe_routing_trace(const chimere_moe_layer* w, int T, const chim
  * prefill arena.  No counterpart in the reference (single GPU, no prefill kernel). */
 int chimere_b200_moe_experts_prefill(const chimere_moe_layer* w_local, const chimere_moe_prefill_weights* pw_local, int n_rows,
                                      chimere_moe_workspace* ws, cudaStream_t stream);
+/* The same on rows that lie where an exchange left them (the row format of chimere_b200_moe_ep_pack). */
+int chimere_b200_moe_experts_packed_prefill(const chimere_moe_layer* w_local, const chimere_moe_prefill_weights* pw_local,
+                                            int n_rows, const void* d_rows, int row_bytes, chimere_moe_workspace* ws,
+                                            cudaStream_t stream);
+/* Exact-size dispatch for a prefill-size batch: after chimere_b200_moe_route_home, ws->perm lists the T * top_k pairs sorted
+ * by expert, i.e. grouped by owner rank (the ranks own contiguous expert ranges; ws->offsets[r * experts_per_rank] is
+ * the first row for rank r).  Row j of d_send = pair perm[j] in the packed row format, d_slot[pair] = j.  The caller sends
+ * the rank ranges with one all-to-all of exact sizes. */
+int chimere_b200_moe_ep_pack_sorted(const chimere_moe_layer* w, int T, chimere_moe_workspace* ws, void* d_send, int32_t* d_slot,
+                                    int experts_per_rank, int row_bytes, cudaStream_t stream);
 
 /* RMSNorm with unit weight over rows of length H: y = x / sqrt(mean(x^2) + eps). Used between
  * stacked layers. */
