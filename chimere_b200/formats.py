@@ -13,7 +13,7 @@ Formats (sizes as in chimere-server/src/gguf_loader.rs:161-193 of the reference)
 The Q4_0 and Q8_0 quantizers follow ggml's reference rounding (tests compare their bytes with
 gguf.quants).  Neither the reference nor the gguf package has an IQ3_S *encoder*; the one here
 is our own (nearest codebook entry per 4 weights through a 4096-entry table) -- any valid
-encoding serves, because parity is judged on identical bytes.
+encoding serves, because parity means identical bytes.
 """
 from __future__ import annotations
 

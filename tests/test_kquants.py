@@ -63,3 +63,48 @@ def test_oracle_dot_is_the_dequantised_dot(qtype):
     ref = oracle.dequant(qtype, W, rows * cols).reshape(rows, cols).astype(np.float64) @ xh.reshape(cols)
     ref += _mins(qtype, W, cols) @ (xh.sum(1) - ds[:, 1])
     np.testing.assert_allclose(y, ref, rtol=0, atol=3e-5 * np.abs(ref).max())
+
+
+# ---- the reference's own Q5_K checks (ffi/src/lib.rs:1050-1270), on blocks built the way its test helper builds them:
+# every six-bit scale 1, every min 0, dmin 0, d = amax / 31, quants round(|v| / d) ----
+def _ramp_block_q5k(values):
+    values = np.asarray(values, np.float32)
+    assert values.size == 256
+    blk = np.zeros(176, np.uint8)
+    amax = float(np.abs(values).max())
+    d = amax / 31.0 if amax > 0 else 0.0
+    blk[0:2] = np.array([d], np.float16).view(np.uint8)
+    blk[4:8] = 1            # scales of sub-blocks 0..3
+    blk[12:16] = 1          # low nibbles: scales of sub-blocks 4..7 (mins stay 0)
+    q = np.clip(np.round(np.abs(values) / d), 0, 31).astype(np.uint8) if d > 0 else np.zeros(256, np.uint8)
+    for j in range(8):
+        sub = q[32 * j:32 * j + 32]
+        qs = blk[48 + 32 * (j // 2):48 + 32 * (j // 2) + 32]
+        qs |= ((sub & 15) << 4) if (j & 1) else (sub & 15)
+        blk[16:48] |= ((sub >> 4) & 1) << j
+    return blk
+
+
+def test_q5k_dot_against_dequantised_dot_as_the_reference_tests_it():
+    w = _ramp_block_q5k(np.arange(256) * 0.1)
+    x = (1.0 - np.arange(256) * 0.005).astype(np.float32)
+    y = oracle.gemv(formats.TYPE_Q5_K, w[None, :], oracle.quantize_q8_1(x), 256, 1)[0]
+    ref = float(oracle.dequant(formats.TYPE_Q5_K, w, 256).astype(np.float64) @ x.astype(np.float64))
+    assert abs(y - ref) / abs(ref) < 0.01          # the reference's bound (lib.rs:1195-1198)
+    # and the decoder returns the ramp up to half a quantisation step
+    np.testing.assert_allclose(oracle.dequant(formats.TYPE_Q5_K, w, 256), np.arange(256) * 0.1, atol=0.5 * 25.5 / 31 + 0.02)   # half a step + the f16 rounding of d
+
+
+def test_q5k_zero_input_gives_zero():
+    w = _ramp_block_q5k(np.ones(256))
+    y = oracle.gemv(formats.TYPE_Q5_K, w[None, :], oracle.quantize_q8_1(np.zeros(256, np.float32)), 256, 1)[0]
+    assert abs(y) < 1e-6                            # lib.rs:1211-1214
+
+
+def test_q5k_matmul_rows_as_the_reference_tests_them():
+    rows = np.stack([_ramp_block_q5k((r + 1) * np.arange(256) * 0.01) for r in range(4)])
+    x = (1.0 / (1.0 + np.arange(256))).astype(np.float32)
+    y = oracle.gemv(formats.TYPE_Q5_K, rows, oracle.quantize_q8_1(x), 256, 4)
+    for r in range(4):
+        ref = float(oracle.dequant(formats.TYPE_Q5_K, rows[r], 256).astype(np.float64) @ x.astype(np.float64))
+        assert abs(y[r] - ref) / abs(ref) < 0.02    # lib.rs:1262-1266
