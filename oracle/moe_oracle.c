@@ -15,7 +15,9 @@
  * src/gguf_loader.rs:1765-1790, SwiGLU values of src/expert.rs:356-411, dot/sigmoid-gate
  * cases of src/scratch_pool.rs:412-491), and on a GPU box the reference's own kernels
  * (chimere-server/kernels/chimere_kernels.cu compiled for sm_100a into oracle/_ref/) are run
- * on the same inputs.  Not pinned by anything in the reference (no implementation there):
+ * on the same inputs.  The K-quant decoders and dots (Q4_K, Q5_K, Q6_K) are checked in tests/test_kquants.py against
+ * an independent decoder (the gguf Python package's dequantize) and with the reference's own Q5_K tests
+ * (ffi/src/lib.rs:1150-1270).  Not pinned by anything in the reference (no implementation there):
  * Q4_0 x Q8_1 integer dots, the dispatch permutation, the sigmoid/top-6 router variant and
  * the squared-ReLU expert -- for those this file is the definition ("parity unpinned").
  */
