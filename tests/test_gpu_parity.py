@@ -466,7 +466,7 @@ def test_layer_loaded_from_a_gguf_file_gives_the_same_output(tmp_path):
 
 
 @pytest.mark.parametrize("sh_types", [(formats.TYPE_Q5_K, formats.TYPE_Q5_K), (formats.TYPE_Q4_K, formats.TYPE_Q6_K)])
-@pytest.mark.parametrize("T,entry", [(1, "decode"), (8, "decode"), (40, "decode"), (96, "prefill")])
+@pytest.mark.parametrize("T,entry", [(1, "decode"), (8, "decode"), (40, "decode"), (333, "decode"), (96, "prefill"), (600, "prefill")])
 def test_layer_with_kquant_shared_expert(sh_types, T, entry):
     """The production mix: IQ3_S / Q4_0 routed experts with the shared expert in K-quant super-blocks (moe_ffn.rs:1597-1730).
     The whole-layer entries run the routed part as usual and the shared expert as GEMVs on the raw blocks."""
