@@ -282,6 +282,7 @@ int chimere_b200_moe_experts(const chimere_moe_layer* w_local, int n_rows, chime
 
 int chimere_b200_moe_experts_packed(const chimere_moe_layer* w_local, int n_rows, const void* d_rows, int row_bytes,
                                     chimere_moe_workspace* ws, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
     if (!d_rows) return -1;
     return run_experts(w_local, n_rows, d_rows, row_bytes, ws, stream);
 }

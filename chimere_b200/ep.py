@@ -134,12 +134,12 @@ class ExpertParallelMoE:
         n = sum(recv_counts)
         assert n <= self.max_rows
         self.last_recv_rows = n
-        recv = all_to_all_rows(ex["send"][:T * k], send_counts, recv_counts, ex["recv"], self.group)
+        all_to_all_rows(ex["send"][:T * k], send_counts, recv_counts, ex["recv"], self.group)   # (a rank may receive nothing)
         if self.pw_owner is not None and n >= 512:   # many rows per expert: the grouped GEMM
-            abi.check(lib.chimere_b200_moe_experts_packed_prefill(C.byref(self.owner), C.byref(self.pw_owner.struct), n, recv.data_ptr(), rb,
+            abi.check(lib.chimere_b200_moe_experts_packed_prefill(C.byref(self.owner), C.byref(self.pw_owner.struct), n, ex["recv"].data_ptr(), rb,
                                                                   C.byref(self.ws_owner.ws), st), "experts_packed_prefill")
         else:
-            abi.check(lib.chimere_b200_moe_experts_packed(C.byref(self.owner), n, recv.data_ptr(), rb, C.byref(self.ws_owner.ws), st), "experts")
+            abi.check(lib.chimere_b200_moe_experts_packed(C.byref(self.owner), n, ex["recv"].data_ptr(), rb, C.byref(self.ws_owner.ws), st), "experts")
         # combine: the pairs' expert rows come home in send order; the finish kernel finds a pair's row through its slot
         back = all_to_all_rows(self.ws_owner.pair_out(self.max_rows)[:n], recv_counts, send_counts, self.back, self.group)
         abi.check(lib.chimere_b200_moe_ep_finish(C.byref(self.home), back.data_ptr(), ex["slot"].data_ptr(), T, C.byref(self.ws_home.ws),

@@ -58,6 +58,26 @@ def main():
               f" (rows received {ep.last_recv_rows}, status {status})", flush=True)
         ok = ok and same and near and status == 0
 
+    # ---- every pair goes to rank 0's experts (a bias of +60 on them): the other ranks receive nothing ----
+    cfg, T = configs.scaled(configs.QWEN_Q4_0, E=32), 8
+    full = configs.make_layer(cfg, device=dev)
+    bias = torch.zeros(cfg.E, device=dev)
+    bias[:cfg.E // world] = 60.0
+    full.router_bias = bias
+    ep = ExpertParallelMoE(full, max_tokens=T, rank=rank, world=world, device=dev)
+    ep.enable_peer_exchange()
+    x = configs.make_input(cfg, T, device=dev, seed=60 + rank)
+    y_a = ep.forward(x).clone()
+    n_exact = ep.last_recv_rows
+    y_b = ep.forward_peer(x, torch.empty_like(x)).clone()
+    packed = MoeWeightsTiled(full)
+    y_ref = forward_moe(packed, MoeScratch(packed, T, device=dev), x)
+    torch.cuda.synchronize()
+    lone_ok = bool(torch.equal(y_a, y_ref)) and close(y_b, y_ref, 1e-5) and n_exact == (world * T * cfg.top_k if rank == 0 else 0)
+    print(f"rank {rank} all pairs to rank 0: {'ok' if lone_ok else 'MISMATCH'} (rows received {n_exact})", flush=True)
+    ok = ok and lone_ok
+    del ep, full, packed
+
     # ---- a prefill-size batch: exact split sizes, the owners' large experts on the grouped GEMM ----
     cfg, T = configs.scaled(configs.QWEN_Q4_0_ZIPF, E=32), 600
     full = configs.make_layer(cfg, device=dev)
