@@ -104,6 +104,7 @@ PROTOTYPES = {
     "chimere_b200_moe_forward_residual_norm": (C.c_int, [_LAYER_P, C.POINTER(PrefillWeights), _P, _P, _P, C.c_float, _P, C.c_int, _WS_P, _P]),
     "chimere_b200_moe_routing_trace": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P, _P, _P]),
     "chimere_b200_moe_experts_prefill": (C.c_int, [_LAYER_P, C.POINTER(PrefillWeights), C.c_int, _WS_P, _P]),
+    "chimere_b200_moe_shared_expert_prefill": (C.c_int, [_LAYER_P, C.POINTER(PrefillWeights), C.c_int, _WS_P, _P]),
     "chimere_b200_moe_experts_packed_prefill": (C.c_int, [_LAYER_P, C.POINTER(PrefillWeights), C.c_int, _P, C.c_int, _WS_P, _P]),
     "chimere_b200_moe_ep_pack_sorted": (C.c_int, [_LAYER_P, C.c_int, _WS_P, _P, _P, C.c_int, C.c_int, _P]),
     "chimere_b200_rmsnorm": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_float, _P]),

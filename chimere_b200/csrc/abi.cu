@@ -731,6 +731,8 @@ static int kshared_chain(const chimere_moe_layer* w, int T, float* d_y, chimere_
 // The expert products of a prefill-size batch whose routing (ws->offsets, ws->perm) and Q8_1 planes (ws->x_q, ws->x_d) are
 // in place: token tiles for the experts with at least kGemmMin pairs (and the shared expert, if any) on the grouped GEMM,
 // the rest on the GEMV kernels; per-pair rows land in ws->pair_out.
+static int prefill_gemms(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, int T, chimere_moe_workspace* ws, uint8_t* base,
+                         const PrefillArena& A, int32_t* tiles, int n_tiles_max, cudaStream_t stream);
 static int prefill_experts(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, int T, chimere_moe_workspace* ws,
                            cudaStream_t stream, const void* d_packed = nullptr, int row_bytes = 0) {
     if (!pw || !ws->prefill_arena) return -1;
@@ -767,6 +769,13 @@ static int prefill_experts(const chimere_moe_layer* w, const chimere_moe_prefill
     e = launch_down_tiled(dn, max_entries, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     // the large experts and the shared expert: grouped GEMMs
+    return prefill_gemms(w, pw, T, ws, base, A, tiles, n_tiles_max, stream);
+}
+
+// The two grouped GEMM launches over the token tiles in `tiles` (gate/up with the fused activation and Q8_1 step, then down).
+static int prefill_gemms(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, int T, chimere_moe_workspace* ws, uint8_t* base,
+                         const PrefillArena& A, int32_t* tiles, int n_tiles_max, cudaStream_t stream) {
+    cudaError_t e;
     PrefillGemmParams g{};
     g.tiles = tiles; g.perm = ws->perm; g.status = ws->status;
     g.act = w->act; g.T = T; g.top_k = w->top_k; g.H = w->H;
@@ -824,6 +833,29 @@ int chimere_b200_moe_experts_prefill(const chimere_moe_layer* w_local, const chi
     cudaError_t e = launch_permute(p, stream);
     if (e != cudaSuccess) return cuda_rc(e);
     return prefill_experts(w_local, pw_local, n_rows, ws, stream);
+}
+
+// Expert-parallel home rank, prefill-size: the shared expert of this rank's T tokens on the grouped GEMM (token tiles of
+// the shared expert only), per-token rows into ws->pair_out[T * top_k + t] as chimere_b200_moe_shared_expert leaves them.
+int chimere_b200_moe_shared_expert_prefill(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, int T, chimere_moe_workspace* ws,
+                                           cudaStream_t stream) {
+    int rc = check_call(w, ws, ws, T, ws);
+    if (rc) return rc;
+    if (w->F_s <= 0) return 0;
+    if (!pw || !pw->sh_gu || !pw->sh_down || !ws->prefill_arena) return -1;
+    if (w->layout != CHIMERE_LAYOUT_TILED32 || !prefill_dims_ok(w)) return -2;
+    const PrefillArena A = prefill_arena(w, ws->max_T);
+    if (ws->prefill_bytes < A.total || ((uintptr_t)ws->prefill_arena & 255)) return -4;
+    uint8_t* base = (uint8_t*)ws->prefill_arena;
+    int32_t* tiles = (int32_t*)(base + A.tiles);
+    const Layout L = make_layout(w, ws->max_T);
+    const int n_tiles = (T + 127) / 128;
+    // no routed expert gets a tile (E = 0): the list holds the shared expert's token tiles alone
+    cudaError_t e = launch_build_tiles(ws->offsets, ws->perm, tiles, ws->group_list, 0, T, w->top_k, 1, kGemmMin, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    e = launch_gather_tiles(tiles, ws->perm, ws->x_q, w->H, ws->x_d, L.x_d_stride, base + A.bx, A.bx_stride, w->H, w->top_k, n_tiles, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    return prefill_gemms(w, pw, T, ws, base, A, tiles, n_tiles, stream);
 }
 
 // ... with the rows where an exchange left them: packed rows [H int8][d_stride f32][int32 local expert id] (see ep_pack).

@@ -96,7 +96,7 @@ class ExpertParallelMoE:
         self.owner.E, self.owner.top_k, self.owner.F_s = self.E_loc, 1, 0
         self.max_tokens = max_tokens
         self.max_rows = max_tokens * self.k * world   # worst case: every pair of every rank lands here
-        self.ws_home = _Scratch(self.home, full_raw, max_tokens, dev)
+        self.ws_home = _Scratch(self.home, full_raw, max_tokens, dev, prefill=prefill and full_raw.F_s > 0)
         self.ws_owner = _Scratch(self.owner, full_raw, self.max_rows, dev, prefill=prefill)
         self.rows_pair = torch.empty(max_tokens * self.k, self.H, dtype=torch.float32, device=dev)
         self.back = torch.empty(max_tokens * self.k, self.H, dtype=torch.float32, device=dev)
@@ -126,8 +126,13 @@ class ExpertParallelMoE:
         abi.check(lib.chimere_b200_moe_route_home(C.byref(self.home), x.data_ptr(), T, C.byref(self.ws_home.ws), st), "route_home")
         abi.check(lib.chimere_b200_moe_ep_pack_sorted(C.byref(self.home), T, C.byref(self.ws_home.ws), ex["send"].data_ptr(), ex["slot"].data_ptr(),
                                                       self.E_loc, rb, st), "ep_pack_sorted")
-        # the shared expert needs nothing from other ranks: enqueue it before the exchanges
-        abi.check(lib.chimere_b200_moe_shared_expert(C.byref(self.home), T, C.byref(self.ws_home.ws), st), "shared_expert")
+        # the shared expert needs nothing from other ranks: enqueue it before the exchanges (on the grouped GEMM when the
+        # batch fills token tiles)
+        if self.pw_owner is not None and self.ws_home.prefill is not None and T >= 128:
+            abi.check(lib.chimere_b200_moe_shared_expert_prefill(C.byref(self.home), C.byref(self.pw_owner.struct), T, C.byref(self.ws_home.ws), st),
+                      "shared_expert_prefill")
+        else:
+            abi.check(lib.chimere_b200_moe_shared_expert(C.byref(self.home), T, C.byref(self.ws_home.ws), st), "shared_expert")
         send_counts_t = self.ws_home.offsets(self.E)[ex["bounds"]].diff().to(torch.int64)
         recv_counts_t = exchange_counts(send_counts_t, self.group)
         send_counts, recv_counts = send_counts_t.tolist(), recv_counts_t.tolist()   # host sync: split sizes

@@ -332,6 +332,10 @@ int chimere_b200_moe_routing_trace(const chimere_moe_layer* w, int T, const chim
  * prefill arena.  No counterpart in the reference (single GPU, no prefill kernel). */
 int chimere_b200_moe_experts_prefill(const chimere_moe_layer* w_local, const chimere_moe_prefill_weights* pw_local, int n_rows,
                                      chimere_moe_workspace* ws, cudaStream_t stream);
+/* Expert-parallel home rank, prefill-size batches: chimere_b200_moe_shared_expert on the grouped GEMM.  pw: a GEMM copy that
+ * holds the shared expert's matrices; ws needs the prefill arena.  Overwrites the work list of the routing call. */
+int chimere_b200_moe_shared_expert_prefill(const chimere_moe_layer* w, const chimere_moe_prefill_weights* pw, int T,
+                                           chimere_moe_workspace* ws, cudaStream_t stream);
 /* The same on rows that lie where an exchange left them (the row format of chimere_b200_moe_ep_pack). */
 int chimere_b200_moe_experts_packed_prefill(const chimere_moe_layer* w_local, const chimere_moe_prefill_weights* pw_local,
                                             int n_rows, const void* d_rows, int row_bytes, chimere_moe_workspace* ws,
