@@ -150,7 +150,11 @@ int chimere_b200_gguf_open(const char* path, chimere_gguf** out) {
         t.n_dims = (int32_t)nd;
         int64_t n_el = 1;
         for (int d = 0; d < 4; ++d) t.dims[d] = 1;
-        for (uint32_t d = 0; d < nd; ++d) { t.dims[d] = (int64_t)r.get<uint64_t>(); n_el *= t.dims[d]; }
+        for (uint32_t d = 0; d < nd; ++d) {
+            t.dims[d] = (int64_t)r.get<uint64_t>();
+            if (t.dims[d] < 0 || __builtin_mul_overflow(n_el, t.dims[d], &n_el)) r.ok = false;   // (a foreign or damaged file)
+        }
+        if (!r.ok) break;
         t.ggml_type = (int32_t)r.get<uint32_t>();
         t.file_offset = (int64_t)r.get<uint64_t>();   // relative for now
         const TypeInfo ti = type_info(t.ggml_type);
