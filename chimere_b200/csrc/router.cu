@@ -440,15 +440,19 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
 // Larger batches.  The order of the additions is fixed (256 partial sums per output, tree of strides 128 .. 1), so
 // a thread can only ever own one partial of an output, and the operands of an output tile have to pass through the
 // SM once per tile: the kernel is bound by how many outputs a CTA can hold per router row it fetches.
-// CTA = 512 threads = two token groups of 256 threads.  Thread (g, p) keeps elements p, p+256, ... of eight token
-// rows in registers (sixteen tokens per CTA) and owns partial p of every output of its group; the router rows come
-// four at a time through a ring of bulk copies shared by both groups, so every fetched row feeds sixteen tokens.
-// The 64 x 256 partial sums of a step are left in shared memory and summed by the sixteen warps, four outputs each,
-// in the reference's order.  A CTA whose row group starts at row 0
+// CTA = kBigGroups token groups of 256 threads.  Thread (g, p) keeps elements p, p+256, ... of eight token rows in
+// registers and owns partial p of every output of its group; the router rows come four at a time through a ring of bulk
+// copies shared by the CTA's groups.  The 32 x 256 partial sums a group makes per step are left in shared memory and summed
+// by the group's eight warps, four outputs each, in the reference's order.  One group per CTA and two CTAs per SM measured
+// faster than two groups in one CTA (747 against 834 us at T = 8192, the same at T = 2048): the phases of a step
+// (multiply-adds, partial sums to shared memory, tree) use different units, and two independent CTAs overlap them where
+// two groups that share their barriers cannot.  A CTA whose row group starts at row 0
 // also writes the Q8_1 form of its tokens, from the values it holds anyway.
-// grid = (row groups, token tiles of 16); NC = ceil(H / 256) <= 8 columns per thread; H a multiple of 32.
-constexpr int kBigTT = 8, kBigTE = 4, kBigThreads = 512, kBigRing = 4;
-constexpr int kBigRedFloats = 2 * kBigTT * kBigTE * 256;                 // [group][token][row][256] partial sums of one step
+// grid = (row groups, token tiles of kBigGroups * 8); NC = ceil(H / 256) <= 8 columns per thread; H a multiple of 32.
+constexpr int kBigGroups = 1;   // token groups (of 256 threads and kBigTT tokens) per CTA
+constexpr int kBigTT = 8, kBigTE = 4, kBigThreads = 256 * kBigGroups, kBigRing = kBigGroups == 1 ? 2 : 4;
+constexpr int kBigCtasPerSm = kBigGroups == 1 ? 2 : 1;
+constexpr int kBigRedFloats = kBigGroups * kBigTT * kBigTE * 256;        // [group][token][row][256] partial sums of one step
 static size_t big_route_smem(int H) { return (size_t)(kBigRedFloats + kBigRing * kBigTE * H) * sizeof(float); }
 // The same tree for two outputs whose partials are interleaved (partial i of the pair at r[2 * i], r[2 * i + 1]): one
 // 64-bit load serves both, two-wide adds keep each lane's order.  Valid in lane 0.
@@ -473,14 +477,14 @@ __device__ __forceinline__ void tree256_pair(const float* r, int lane, float& v0
 // The partial sums of two neighbouring tokens travel together (two-wide fused multiply-adds, each lane rounded like the
 // scalar instruction), so the sums of a step sit in shared memory as [group][token pair][row][partial][2].
 template <int NC, bool EXACT>
-__global__ void __launch_bounds__(kBigThreads, 1) route_big_kernel(const RouteParams p, int rows_per_group, int split_dispatch) {
+__global__ void __launch_bounds__(kBigThreads, kBigCtasPerSm) route_big_kernel(const RouteParams p, int rows_per_group, int split_dispatch) {
     extern __shared__ __align__(16) float smem_f[];   // [kBigRedFloats] partial sums, then [kBigRing][kBigTE][H] router rows
     __shared__ __align__(8) uint64_t s_full[kBigRing];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = tid >> 8, pt = tid & 255;
     const int H = EXACT ? NC * 256 : p.H, E = p.E;
     const int nrows = E + (p.shexp_gate_w ? 1 : 0);
-    const int t0 = blockIdx.y * (2 * kBigTT) + g * kBigTT;
+    const int t0 = blockIdx.y * (kBigGroups * kBigTT) + g * kBigTT;
     const int r_begin = blockIdx.x * rows_per_group, r_end = min(nrows, r_begin + rows_per_group);
     const int nsteps = (r_end - r_begin + kBigTE - 1) / kBigTE;
     if (tid == 0) griddep_launch();
@@ -568,7 +572,7 @@ __global__ void __launch_bounds__(kBigThreads, 1) route_big_kernel(const RoutePa
         {
             const int og = warp >> 3, a2 = (warp >> 1) & 3, bh = warp & 1;
             const float* rb = smem_f + og * (kBigTT * kBigTE * 256) + a2 * (kBigTE * 512);
-            const int t = blockIdx.y * (2 * kBigTT) + og * kBigTT + 2 * a2;
+            const int t = blockIdx.y * (kBigGroups * kBigTT) + og * kBigTT + 2 * a2;
 #pragma unroll
             for (int bb = 0; bb < kBigTE / 2; ++bb) {
                 const int b = bh * (kBigTE / 2) + bb, rr = r + b;
@@ -598,7 +602,7 @@ __global__ void __launch_bounds__(kBigThreads, 1) route_big_kernel(const RoutePa
     __threadfence();
     if (tid == 0) p.counters[kCtrRouteTile + blockIdx.y] = 0;
     {
-        const int t = blockIdx.y * (2 * kBigTT) + warp;
+        const int t = blockIdx.y * (kBigGroups * kBigTT) + warp;
         if (t < p.T) topk_warp(p, p.router_logits + (size_t)t * E, t, lane, smem_f + warp * 256, nullptr);
     }
     if (split_dispatch) return;   // three small launches follow and do the dispatch over the whole GPU
@@ -1076,10 +1080,10 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
         dim3 grid((nrows + TE - 1) / TE, (p.T + TT - 1) / TT);
         return launch_pdl(route_kernel<TT, TE>, grid, 256, route_smem(TT, TE), stream, p);
     } else if (p.H <= 2048 && p.H % 32 == 0) {
-        // token tiles of 16; the router rows are cut into row groups (multiples of four rows) only while there are too few
+        // token tiles of kBigGroups * 8; the router rows are cut into row groups (multiples of four rows) only while there are too few
         // token tiles to fill the GPU, because every row group fetches its tokens again
-        const int token_tiles = (p.T + 2 * kBigTT - 1) / (2 * kBigTT);
-        int groups = sm_count() / token_tiles;   // (rounded down: a second wave of a few CTAs would double the time)
+        const int token_tiles = (p.T + kBigGroups * kBigTT - 1) / (kBigGroups * kBigTT);
+        int groups = sm_count() * kBigCtasPerSm / token_tiles;   // (rounded down: a second wave of a few CTAs would double the time)
         const int max_groups = (nrows + kBigTE - 1) / kBigTE;
         groups = groups < 1 ? 1 : (groups > max_groups ? max_groups : groups);
         const int rows_per_group = kBigTE * (((nrows + groups - 1) / groups + kBigTE - 1) / kBigTE);
