@@ -490,3 +490,31 @@ def test_layer_with_kquant_shared_expert(sh_types, T, entry):
     t2 = MoeWeightsTiled(routed_only)
     y2 = forward_moe(t2, MoeScratch(t2, T), x)
     assert (y - y2).abs().max() > 1e-3 * y.abs().max()
+
+
+def test_kquant_shared_layer_through_the_host_and_residual_norm_entries():
+    """The other whole-layer entries on a layer with a Q5_K shared expert: host buffers (staged copy back, because the
+    shared expert's last step adds into y) and the fused residual-add + RMSNorm prologue."""
+    from chimere_b200.layer import forward_moe_residual_norm
+    cfg = configs.scaled(configs.QWEN_IQ3S, E=32, F=256, F_s=512, H=1024, type_sh_gate_up=formats.TYPE_Q5_K, type_sh_down=formats.TYPE_Q5_K, seed=33)
+    raw = configs.make_layer(cfg, device="cuda")
+    tiled = MoeWeightsTiled(raw)
+    T = 6
+    x = configs.make_input(cfg, T, device="cuda")
+    sc = MoeScratch(tiled, 8)
+    y = forward_moe(tiled, sc, x).clone()
+    xh, yh = x.cpu().pin_memory(), torch.empty(T, cfg.H).pin_memory()
+    forward_moe_host(tiled, sc, xh, yh)
+    assert torch.equal(yh, y.cpu())
+    # residual + norm prologue: hidden = 0, residual = x', unit weight -> the layer sees rmsnorm(x')
+    resid = (x * 3.0).clone()
+    y2 = forward_moe_residual_norm(tiled, sc, torch.zeros_like(x), resid, torch.ones(cfg.H, device="cuda"), 1e-6)
+    lib = abi.load()
+    normed = torch.empty_like(x)
+    abi.check(lib.chimere_b200_rmsnorm((x * 3.0).contiguous().data_ptr(), normed.data_ptr(), T, cfg.H, 1e-6, None), "rmsnorm")
+    y3 = forward_moe(tiled, MoeScratch(tiled, 8), normed)
+    torch.cuda.synchronize()
+    assert sc.status() == 0
+    assert (y2 - y3).abs().max() <= 2e-5 * y3.abs().max()
+    # the step-wise entries refuse such a layer
+    assert lib.chimere_b200_moe_route(C.byref(tiled.as_struct()), x.data_ptr(), T, C.byref(sc.ws), None) == -6
