@@ -110,6 +110,35 @@ __device__ __forceinline__ void group_units(const typename Tiled<TYPE>::Regs& r,
     }
 }
 
+// The same for one token against the same group of two matrices (up and gate rows of one tile): the token's quants,
+// scale and correction word are fetched once per unit and serve both, and the two dot chains are independent.
+template <int TYPE, bool FULL>
+__device__ __forceinline__ void group_units_pair(const typename Tiled<TYPE>::Regs& ra, const typename Tiled<TYPE>::Regs& rb, int g, int nu,
+                                                 uint32_t aq, uint32_t ad, float& acc_a, float& acc_b) {
+    using TT = Tiled<TYPE>;
+    float part_a = 0.0f, part_b = 0.0f;
+#pragma unroll
+    for (int u = 0; u < kGroupUnits; ++u) {
+        if (FULL || u < nu) {
+            const uint32_t qb = aq + (g * kGroupUnits + u) * 32, db = ad + (g * kGroupUnits + u) * 8;
+            const uint4 q0 = lds128(qb), q1 = lds128(qb + 16);
+            const uint2 dc = lds64(db);
+            const float dx = __uint_as_float(dc.x);
+            int wa[8], wb[8];
+            TT::decode(ra, u, wa);
+            TT::decode(rb, u, wb);
+            const float ta = (float)unit_dot<TYPE>(wa, q0, q1, (int)dc.y, ra, u);
+            const float tb = (float)unit_dot<TYPE>(wb, q0, q1, (int)dc.y, rb, u);
+            if (TT::kGroupScale) { part_a = fmaf(ta, dx, part_a); part_b = fmaf(tb, dx, part_b); }
+            else { acc_a = fmaf(TT::dscale(ra, u) * dx, ta, acc_a); acc_b = fmaf(TT::dscale(rb, u) * dx, tb, acc_b); }
+        }
+    }
+    if (TT::kGroupScale) {
+        acc_a = fmaf(TT::dscale(ra, 0), part_a, acc_a);
+        acc_b = fmaf(TT::dscale(rb, 0), part_b, acc_b);
+    }
+}
+
 // One pass over groups g0, g0+gstep, ... < ngroups of the tile at `tile` (global memory) for M tokens whose int8
 // rows start at shared address aq (row pitch qrow) and whose f32 scales start at shared address ad (row pitch
 // drow bytes): acc[i] += (scale_w * scale_x) * integer block dot.
@@ -330,6 +359,20 @@ __device__ __forceinline__ void dot_pass_s(uint32_t tile, int g0, int g1, int la
     }
 }
 
+template <int TYPE>
+__device__ __forceinline__ void dot_pass_pair_s(uint32_t tile_a, uint32_t tile_b, int g0, int g1, int lane, int nb, uint32_t aq, uint32_t ad,
+                                                float& acc_a, float& acc_b) {
+    using TT = Tiled<TYPE>;
+    for (int g = g0; g < g1; ++g) {
+        const int nu = min(kGroupUnits, nb - g * kGroupUnits);
+        typename TT::Regs ra, rb;
+        TT::loads(tile_a, g, lane, nu, ra);
+        TT::loads(tile_b, g, lane, nu, rb);
+        if (nu == kGroupUnits) group_units_pair<TYPE, true>(ra, rb, g, nu, aq, ad, acc_a, acc_b);
+        else group_units_pair<TYPE, false>(ra, rb, g, nu, aq, ad, acc_a, acc_b);
+    }
+}
+
 // grid = (row items, max entries), block = 32 * wr * wk threads (wk = 1 << wk_shift, wr = 1 << wr_shift).
 template <int TYPE, int STAGE, bool DUAL, int MT>
 __global__ void __launch_bounds__(kThreadsT, 3) bulk_kernel(const GemvParams p, int wk_shift, int wr_shift, uint32_t tile_bytes_max) {
@@ -420,6 +463,13 @@ __global__ void __launch_bounds__(kThreadsT, 3) bulk_kernel(const GemvParams p, 
             }
             arrived = true;
         }
+        if (DUAL && need_red && (MT == 1 || mp == 1)) {
+            // one token, gate and up rows of the tile together: the token's values are fetched once for both
+            float au = 0.0f, ag = 0.0f;
+            if (bytes > 0) dot_pass_pair_s<TYPE>(ws0, ws1, g0, g1, lane, nb, aq, ad, au, ag);
+            red[(wk_id * mt) * width + wr_id * 32 + lane] = au;
+            red[((wk + wk_id) * mt) * width + wr_id * 32 + lane] = ag;
+        } else
 #pragma unroll
         for (int mat = 0; mat < kMat; ++mat) {
             float acc[MT];
