@@ -80,6 +80,13 @@ int max_entries_for(const chimere_moe_layer* w, int T) {
     const int P = T * w->top_k;
     return (w->E < P ? w->E : P) + P / kMaxGroupTokens + (w->F_s > 0 ? (T + shared_group_tokens(T) - 1) / shared_group_tokens(T) : 0);
 }
+// The same bound when the ids come from the library's own top-k (distinct within a token): an expert's pairs are cut into
+// entries of kMaxGroupTokens, so with at most that many tokens no expert needs a second entry.  Sizes launch grids only.
+int routed_entries_for(const chimere_moe_layer* w, int T) {
+    const int P = T * w->top_k;
+    const int extra = T <= kMaxGroupTokens ? 0 : P / kMaxGroupTokens;
+    return (w->E < P ? w->E : P) + extra + (w->F_s > 0 ? (T + shared_group_tokens(T) - 1) / shared_group_tokens(T) : 0);
+}
 
 Layout make_layout(const chimere_moe_layer* w, int T) {
     if (kshared(w)) { const chimere_moe_layer r = routed_only(w); return make_layout(&r, T); }
@@ -522,7 +529,7 @@ int chimere_b200_moe_forward(const chimere_moe_layer* w, const float* d_x, float
     const chimere_moe_layer wr_ = ks ? routed_only(w) : *w;
     const chimere_moe_layer* wr = &wr_;
     const Layout L = make_layout(wr, ws->max_T);
-    const int max_entries = max_entries_for(wr, T);
+    const int max_entries = routed_entries_for(wr, T);
     cudaError_t e = launch_route(route_params(wr, d_x, T, ws, ks), stream);
     if (e != cudaSuccess) return cuda_rc(e);
     e = run_gate_up(wr, gate_up_params(wr, T, ws, L), max_entries, stream);
