@@ -81,6 +81,15 @@ __device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm(
 __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) { uint64_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
 __device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) { uint64_t d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
 
+// Counter increment that publishes this thread's (and, behind a CTA barrier, its CTA's) earlier writes and makes the
+// writes published by the other arrivals visible: release and acquire in the one instruction, instead of a fence on
+// either side of a relaxed atomic.  Returns the old value.
+__device__ __forceinline__ int atom_add_acq_rel_gpu(int* p, int v) {
+    int old;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+    return old;
+}
+
 // ---- programmatic dependent launch ---------------------------------------------------------
 // A kernel launched with the programmatic-serialization attribute may start while its predecessor in the
 // stream still runs; griddep_wait() blocks until that predecessor has completed and its writes are visible

@@ -289,19 +289,17 @@ __global__ void __launch_bounds__(kThreadsT, 4) tile_kernel(const GemvParams p, 
     }
     if (p.no_combine) return;
     // Whoever completes a token's contributions for this row tile adds them up.  The CTA barrier orders the rows
-    // written above before thread 0's device-scope fence (fences are cumulative); its second fence, before the
-    // next barrier, orders the reads below.
+    // written above before thread 0's counter increment, which releases them and acquires the other arrivals'
+    // (both cumulative); the next barrier orders the reads below behind it.
     __syncthreads();
     if (tid == 0) {
         const int expected = p.top_k + (p.nrows_shared > 0 ? 1 : 0);
-        __threadfence();
         for (int i = 0; i < m; ++i) {
             int* ctr = p.combine_ctr + (size_t)s_tok[i] * p.n_row_tiles + blockIdx.x;
-            const int c = atomicAdd(ctr, 1);
+            const int c = atom_add_acq_rel_gpu(ctr, 1);   // (release: the CTA's rows, behind the barrier above; acquire: the others')
             s_done[i] = (c == expected - 1);
             if (c == expected - 1) *ctr = 0;
         }
-        __threadfence();
     }
     __syncthreads();
     const int k = p.top_k;
@@ -556,14 +554,12 @@ __global__ void __launch_bounds__(kThreadsT, 3) bulk_kernel(const GemvParams p, 
     __syncthreads();
     if (tid == 0) {
         const int expected = p.top_k + (p.nrows_shared > 0 ? 1 : 0);
-        __threadfence();
         for (int i = 0; i < m; ++i) {
             int* ctr = p.combine_ctr + (size_t)s_tok[i] * p.n_row_tiles + blockIdx.x;
-            const int c = atomicAdd(ctr, 1);
+            const int c = atom_add_acq_rel_gpu(ctr, 1);   // (release: the CTA's rows, behind the barrier above; acquire: the others')
             s_done[i] = (c == expected - 1);
             if (c == expected - 1) *ctr = 0;
         }
-        __threadfence();
     }
     __syncthreads();
     const int k = p.top_k;

@@ -408,12 +408,10 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
     // ---- last CTA of the token tile: scores and top-k ----
     __shared__ int s_flag;
     __shared__ int s_ids[TT * kMaxTopK];
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) s_flag = (atomicAdd(&p.counters[kCtrRouteTile + blockIdx.y], 1) == n_rtiles - 1);
+    __syncthreads();   // every thread's writes are ordered before thread 0's counter increment, which releases them
+    if (tid == 0) s_flag = (atom_add_acq_rel_gpu(&p.counters[kCtrRouteTile + blockIdx.y], 1) == n_rtiles - 1);   // ... and acquires the other CTAs'
     __syncthreads();
     if (!s_flag) return;
-    __threadfence();
     if (tid == 0) p.counters[kCtrRouteTile + blockIdx.y] = 0;
     for (int a = warp; a < TT; a += 8) {
         const int t = t0 + a;
@@ -427,12 +425,10 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
         build_dispatch(p, reinterpret_cast<int*>(smem_f), s_ids, 0);
         return;
     }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) s_flag = (atomicAdd(&p.counters[kCtrRouteAll], 1) == (int)gridDim.y - 1);
+    __syncthreads();   // every thread's writes are ordered before thread 0's counter increment, which releases them
+    if (tid == 0) s_flag = (atom_add_acq_rel_gpu(&p.counters[kCtrRouteAll], 1) == (int)gridDim.y - 1);   // ... and acquires the other CTAs'
     __syncthreads();
     if (!s_flag) return;
-    __threadfence();
     if (tid == 0) p.counters[kCtrRouteAll] = 0;
     build_dispatch(p, reinterpret_cast<int*>(smem_f), nullptr, (int)(TT * TE * 256) - kDispatchSmemInts);
 }
@@ -594,12 +590,10 @@ __global__ void __launch_bounds__(kBigThreads, kBigCtasPerSm) route_big_kernel(c
 
     // ---- last CTA of the token tile: scores and top-k, one warp per token ----
     __shared__ int s_flag;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) s_flag = (atomicAdd(&p.counters[kCtrRouteTile + blockIdx.y], 1) == (int)gridDim.x - 1);
+    __syncthreads();   // every thread's writes are ordered before thread 0's counter increment, which releases them
+    if (tid == 0) s_flag = (atom_add_acq_rel_gpu(&p.counters[kCtrRouteTile + blockIdx.y], 1) == (int)gridDim.x - 1);   // ... and acquires the other CTAs'
     __syncthreads();
     if (!s_flag) return;
-    __threadfence();
     if (tid == 0) p.counters[kCtrRouteTile + blockIdx.y] = 0;
     {
         const int t = blockIdx.y * (kBigGroups * kBigTT) + warp;
@@ -607,12 +601,10 @@ __global__ void __launch_bounds__(kBigThreads, kBigCtasPerSm) route_big_kernel(c
     }
     if (split_dispatch) return;   // three small launches follow and do the dispatch over the whole GPU
     // ---- last token tile overall: dispatch permutation and work list (the first 256 threads) ----
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) s_flag = (atomicAdd(&p.counters[kCtrRouteAll], 1) == (int)gridDim.y - 1);
+    __syncthreads();   // every thread's writes are ordered before thread 0's counter increment, which releases them
+    if (tid == 0) s_flag = (atom_add_acq_rel_gpu(&p.counters[kCtrRouteAll], 1) == (int)gridDim.y - 1);   // ... and acquires the other CTAs'
     __syncthreads();
     if (!s_flag || tid >= 256) return;
-    __threadfence();
     if (tid == 0) p.counters[kCtrRouteAll] = 0;
     build_dispatch(p, reinterpret_cast<int*>(smem_f), nullptr, kBigRedFloats - kDispatchSmemInts);
 }
@@ -695,12 +687,10 @@ __global__ void __launch_bounds__(kDispatchChunk) dispatch_place_kernel(const Ro
     // ---- the chunk that finishes last writes the work list ----
     int32_t* ent_base = hist + (size_t)nchunks * 256;
     int32_t* done = ent_base + 258;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) s_last = (atomicAdd(done, 1) == nchunks - 1);
+    __syncthreads();   // every thread's writes are ordered before thread 0's counter increment, which releases them
+    if (tid == 0) s_last = (atom_add_acq_rel_gpu(done, 1) == nchunks - 1);   // ... and acquires the other CTAs'
     __syncthreads();
     if (!s_last) return;
-    __threadfence();
     __shared__ int s_ent[257], s_off[257];
     for (int x = tid; x < 257; x += kDispatchChunk) { s_ent[x] = __ldcg(ent_base + x); s_off[x] = x <= p.E ? __ldcg(p.offsets + x) : 0; }
     __syncthreads();
