@@ -294,12 +294,15 @@ __global__ void __launch_bounds__(kThreadsT, 4) tile_kernel(const GemvParams p, 
     __syncthreads();
     if (tid == 0) {
         const int expected = p.top_k + (p.nrows_shared > 0 ? 1 : 0);
+        // one token: release and acquire in the increment itself; several: one fence on either side of their increments
+        if (m > 1) __threadfence();
         for (int i = 0; i < m; ++i) {
             int* ctr = p.combine_ctr + (size_t)s_tok[i] * p.n_row_tiles + blockIdx.x;
-            const int c = atom_add_acq_rel_gpu(ctr, 1);   // (release: the CTA's rows, behind the barrier above; acquire: the others')
+            const int c = m > 1 ? atomicAdd(ctr, 1) : atom_add_acq_rel_gpu(ctr, 1);
             s_done[i] = (c == expected - 1);
             if (c == expected - 1) *ctr = 0;
         }
+        if (m > 1) __threadfence();
     }
     __syncthreads();
     const int k = p.top_k;
@@ -554,12 +557,15 @@ __global__ void __launch_bounds__(kThreadsT, 3) bulk_kernel(const GemvParams p, 
     __syncthreads();
     if (tid == 0) {
         const int expected = p.top_k + (p.nrows_shared > 0 ? 1 : 0);
+        // one token: release and acquire in the increment itself; several: one fence on either side of their increments
+        if (m > 1) __threadfence();
         for (int i = 0; i < m; ++i) {
             int* ctr = p.combine_ctr + (size_t)s_tok[i] * p.n_row_tiles + blockIdx.x;
-            const int c = atom_add_acq_rel_gpu(ctr, 1);   // (release: the CTA's rows, behind the barrier above; acquire: the others')
+            const int c = m > 1 ? atomicAdd(ctr, 1) : atom_add_acq_rel_gpu(ctr, 1);
             s_done[i] = (c == expected - 1);
             if (c == expected - 1) *ctr = 0;
         }
+        if (m > 1) __threadfence();
     }
     __syncthreads();
     const int k = p.top_k;
