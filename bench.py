@@ -671,7 +671,7 @@ def main():
     e2e = {"value": world * T * L * K / e2e_secs, "unit": UNIT, "h2d_bytes_per_step": L * T * cfg.H * 4,
            "d2h_bytes_per_step": L * T * cfg.H * 4, "ms_per_step": 1e3 * e2e_secs / K,
            "ms_per_step_stats": pct([1e3 * t for t in e2e_steps]),
-           "how": "chimere_b200_moe_forward_host per layer call: pinned host x copied in, layer, y copied out, stream synchronised; host clock"}
+           "how": "chimere_b200_moe_forward_host per layer call: pinned host x copied in, layer (its last kernel stores y straight into the pinned host buffer), stream synchronised; host clock"}
 
     status = max(sc.status() for sc in scratch)
     secondary, i8 = None, None
